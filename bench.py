@@ -1,0 +1,330 @@
+#!/usr/bin/env python
+"""Benchmark of the chunked-retention hot path (forward + backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload ns|c3|c4]
+
+Workload "ns" (default) is the configuration the headline metric is quoted on: chunked retention
+forward+backward, bf16, B=8, H=16, T=8192, dk=dv=128 per GPU, decays 1-2^-linspace(5,12,H), seeded
+synthetic inputs q,k,v ~ N(0,1)*d^-0.5, dO ~ N(0,1).  A step is one forward and one backward of the
+operator through the C ABI.  With N GPUs every rank runs the same per-GPU problem on its own batch
+rows (weak scaling, no collective on the data path); the time is the max over ranks.
+
+Prints ONE JSON line (rank 0).  `value` is algorithmic TFLOP/s with inputs resident in HBM; `e2e` is
+the same metric with host buffers (pinned) copied in and every result copied back inside the timed
+region.  `--impl reference` times the reference's PyTorch CPU algorithm (the CPU port in oracle/) on
+the host cores over a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: B, H, T, dk, dv, pop block (0 = plain retention)
+    "ns": dict(B=8, H=16, T=8192, dk=128, dv=128, block=0),
+    "c3": dict(B=4, H=32, T=16384, dk=128, dv=256, block=0),
+    "c4": dict(B=16, H=8, T=5120, dk=64, dv=64, block=80),
+}
+CHUNK = 64
+
+
+def flops_per_token_head(dk, dv, C=CHUNK):
+    ch = (C + 1) / 2
+    fwd = 2 * ch * (dk + dv) + 4 * dk * dv
+    bwd = 2 * ch * (3 * dk + 2 * dv) + 8 * dk * dv
+    return fwd, bwd
+
+
+def bytes_per_token_head(dk, dv, e=2):
+    return e * (2 * dk + 2 * dv), e * (4 * dk + 3 * dv)
+
+
+def decays_for(H):
+    import numpy as np
+    return tuple((1 - np.exp2(-np.linspace(5, 12, H))).tolist())
+
+
+def make_host_inputs(w, seed, pin):
+    g = torch.Generator().manual_seed(seed)
+    B, H, T, dk, dv = w["B"], w["H"], w["T"], w["dk"], w["dv"]
+    out = []
+    for d, sc in ((dk, dk ** -0.5), (dk, dk ** -0.5), (dv, dk ** -0.5), (dv, 1.0)):
+        t = torch.empty(B, T, H, d, dtype=torch.bfloat16)
+        for b in range(B):   # row by row keeps the fp32 temporary small
+            t[b] = (torch.randn(T, H, d, generator=g) * sc).to(torch.bfloat16)
+        out.append(t.pin_memory() if pin else t)
+    return out   # q, k, v, dO
+
+
+# --------------------------------------------------------------------------------------------------
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.rows, self.proc = index, [], None
+
+    def run(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            for line in self.proc.stdout:
+                self.rows.append([c.strip() for c in line.split(",")])
+        except Exception:
+            pass
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+        self.join(timeout=2)
+        sm, reasons, mx = [], set(), None
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx = float(r[1])
+            except Exception:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def event_time_ms(fn, steps):
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / steps
+
+
+# --------------------------------------------------------------------------------------------------
+def cpu_port_tflops(w, rows, reps, threads):
+    """The reference's PyTorch algorithm (CPU port in oracle/) forward+backward on `rows` batch rows."""
+    from oracle import retention_oracle as orc
+    torch.set_num_threads(threads)
+    H, T, dk, dv = w["H"], w["T"], w["dk"], w["dv"]
+    dec = decays_for(H)
+    g = torch.Generator().manual_seed(2)
+    q, k, v = (torch.randn(rows, T, H, d, generator=g) * dk ** -0.5 for d in (dk, dk, dv))
+    dO = torch.randn(rows, T, H, dv, generator=g)
+    best = float("inf")
+    for it in range(reps + 1):
+        leaves = [t.clone().requires_grad_(True) for t in (q, k, v)]
+        t0 = time.perf_counter()
+        if w["block"]:
+            o, bs = orc.pop_retention(*leaves, None, dec, w["block"])
+        else:
+            o, _ = orc.retention_chunkwise(*leaves, None, dec, chunk_size=CHUNK)
+        (o * dO).sum().backward()
+        dt = time.perf_counter() - t0
+        best = min(best, dt) if it else best   # first pass is the warm-up
+    ff, fb = flops_per_token_head(dk, dv)
+    return (ff + fb) * rows * T * H / best / 1e12, best
+
+
+def run_reference(args, w, rank):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    rows = 1
+    times = []
+    for i in range(args.warmup + args.steps):
+        tf, dt = cpu_port_tflops(w, rows, 1, threads)
+        if i >= args.warmup:
+            times.append(dt)
+    ff, fb = flops_per_token_head(w["dk"], w["dv"])
+    dt = sum(times) / len(times)
+    tf = (ff + fb) * rows * w["T"] * w["H"] / dt / 1e12
+    sample = f"{rows} of {w['B']} batch rows per step (H={w['H']}, T={w['T']}), fp32, chunk {CHUNK}, torch CPU"
+    line = {
+        "impl": "reference", "metric": "chunked_retention_fwd_bwd_tflops", "value": tf, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "tokens_per_s": rows * w["T"] / dt,
+        "config": {"workload": workload_name(args, w), "l2": "inputs larger than L2"},
+        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_name(args, w):
+    kind = "POP retention" if w["block"] else "chunked retention"
+    return (f"{kind} fwd+bwd bf16 B={w['B']} H={w['H']} T={w['T']} dk={w['dk']} dv={w['dv']} C={CHUNK}"
+            + (f" block={w['block']}" if w["block"] else "") + " per GPU")
+
+
+# --------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="ns", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    w = WORKLOADS[args.workload]
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, w, rank)
+        return
+
+    import torch.distributed as dist
+    import flash_pop_b200 as fp
+    from flash_pop_b200 import _lib
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    B, H, T, dk, dv = w["B"], w["H"], w["T"], w["dk"], w["dv"]
+    dec = decays_for(H)
+    hq, hk, hv, hdO = make_host_inputs(w, seed=2 + rank, pin=True)
+    q, k, v, dO = (t.to(dev, non_blocking=True) for t in (hq, hk, hv, hdO))
+    torch.cuda.synchronize()
+
+    def op(q_, k_, v_):
+        if w["block"]:
+            return fp.flash_pop_retention(q_, k_, v_, None, dec, w["block"])[0]
+        return fp.fused_chunk_retention(q_, k_, v_, None, dec)[0]
+
+    def step():
+        ql, kl, vl = (t.detach().requires_grad_(True) for t in (q, k, v))
+        o = op(ql, kl, vl)
+        o.backward(dO)
+        return o, ql.grad, kl.grad, vl.grad
+
+    def fwd_only():
+        with torch.no_grad():
+            return op(q, k, v)
+
+    for _ in range(args.warmup):
+        step()
+    _lib.device_status(dev)
+    path = _lib.last_path()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+        time.sleep(0.3)
+    launches0 = _lib.launch_count()
+    barrier()
+    ms = event_time_ms(step, args.steps)
+    barrier()
+    launches = _lib.launch_count() - launches0
+    clocks = sampler.stop() if sampler else None
+
+    # per-entry-point device times for the roofline (same inputs, > L2, so no flush needed)
+    ms_fwd = event_time_ms(fwd_only, max(args.steps, 5))
+    ms_bwd = max(ms - ms_fwd, 1e-6)
+
+    # end to end: host (pinned) -> device, forward+backward, every result back to the host
+    e2e_ms = None
+    h2d = sum(t.numel() * 2 for t in (hq, hk, hv, hdO))
+    d2h = (2 * hq.numel() + 2 * hv.numel()) * 2
+    if not args.no_e2e:
+        outs_host = [torch.empty_like(hv).pin_memory(), torch.empty_like(hq).pin_memory(),
+                     torch.empty_like(hk).pin_memory(), torch.empty_like(hv).pin_memory()]
+
+        def e2e_step():
+            nonlocal q, k, v, dO
+            q.copy_(hq, non_blocking=True); k.copy_(hk, non_blocking=True)
+            v.copy_(hv, non_blocking=True); dO.copy_(hdO, non_blocking=True)
+            res = step()
+            for dst, src in zip(outs_host, res):
+                dst.copy_(src, non_blocking=True)
+
+        e2e_step()
+        barrier()
+        e2e_ms = event_time_ms(e2e_step, max(3, min(args.steps, 5)))
+        barrier()
+
+    t_ms = torch.tensor([ms, ms_fwd, ms_bwd, e2e_ms or 0.0], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
+    ms, ms_fwd, ms_bwd, e2e_max = t_ms.tolist()
+    _lib.device_status(dev)
+
+    if rank == 0:
+        ff, fb = flops_per_token_head(dk, dv)
+        bf, bb = bytes_per_token_head(dk, dv)
+        units = B * T * H                       # token-heads per GPU per step
+        total_flop = (ff + fb) * units * world
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+            peak_src = "measured"
+        except Exception:
+            peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+            peak_src = "fallback"
+        value = total_flop / (ms * 1e-3) / 1e12
+        # the backward takes the larger share of a step: it is the dominant launch group
+        dom_bytes, dom_ms, dom_name = (bb * units, ms_bwd, "backward (dK/dV/dS + dQ kernels)")
+        if ms_fwd > ms_bwd:
+            dom_bytes, dom_ms, dom_name = (bf * units, ms_fwd, "forward kernel")
+        achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
+        line = {
+            "metric": "chunked_retention_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "tokens_per_s": B * T * world / (ms * 1e-3),
+            "pct_bf16_peak_nominal": 100 * value / world / 2250.0,
+            "pct_bf16_peak_measured": 100 * value / world / peaks.get("bf16_tflops", 1590.0),
+            "hbm_gbs_algorithmic": (bf + bb) * units / (ms * 1e-3) / 1e9,
+            "ms_fwd": ms_fwd, "ms_bwd": ms_bwd,
+            "path": {1: "cuda-core", 2: "tcgen05"}.get(path, "none"),
+            "config": {"workload": workload_name(args, w), "l2": "inputs (1 GB+) larger than the 126 MB L2; no flush",
+                       "flop_count": "algorithmic, causal half of intra-chunk tiles (C=64)"},
+            "roofline": {"bound": "hbm", "kernel": dom_name, "achieved": achieved, "peak": peaks["hbm_gbs"],
+                         "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peak_src, "traffic": None},
+            "clocks": clocks,
+            "gpu_launches": launches,
+        }
+        if e2e_ms is not None:
+            line["e2e"] = {"value": total_flop / (e2e_max * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_max,
+                           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+        if not args.no_cpu_baseline and world == 1:
+            threads = os.cpu_count() or 1
+            tf, dt = cpu_port_tflops(w, 1, 2, threads)
+            line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                                    "sample": f"1 of {B} batch rows (H={H}, T={T}), fp32 torch CPU, chunk {CHUNK}, "
+                                              f"best of 2 after a warm-up, {dt:.2f} s per pass"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

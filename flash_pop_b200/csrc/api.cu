@@ -1,0 +1,337 @@
+// extern "C" entry points of flash_pop_b200: argument validation, choice between the tcgen05
+// kernels and the CUDA-core kernels, launches.  Declarations and the reference interfaces each
+// entry point replaces are in include/flash_pop_b200.h.
+#include <atomic>
+#include <cmath>
+#include <cstring>
+
+#include "fpb_common.cuh"
+#include "umma_launch.h"
+
+namespace fpb {
+
+__device__ int32_t g_device_status = 0;
+
+int32_t* device_status_ptr() {
+  // one address per device; a handful of devices at most
+  static std::atomic<int32_t*> cache[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  int32_t* p = cache[dev].load(std::memory_order_acquire);
+  if (!p) {
+    void* sym = nullptr;
+    if (cudaGetSymbolAddress(&sym, g_device_status) != cudaSuccess) return nullptr;
+    p = (int32_t*)sym;
+    cache[dev].store(p, std::memory_order_release);
+  }
+  return p;
+}
+
+namespace {
+
+thread_local int tl_last_path = FPB_PATH_NONE;
+thread_local int tl_last_cuda_error = 0;
+std::atomic<int64_t> g_launches{0};
+
+struct Call {
+  int dtype, B, T, H, dk, dv, block_size, n_blocks, flags;
+  float gamma[FPB_MAX_HEADS];
+  bool tensor_core_decays;   // every decay large enough for the gamma^-L rescaling of the tcgen05 path
+};
+
+SeqView view(const fpb_seq* s) { return s ? SeqView{s->data, s->stride_b, s->stride_t, s->stride_h} : SeqView{nullptr, 0, 0, 0}; }
+StateView view(const fpb_state* s) { return s ? StateView{s->data, s->stride_b, s->stride_h} : StateView{nullptr, 0, 0}; }
+
+int check_device() {
+  static std::atomic<int> ok[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return FPB_ERR_NO_DEVICE_CODE;
+  if (dev >= 0 && dev < 64 && ok[dev].load()) return FPB_OK;
+  int major = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess || major != 10)
+    return FPB_ERR_NO_DEVICE_CODE;
+  if (dev >= 0 && dev < 64) ok[dev].store(1);
+  return FPB_OK;
+}
+
+int check_dims(const fpb_dims* d, bool pop, Call* c) {
+  if (!d) return FPB_ERR_NULL_POINTER;
+  if (d->dtype != FPB_BF16 && d->dtype != FPB_F32) return FPB_ERR_BAD_DTYPE;
+  if (d->B < 0 || d->T < 0 || d->H < 0 || d->dk <= 0 || d->dv <= 0) return FPB_ERR_BAD_SHAPE;
+  if (d->H > FPB_MAX_HEADS || d->dk > 256 || d->dv > 256) return FPB_ERR_BAD_SHAPE;
+  if (pop && d->block_size <= 0) return FPB_ERR_BAD_BLOCK_SIZE;
+  if (d->H > 0 && !d->head_decays) return FPB_ERR_NULL_POINTER;
+  c->dtype = d->dtype; c->B = d->B; c->T = d->T; c->H = d->H; c->dk = d->dk; c->dv = d->dv;
+  c->flags = d->flags;
+  c->block_size = pop ? d->block_size : 0;
+  c->n_blocks = pop ? d->T / d->block_size : 0;
+  c->tensor_core_decays = true;
+  for (int h = 0; h < d->H; ++h) {
+    const double g = d->head_decays[h];
+    if (!std::isfinite(g) || g < 0.0 || g > 1.0) return FPB_ERR_BAD_DECAY;
+    c->gamma[h] = (float)g;              // the reference rounds gamma to fp32 before any power
+    if (g < 0.5) c->tensor_core_decays = false;
+  }
+  return FPB_OK;
+}
+
+int check_seq(const Call& c, const fpb_seq* s, int d, int64_t batch) {
+  if (!s) return FPB_ERR_NULL_POINTER;
+  const bool empty = batch == 0 || c.T == 0 || c.H == 0;
+  if (!s->data) return empty ? FPB_OK : FPB_ERR_NULL_POINTER;
+  if ((batch > 1 && s->stride_b <= 0) || (c.T > 1 && s->stride_t <= 0) || (c.H > 1 && s->stride_h < d))
+    return FPB_ERR_BAD_STRIDE;
+  return FPB_OK;
+}
+
+int check_state(const fpb_state* s, const Call& c) {
+  if (!s || !s->data) return FPB_OK;
+  const int64_t blk = (int64_t)c.dk * c.dv;
+  if ((c.H > 1 && s->stride_h < blk) || (c.B > 1 && s->stride_b < blk)) return FPB_ERR_BAD_STRIDE;
+  return FPB_OK;
+}
+
+int finish_launches(int n, int path) {
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { tl_last_cuda_error = (int)e; return FPB_ERR_LAUNCH; }
+  g_launches.fetch_add(n);
+  tl_last_path = path;
+  return FPB_OK;
+}
+
+void fill_common(WalkParams& p, const Call& c, int dir, const SuffixStates& sfx) {
+  std::memset(&p, 0, sizeof(p));
+  p.T = c.T; p.H = c.H; p.dk = c.dk; p.dv = c.dv; p.dir = dir;
+  p.block_size = c.block_size; p.n_blocks = c.n_blocks;
+  p.scale_u = p.scale_w = p.scale_r = p.scale_out = 1.0f;
+  p.sfx = sfx;
+  std::memcpy(p.gamma, c.gamma, sizeof(float) * c.H);
+}
+
+void own_is_dv(WalkParams& p, const Call& c) { p.n_own = c.dv; p.n_red = c.dk; p.x_stride_red = c.dv; p.x_stride_own = 1; }
+void own_is_dk(WalkParams& p, const Call& c) { p.n_own = c.dk; p.n_red = c.dv; p.x_stride_red = 1; p.x_stride_own = c.dv; }
+
+// ---- forward (plain, POP, suffix) --------------------------------------------------------------
+int forward(const Call& c, int64_t batch, SeqView q, SeqView k, SeqView v, StateView s0, SeqView o, StateView s_out,
+            void* block_states, SuffixStates sfx, cudaStream_t stream) {
+  if (batch == 0 || c.H == 0) return FPB_OK;
+  const float rs = 1.0f / sqrtf((float)c.dk);
+  if (!(c.flags & FPB_FLAG_FORCE_SIMT) && c.tensor_core_decays && c.T > 0) {
+    UmmaFwdArgs a{};
+    a.q = q; a.k = k; a.v = v; a.o = o; a.s0 = s0; a.s_out = s_out; a.block_states = block_states; a.sfx = sfx;
+    a.B = (int)batch; a.T = c.T; a.H = c.H; a.dk = c.dk; a.dv = c.dv; a.dtype = c.dtype;
+    a.block_size = c.block_size; a.n_blocks = c.n_blocks; a.gamma = c.gamma;
+    const int r = launch_umma_fwd(a, stream);
+    if (r == FPB_OK) return finish_launches(1, FPB_PATH_TCGEN05);
+    if (r != FPB_UMMA_NOT_APPLICABLE) return r;
+  }
+  WalkParams p;
+  fill_common(p, c, +1, sfx);
+  own_is_dv(p, c);
+  p.u = v; p.w = k; p.r = q; p.out = o; p.scale_w = rs;
+  p.x0 = s0; p.x_out = s_out; p.block_out = block_states;
+  const int r = launch_walk(p, c.dtype, (int)batch, stream);
+  return r != FPB_OK ? r : finish_launches(1, FPB_PATH_SIMT);
+}
+
+// ---- backward (plain, POP, suffix) -------------------------------------------------------------
+int backward(const Call& c, int64_t batch, SeqView q, SeqView k, SeqView v, StateView s0, SeqView dO, StateView d_s_out,
+             const void* d_block_states, SeqView dQ, SeqView dK, SeqView dV, StateView d_s0, SuffixStates sfx_in,
+             SuffixStates sfx_grad, cudaStream_t stream) {
+  if (batch == 0 || c.H == 0) return FPB_OK;
+  const float rs = 1.0f / sqrtf((float)c.dk);
+  if (!(c.flags & FPB_FLAG_FORCE_SIMT) && c.tensor_core_decays && c.T > 0) {
+    UmmaBwdArgs a{};
+    a.q = q; a.k = k; a.v = v; a.dO = dO; a.dQ = dQ; a.dK = dK; a.dV = dV;
+    a.s0 = s0; a.d_s_out = d_s_out; a.d_s0 = d_s0; a.d_block_states = d_block_states;
+    a.sfx_in = sfx_in; a.sfx_grad = sfx_grad;
+    a.B = (int)batch; a.T = c.T; a.H = c.H; a.dk = c.dk; a.dv = c.dv; a.dtype = c.dtype;
+    a.block_size = c.block_size; a.n_blocks = c.n_blocks; a.gamma = c.gamma;
+    int n_launched = 0;
+    const int r = launch_umma_bwd(a, stream, &n_launched);
+    if (r == FPB_OK) return finish_launches(n_launched, FPB_PATH_TCGEN05);
+    if (r != FPB_UMMA_NOT_APPLICABLE) return r;
+  }
+  WalkParams p;
+  int r;
+  // dQ: forward walk over the states
+  fill_common(p, c, +1, sfx_in);
+  own_is_dk(p, c);
+  p.u = k; p.w = v; p.r = dO; p.out = dQ; p.scale_u = rs; p.x0 = s0;
+  if ((r = launch_walk(p, c.dtype, (int)batch, stream)) != FPB_OK) return r;
+  // dV and dS_0: reverse walk over the state gradient
+  fill_common(p, c, -1, sfx_grad);
+  own_is_dv(p, c);
+  p.u = dO; p.w = q; p.r = k; p.out = dV; p.scale_r = rs;
+  p.x0 = d_s_out; p.x_out = d_s0; p.block_in = d_block_states;
+  if ((r = launch_walk(p, c.dtype, (int)batch, stream)) != FPB_OK) return r;
+  // dK: reverse walk, transposed ownership
+  SuffixStates no_write = sfx_grad;
+  no_write.blocks = nullptr;
+  fill_common(p, c, -1, no_write);
+  own_is_dk(p, c);
+  p.u = q; p.w = dO; p.r = v; p.out = dK; p.scale_out = rs;
+  p.x0 = d_s_out; p.block_in = d_block_states;
+  if ((r = launch_walk(p, c.dtype, (int)batch, stream)) != FPB_OK) return r;
+  return finish_launches(3, FPB_PATH_SIMT);
+}
+
+}  // namespace
+}  // namespace fpb
+
+using namespace fpb;
+
+#define FPB_TRY(expr) do { const int _s = (expr); if (_s != FPB_OK) return _s; } while (0)
+
+extern "C" {
+
+int fpb_retention_fwd(const fpb_dims* dims, const fpb_seq* q, const fpb_seq* k, const fpb_seq* v,
+                      const fpb_state* s0, const fpb_seq* o, const fpb_state* s_out, fpb_stream_t stream) {
+  Call c;
+  FPB_TRY(check_dims(dims, false, &c));
+  FPB_TRY(check_seq(c, q, c.dk, c.B)); FPB_TRY(check_seq(c, k, c.dk, c.B));
+  FPB_TRY(check_seq(c, v, c.dv, c.B)); FPB_TRY(check_seq(c, o, c.dv, c.B));
+  FPB_TRY(check_state(s0, c)); FPB_TRY(check_state(s_out, c));
+  FPB_TRY(check_device());
+  return forward(c, c.B, view(q), view(k), view(v), view(s0), view(o), view(s_out), nullptr, SuffixStates{0, 0, nullptr},
+                 (cudaStream_t)stream);
+}
+
+int fpb_retention_bwd(const fpb_dims* dims, const fpb_seq* q, const fpb_seq* k, const fpb_seq* v,
+                      const fpb_state* s0, const fpb_seq* d_o, const fpb_state* d_s_out,
+                      const fpb_seq* d_q, const fpb_seq* d_k, const fpb_seq* d_v, const fpb_state* d_s0,
+                      fpb_stream_t stream) {
+  Call c;
+  FPB_TRY(check_dims(dims, false, &c));
+  FPB_TRY(check_seq(c, q, c.dk, c.B)); FPB_TRY(check_seq(c, k, c.dk, c.B)); FPB_TRY(check_seq(c, v, c.dv, c.B));
+  FPB_TRY(check_seq(c, d_o, c.dv, c.B));
+  FPB_TRY(check_seq(c, d_q, c.dk, c.B)); FPB_TRY(check_seq(c, d_k, c.dk, c.B)); FPB_TRY(check_seq(c, d_v, c.dv, c.B));
+  FPB_TRY(check_state(s0, c)); FPB_TRY(check_state(d_s_out, c)); FPB_TRY(check_state(d_s0, c));
+  FPB_TRY(check_device());
+  const SuffixStates none{0, 0, nullptr};
+  return backward(c, c.B, view(q), view(k), view(v), view(s0), view(d_o), view(d_s_out), nullptr, view(d_q), view(d_k),
+                  view(d_v), view(d_s0), none, none, (cudaStream_t)stream);
+}
+
+int fpb_pop_retention_fwd(const fpb_dims* dims, const fpb_seq* q, const fpb_seq* k, const fpb_seq* v,
+                          const fpb_state* s0, const fpb_seq* o, void* block_states, fpb_stream_t stream) {
+  Call c;
+  FPB_TRY(check_dims(dims, true, &c));
+  FPB_TRY(check_seq(c, q, c.dk, c.B)); FPB_TRY(check_seq(c, k, c.dk, c.B));
+  FPB_TRY(check_seq(c, v, c.dv, c.B)); FPB_TRY(check_seq(c, o, c.dv, c.B));
+  FPB_TRY(check_state(s0, c));
+  if (c.n_blocks > 0 && c.B > 0 && c.H > 0 && !block_states) return FPB_ERR_NULL_POINTER;
+  FPB_TRY(check_device());
+  return forward(c, c.B, view(q), view(k), view(v), view(s0), view(o), StateView{nullptr, 0, 0}, block_states,
+                 SuffixStates{0, 0, nullptr}, (cudaStream_t)stream);
+}
+
+int fpb_pop_retention_bwd(const fpb_dims* dims, const fpb_seq* q, const fpb_seq* k, const fpb_seq* v,
+                          const fpb_state* s0, const fpb_seq* d_o, const void* d_block_states,
+                          const fpb_seq* d_q, const fpb_seq* d_k, const fpb_seq* d_v, const fpb_state* d_s0,
+                          fpb_stream_t stream) {
+  Call c;
+  FPB_TRY(check_dims(dims, true, &c));
+  FPB_TRY(check_seq(c, q, c.dk, c.B)); FPB_TRY(check_seq(c, k, c.dk, c.B)); FPB_TRY(check_seq(c, v, c.dv, c.B));
+  FPB_TRY(check_seq(c, d_o, c.dv, c.B));
+  FPB_TRY(check_seq(c, d_q, c.dk, c.B)); FPB_TRY(check_seq(c, d_k, c.dk, c.B)); FPB_TRY(check_seq(c, d_v, c.dv, c.B));
+  FPB_TRY(check_state(s0, c)); FPB_TRY(check_state(d_s0, c));
+  FPB_TRY(check_device());
+  const SuffixStates none{0, 0, nullptr};
+  return backward(c, c.B, view(q), view(k), view(v), view(s0), view(d_o), StateView{nullptr, 0, 0}, d_block_states,
+                  view(d_q), view(d_k), view(d_v), view(d_s0), none, none, (cudaStream_t)stream);
+}
+
+int fpb_pop_suffix_fwd(const fpb_dims* dims, int32_t M, int32_t N, const fpb_seq* q, const fpb_seq* k,
+                       const fpb_seq* v, const fpb_state* s0, const void* block_states, const fpb_seq* o,
+                       fpb_stream_t stream) {
+  Call c;
+  FPB_TRY(check_dims(dims, false, &c));
+  if (M < 0 || N < 0 || M > N + 1) return FPB_ERR_BAD_SHAPE;
+  const int64_t batch = (int64_t)c.B * M;
+  if (batch > 0x7fffffff) return FPB_ERR_TOO_LARGE;
+  FPB_TRY(check_seq(c, q, c.dk, batch)); FPB_TRY(check_seq(c, k, c.dk, batch));
+  FPB_TRY(check_seq(c, v, c.dv, batch)); FPB_TRY(check_seq(c, o, c.dv, batch));
+  FPB_TRY(check_state(s0, c));
+  if (M > 1 && c.B > 0 && c.H > 0 && !block_states) return FPB_ERR_NULL_POINTER;
+  FPB_TRY(check_device());
+  if (M == 0) return FPB_OK;
+  return forward(c, batch, view(q), view(k), view(v), view(s0), view(o), StateView{nullptr, 0, 0}, nullptr,
+                 SuffixStates{M, N, const_cast<void*>(block_states)}, (cudaStream_t)stream);
+}
+
+int fpb_pop_suffix_bwd(const fpb_dims* dims, int32_t M, int32_t N, const fpb_seq* q, const fpb_seq* k,
+                       const fpb_seq* v, const fpb_state* s0, const void* block_states, const fpb_seq* d_o,
+                       const fpb_seq* d_q, const fpb_seq* d_k, const fpb_seq* d_v, const fpb_state* d_s0,
+                       void* d_block_states, fpb_stream_t stream) {
+  Call c;
+  FPB_TRY(check_dims(dims, false, &c));
+  if (M < 0 || N < 0 || M > N + 1) return FPB_ERR_BAD_SHAPE;
+  const int64_t batch = (int64_t)c.B * M;
+  if (batch > 0x7fffffff) return FPB_ERR_TOO_LARGE;
+  FPB_TRY(check_seq(c, q, c.dk, batch)); FPB_TRY(check_seq(c, k, c.dk, batch)); FPB_TRY(check_seq(c, v, c.dv, batch));
+  FPB_TRY(check_seq(c, d_o, c.dv, batch));
+  FPB_TRY(check_seq(c, d_q, c.dk, batch)); FPB_TRY(check_seq(c, d_k, c.dk, batch)); FPB_TRY(check_seq(c, d_v, c.dv, batch));
+  FPB_TRY(check_state(s0, c)); FPB_TRY(check_state(d_s0, c));
+  if (M > 1 && c.B > 0 && c.H > 0 && (!block_states || !d_block_states)) return FPB_ERR_NULL_POINTER;
+  FPB_TRY(check_device());
+  if (c.B == 0 || c.H == 0) return FPB_OK;
+  const size_t esize = c.dtype == FPB_F32 ? 4 : 2;
+  const size_t blk = (size_t)c.H * c.dk * c.dv * esize;
+  // blocks that no suffix starts from get a zero gradient
+  if (d_block_states && N > 0) {
+    const int used = M > 0 ? M - 1 : 0;
+    if (used < N) {
+      if (cudaMemset2DAsync((char*)d_block_states + used * blk, (size_t)N * blk, 0, (size_t)(N - used) * blk, c.B,
+                            (cudaStream_t)stream) != cudaSuccess)
+        return finish_launches(0, FPB_PATH_NONE);
+    }
+  }
+  if (M == 0) {
+    if (d_s0 && d_s0->data) {
+      for (int b = 0; b < c.B; ++b)
+        cudaMemset2DAsync((char*)d_s0->data + b * d_s0->stride_b * esize, d_s0->stride_h * esize, 0,
+                          (size_t)c.dk * c.dv * esize, c.H, (cudaStream_t)stream);
+    }
+    return finish_launches(0, FPB_PATH_NONE);
+  }
+  return backward(c, batch, view(q), view(k), view(v), view(s0), view(d_o), StateView{nullptr, 0, 0}, nullptr, view(d_q),
+                  view(d_k), view(d_v), view(d_s0), SuffixStates{M, N, const_cast<void*>(block_states)},
+                  SuffixStates{M, N, d_block_states}, (cudaStream_t)stream);
+}
+
+const char* fpb_strerror(int status) {
+  switch (status) {
+    case FPB_OK: return "ok";
+    case FPB_ERR_NULL_POINTER: return "a required pointer is null";
+    case FPB_ERR_BAD_SHAPE: return "unsupported or inconsistent shape (need 0 < dk, dv <= 256, H <= 256)";
+    case FPB_ERR_BAD_DTYPE: return "unsupported dtype (bf16 and fp32 only)";
+    case FPB_ERR_BAD_STRIDE: return "bad stride (inner stride must be 1, others positive and non-overlapping)";
+    case FPB_ERR_BAD_DECAY: return "head decay outside [0, 1] or not finite";
+    case FPB_ERR_BAD_BLOCK_SIZE: return "block_size must be positive";
+    case FPB_ERR_NO_DEVICE_CODE: return "current CUDA device is not sm_100 (B200); this library has no other code path";
+    case FPB_ERR_LAUNCH: return "CUDA launch failed (see fpb_last_cuda_error)";
+    case FPB_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel gave up";
+    case FPB_ERR_TENSOR_MAP: return "could not encode a TMA tensor map for a tensor";
+    case FPB_ERR_TOO_LARGE: return "size beyond a fixed limit of this entry point";
+    default: return "unknown status";
+  }
+}
+
+int fpb_version(void) { return 100; }
+int fpb_last_path(void) { return tl_last_path; }
+int fpb_last_cuda_error(void) { return tl_last_cuda_error; }
+int64_t fpb_launch_count(void) { return g_launches.load(); }
+
+int fpb_device_status(fpb_stream_t stream, int32_t* detail) {
+  if (cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess) { tl_last_cuda_error = (int)cudaGetLastError(); return FPB_ERR_LAUNCH; }
+  int32_t word = 0;
+  if (cudaMemcpyFromSymbol(&word, g_device_status, sizeof(word)) != cudaSuccess) { tl_last_cuda_error = (int)cudaGetLastError(); return FPB_ERR_LAUNCH; }
+  if (detail) *detail = word;
+  if (word == 0) return FPB_OK;
+  const int32_t zero = 0;
+  cudaMemcpyToSymbol(g_device_status, &zero, sizeof(zero));
+  return FPB_ERR_DEVICE_TIMEOUT;
+}
+
+}  // extern "C"

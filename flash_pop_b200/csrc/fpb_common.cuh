@@ -1,0 +1,56 @@
+// Shared declarations of the flash_pop_b200 CUDA sources: launch parameter blocks, the device
+// status word, and the internal launcher interface between api.cu and the kernel files.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#include "../../include/flash_pop_b200.h"
+
+#define FPB_MAX_HEADS 256
+
+namespace fpb {
+
+// One (B,T,H,d) tensor as the kernels see it.
+struct SeqView {
+  void* data;
+  int64_t sb, st, sh;
+};
+
+// One (B,H,dk,dv) state, or a slice of a (B,N,H,dk,dv) block-state tensor.
+struct StateView {
+  void* data;
+  int64_t sb, sh;
+};
+
+// Where a walk starts (or a reverse walk ends) when the batch is a flattened (row, suffix) pair:
+// suffix m of row r uses first[r] for m == 0 and blocks[r, m-1] otherwise.
+struct SuffixStates {
+  int32_t M;           // suffixes per row; 0 = not a suffix call
+  int32_t N;           // blocks per row in `blocks`
+  void* blocks;        // (B, N, H, dk, dv) contiguous
+};
+
+// Parameters of the CUDA-core "walk" kernel (walk_generic.cu).
+struct WalkParams {
+  SeqView u, w, r, out;
+  StateView x0, x_out;
+  SuffixStates sfx;
+  void* block_out;         // forward: states after full blocks (B, NB, H, dk, dv)
+  const void* block_in;    // reverse: gradients of those states
+  int64_t x_stride_red, x_stride_own;   // element strides inside one (dk, dv) state
+  int32_t n_own, n_red, T, H, dk, dv;
+  int32_t dir;             // +1 walks t = 0..T-1, -1 walks t = T-1..0
+  int32_t block_size, n_blocks;
+  float scale_u, scale_w, scale_r, scale_out;
+  float gamma[FPB_MAX_HEADS];
+};
+
+int launch_walk(const WalkParams& p, int dtype, int B, cudaStream_t stream);
+
+// Device status word shared by all kernels: 0 = fine; otherwise (role << 8 | barrier id) of the
+// first bounded wait that gave up.
+int32_t* device_status_ptr();
+
+}  // namespace fpb

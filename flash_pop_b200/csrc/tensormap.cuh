@@ -1,0 +1,54 @@
+// Host-side construction of TMA tensor maps for (B,T,H,d) bf16 activations.  The driver entry point
+// cuTensorMapEncodeTiled is looked up at run time through the CUDA runtime, so the library does not
+// link against libcuda and can be built on a machine without a GPU driver.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "fpb_common.cuh"
+
+namespace fpb {
+
+typedef CUresult (*tensor_map_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                         const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                         CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline tensor_map_encode_fn tensor_map_encoder() {
+  static tensor_map_encode_fn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return (tensor_map_encode_fn)p;
+  }();
+  return fn;
+}
+
+// True if TMA can address the tensor: 16-byte aligned base and strides.
+inline bool tma_addressable(const SeqView& s, int elem_bytes) {
+  const int64_t m = 16 / elem_bytes;
+  return s.data && ((uintptr_t)s.data % 16 == 0) && s.st % m == 0 && s.sh % m == 0 && s.sb % m == 0;
+}
+
+// Map over a bf16 (B,T,H,d) tensor as dims (d, T, H, B); box = 64 elements (128 bytes, swizzled) x
+// `box_rows` tokens of one head of one batch row.  Rows past T read as zero and are not written.
+inline int make_seq_map(CUtensorMap* out, const SeqView& s, int B, int T, int H, int d, int box_rows) {
+  tensor_map_encode_fn enc = tensor_map_encoder();
+  if (!enc) return FPB_ERR_TENSOR_MAP;
+  const cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)T, (cuuint64_t)H, (cuuint64_t)B};
+  // a dimension of extent 1 may come with any stride; give the encoder a harmless valid one
+  const int64_t st = T > 1 ? s.st : (int64_t)d;
+  const int64_t sh = H > 1 ? s.sh : (int64_t)d;
+  const int64_t sb = B > 1 ? s.sb : (int64_t)d;
+  const cuuint64_t strides[3] = {(cuuint64_t)st * 2, (cuuint64_t)sh * 2, (cuuint64_t)sb * 2};
+  const cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, s.data, dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FPB_OK : FPB_ERR_TENSOR_MAP;
+}
+
+}  // namespace fpb

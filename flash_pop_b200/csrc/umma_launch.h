@@ -1,0 +1,33 @@
+// Interface between api.cu and the tcgen05 (5th-generation tensor core) kernel files.
+#pragma once
+
+#include "fpb_common.cuh"
+
+namespace fpb {
+
+// Returned by a launcher when the call's shape, dtype or alignment is outside what the tcgen05
+// kernels take; the caller then uses the CUDA-core kernels.
+constexpr int FPB_UMMA_NOT_APPLICABLE = -1;
+
+struct UmmaFwdArgs {
+  SeqView q, k, v, o;
+  StateView s0, s_out;
+  void* block_states;
+  SuffixStates sfx;
+  const float* gamma;   // host, H entries
+  int B, T, H, dk, dv, dtype, block_size, n_blocks;
+};
+
+struct UmmaBwdArgs {
+  SeqView q, k, v, dO, dQ, dK, dV;
+  StateView s0, d_s_out, d_s0;
+  const void* d_block_states;
+  SuffixStates sfx_in, sfx_grad;
+  const float* gamma;
+  int B, T, H, dk, dv, dtype, block_size, n_blocks;
+};
+
+int launch_umma_fwd(const UmmaFwdArgs& a, cudaStream_t stream);
+int launch_umma_bwd(const UmmaBwdArgs& a, cudaStream_t stream, int* n_launched);
+
+}  // namespace fpb

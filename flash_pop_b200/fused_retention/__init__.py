@@ -1,0 +1,93 @@
+"""Fused chunked retention as a ``torch.autograd.Function`` over the C ABI.
+
+Same call as the reference operator (flash_pop/fused_retention/__init__.py:10-67):
+
+    o, s_out = fused_chunk_retention(q, k, v, s, head_decays)
+
+q, k: (B, T, H, dk); v: (B, T, H, dv); s: (B, H, dk, dv) or None; head_decays: H Python floats.
+Returns o (B, T, H, dv) and the state after the last token.  K is scaled by 1/sqrt(dk) inside the
+operator.  Gradients flow to q, k, v and s; ``head_decays`` is not differentiable.
+"""
+from __future__ import annotations
+
+import contextlib
+from typing import Optional, Sequence
+
+import torch
+
+from flash_pop_b200 import _lib
+
+_force_simt = False
+
+
+@contextlib.contextmanager
+def cuda_core_kernels():
+    """Within this context the operators take the fp32-arithmetic CUDA-core kernels even for shapes the
+    tensor-core kernels handle (this is what ``use_fused_version=False`` selects in the layers)."""
+    global _force_simt
+    old, _force_simt = _force_simt, True
+    try:
+        yield
+    finally:
+        _force_simt = old
+
+
+def _flags() -> int:
+    return _lib.FLAG_FORCE_SIMT if _force_simt else 0
+
+
+def _prepare(q, k, v, s, head_decays):
+    _lib.require_cuda(q, k, v, s)
+    if q.dim() != 4 or k.shape != q.shape or v.dim() != 4 or v.shape[:3] != q.shape[:3]:
+        raise ValueError(f"expected q,k (B,T,H,dk) and v (B,T,H,dv); got {tuple(q.shape)}, {tuple(k.shape)}, {tuple(v.shape)}")
+    B, T, H, dk = q.shape
+    dv = v.shape[-1]
+    assert len(head_decays) == H, f"got {len(head_decays)} decays for {H} heads"
+    if not (q.dtype == k.dtype == v.dtype) or (s is not None and s.dtype != q.dtype):
+        raise ValueError("q, k, v and the state must share one dtype")
+    if s is not None and tuple(s.shape) != (B, H, dk, dv):
+        raise ValueError(f"state must be (B,H,dk,dv)={(B, H, dk, dv)}, got {tuple(s.shape)}")
+    return _lib.unit_inner(q), _lib.unit_inner(k), _lib.unit_inner(v), _lib.state_tensor(s)
+
+
+class FusedChunkRetention(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, q, k, v, s, head_decays: Sequence[float]):
+        head_decays = tuple(float(g) for g in head_decays)
+        q, k, v, s = _prepare(q, k, v, s, head_decays)
+        B, T, H, dk = q.shape
+        dv = v.shape[-1]
+        o = torch.empty((B, T, H, dv), device=q.device, dtype=q.dtype)
+        s_out = torch.empty((B, H, dk, dv), device=q.device, dtype=q.dtype)
+        flags = _flags()
+        with torch.cuda.device(q.device):
+            d = _lib.dims(q, dv, head_decays, flags=flags)
+            _lib.check(_lib.lib().fpb_retention_fwd(d, _lib.seq(q), _lib.seq(k), _lib.seq(v), _lib.state(s),
+                                                    _lib.seq(o), _lib.state(s_out), _lib.stream_ptr(q.device)))
+        ctx.save_for_backward(q, k, v, s)
+        ctx.head_decays = head_decays
+        ctx.flags = flags
+        ctx.set_materialize_grads(False)
+        return o, s_out
+
+    @staticmethod
+    def backward(ctx, dO, dS_new):
+        q, k, v, s = ctx.saved_tensors
+        B, T, H, dk = q.shape
+        dv = v.shape[-1]
+        if dO is None:
+            dO = torch.zeros((B, T, H, dv), device=q.device, dtype=q.dtype)
+        dO = _lib.unit_inner(dO.to(q.dtype))
+        dS_new = _lib.state_tensor(None if dS_new is None else dS_new.to(q.dtype))
+        dQ, dK, dV = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        dS = torch.empty((B, H, dk, dv), device=q.device, dtype=q.dtype) if (s is not None and ctx.needs_input_grad[3]) else None
+        with torch.cuda.device(q.device):
+            d = _lib.dims(q, dv, ctx.head_decays, flags=ctx.flags)
+            _lib.check(_lib.lib().fpb_retention_bwd(d, _lib.seq(q), _lib.seq(k), _lib.seq(v), _lib.state(s),
+                                                    _lib.seq(dO), _lib.state(dS_new), _lib.seq(dQ), _lib.seq(dK),
+                                                    _lib.seq(dV), _lib.state(dS), _lib.stream_ptr(q.device)))
+        return dQ, dK, dV, dS, None
+
+
+fused_chunk_retention = FusedChunkRetention.apply

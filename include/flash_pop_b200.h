@@ -1,0 +1,153 @@
+/*
+ * flash_pop_b200 — C ABI of the B200 (sm_100a) retention / POP-retention kernels.
+ *
+ * This is the whole boundary between a host framework and the CUDA code: plain pointers,
+ * sizes and a cudaStream_t.  No entry point allocates, frees or keeps device memory, none
+ * synchronises the host, all are stream-ordered and re-entrant.  Every entry point returns
+ * an fpb_status (0 = ok); nothing aborts or traps.
+ *
+ * Tensor conventions (the reference's own, flash_pop/fused_retention/fused_chunk_fwd.py:96-101):
+ *   q, k          (B, T, H, dk)      element strides (stride_b, stride_t, stride_h), inner stride 1
+ *   v, o, dO      (B, T, H, dv)
+ *   states        (B, H, dk, dv)     inner (dk, dv) block contiguous, strides (stride_b, stride_h)
+ *   block_states  (B, N, H, dk, dv)  contiguous, N = T / block_size
+ * The operator scales k by 1/sqrt(dk) itself (flash_pop/fused_retention/reference.py:57).
+ * head_decays is a HOST array of H doubles, gamma_h in [0, 1]  (the reference passes a Python
+ * tuple of floats: flash_pop/fused_retention/__init__.py:13,20).
+ */
+#ifndef FLASH_POP_B200_H_
+#define FLASH_POP_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* fpb_stream_t; /* == cudaStream_t */
+
+typedef enum fpb_status {
+  FPB_OK = 0,
+  FPB_ERR_NULL_POINTER = 1,
+  FPB_ERR_BAD_SHAPE = 2,       /* negative size, dk/dv not supported by any kernel, H too large */
+  FPB_ERR_BAD_DTYPE = 3,
+  FPB_ERR_BAD_STRIDE = 4,      /* overlapping or negative strides */
+  FPB_ERR_BAD_DECAY = 5,       /* decay outside [0, 1] or not finite */
+  FPB_ERR_BAD_BLOCK_SIZE = 6,
+  FPB_ERR_NO_DEVICE_CODE = 7,  /* current device is not sm_100 */
+  FPB_ERR_LAUNCH = 8,          /* cudaGetLastError() after a launch, see fpb_last_cuda_error */
+  FPB_ERR_DEVICE_TIMEOUT = 9,  /* a bounded in-kernel wait gave up (reported by fpb_device_status) */
+  FPB_ERR_TENSOR_MAP = 10,     /* cuTensorMapEncodeTiled refused the tensor */
+  FPB_ERR_TOO_LARGE = 11       /* size beyond a fixed limit of this entry point */
+} fpb_status;
+
+typedef enum fpb_dtype { FPB_BF16 = 0, FPB_F32 = 1 } fpb_dtype;
+
+/* which implementation a call took (fpb_last_path) */
+typedef enum fpb_path { FPB_PATH_NONE = 0, FPB_PATH_SIMT = 1, FPB_PATH_TCGEN05 = 2 } fpb_path;
+
+enum {
+  FPB_FLAG_FORCE_SIMT = 1   /* take the CUDA-core fp32-math kernels even where the tensor-core ones apply */
+};
+
+/* A (B, T, H, d) activation. */
+typedef struct fpb_seq {
+  void* data;
+  int64_t stride_b, stride_t, stride_h;
+} fpb_seq;
+
+/* A (B, H, dk, dv) state; data == NULL means "all zeros" for inputs, "not wanted" for outputs. */
+typedef struct fpb_state {
+  void* data;
+  int64_t stride_b, stride_h;
+} fpb_state;
+
+typedef struct fpb_dims {
+  int32_t dtype;        /* fpb_dtype of every tensor of the call */
+  int32_t B, T, H, dk, dv;
+  int32_t block_size;   /* POP entry points only: tokens per block (> 0) */
+  int32_t flags;
+  const double* head_decays; /* host, H entries */
+} fpb_dims;
+
+/*
+ * Forward of fused chunked retention.
+ *   o = (Q K^T/sqrt(dk) . D) V + zeta . (Q S_0),   s_out = gamma^T S_0 + sum_j gamma^(T-1-j) k_j^T v_j / sqrt(dk)
+ * Replaces FusedChunkRetention.forward + the fused_chunk_retention_fwd kernel
+ * (flash_pop/fused_retention/__init__.py:12-31, fused_chunk_fwd.py:95-187).
+ */
+int fpb_retention_fwd(const fpb_dims* dims, const fpb_seq* q, const fpb_seq* k, const fpb_seq* v,
+                      const fpb_state* s0, const fpb_seq* o, const fpb_state* s_out, fpb_stream_t stream);
+
+/*
+ * Backward of fused chunked retention: given dO and the gradient d_s_out of the returned state,
+ * writes dQ, dK, dV and (if wanted) dS_0.
+ * Replaces FusedChunkRetention.backward + fused_retention_bwd_dk_dv_ds + fused_retention_bwd_dq
+ * (flash_pop/fused_retention/__init__.py:33-47, fused_chunk_bwd.py:218-346,349-449).
+ */
+int fpb_retention_bwd(const fpb_dims* dims, const fpb_seq* q, const fpb_seq* k, const fpb_seq* v,
+                      const fpb_state* s0, const fpb_seq* d_o, const fpb_state* d_s_out,
+                      const fpb_seq* d_q, const fpb_seq* d_k, const fpb_seq* d_v, const fpb_state* d_s0,
+                      fpb_stream_t stream);
+
+/*
+ * Forward of POP retention: retention outputs plus the state after every full block of
+ * dims->block_size tokens, block_states (B, N, H, dk, dv) contiguous with N = T / block_size.
+ * No final state is produced.
+ * Replaces FlashPOPRetention.forward + fused_pop_retention_fwd
+ * (flash_pop/pop_retention/__init__.py:13-31, pop_fwd.py:7-140).
+ */
+int fpb_pop_retention_fwd(const fpb_dims* dims, const fpb_seq* q, const fpb_seq* k, const fpb_seq* v,
+                          const fpb_state* s0, const fpb_seq* o, void* block_states, fpb_stream_t stream);
+
+/*
+ * Backward of POP retention: d_block_states (B, N, H, dk, dv) is added to the carried state
+ * gradient where each block ends.
+ * Replaces FlashPOPRetention.backward + pop_retention_bwd_dk_dv_ds + fused_retention_bwd_dq
+ * (flash_pop/pop_retention/__init__.py:33-50, pop_bwd.py:9-165).
+ */
+int fpb_pop_retention_bwd(const fpb_dims* dims, const fpb_seq* q, const fpb_seq* k, const fpb_seq* v,
+                          const fpb_state* s0, const fpb_seq* d_o, const void* d_block_states,
+                          const fpb_seq* d_q, const fpb_seq* d_k, const fpb_seq* d_v, const fpb_state* d_s0,
+                          fpb_stream_t stream);
+
+/*
+ * POP prediction-token suffixes, forward and backward.  Tensors are (B*M, P, H, d): M suffixes
+ * of P tokens per batch row, flattened into the batch as the reference does.  Suffix m of row b
+ * starts from the state at the START of block m — s0[b] for m == 0, block_states[b, m-1]
+ * otherwise — read in place; its own end state is dropped, so the stream state is never written.
+ * dims->B is the number of stream rows B, dims->T the suffix length P, dims->block_size is unused.
+ * The backward writes d_s0 (B,H,dk,dv) and d_block_states (B, N, H, dk, dv), N >= M-1 (blocks
+ * with no suffix get zero).
+ * Replaces POPDecoderLayer._suffixes_forward's torch.cat + second operator call
+ * (flash_pop/pop_retnet.py:152-171).
+ */
+int fpb_pop_suffix_fwd(const fpb_dims* dims, int32_t M, int32_t N, const fpb_seq* q, const fpb_seq* k,
+                       const fpb_seq* v, const fpb_state* s0, const void* block_states, const fpb_seq* o,
+                       fpb_stream_t stream);
+int fpb_pop_suffix_bwd(const fpb_dims* dims, int32_t M, int32_t N, const fpb_seq* q, const fpb_seq* k,
+                       const fpb_seq* v, const fpb_state* s0, const void* block_states, const fpb_seq* d_o,
+                       const fpb_seq* d_q, const fpb_seq* d_k, const fpb_seq* d_v, const fpb_state* d_s0,
+                       void* d_block_states, fpb_stream_t stream);
+
+/* Text for a status code. */
+const char* fpb_strerror(int status);
+/* Library version, major*10000 + minor*100 + patch. */
+int fpb_version(void);
+/* Which implementation the last successful call on this host thread launched (fpb_path). */
+int fpb_last_path(void);
+/* The cudaError_t behind the last FPB_ERR_LAUNCH on this host thread. */
+int fpb_last_cuda_error(void);
+/* How many kernels this library has launched so far in this process. */
+int64_t fpb_launch_count(void);
+/*
+ * Synchronises `stream`, then reads and clears the device status word that the kernels set when
+ * one of their bounded waits (mbarrier / tensor-memory allocation) gave up.  Returns FPB_OK or
+ * FPB_ERR_DEVICE_TIMEOUT; *detail (optional) receives the raw word (role and barrier that gave up).
+ */
+int fpb_device_status(fpb_stream_t stream, int32_t* detail);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASH_POP_B200_H_ */
