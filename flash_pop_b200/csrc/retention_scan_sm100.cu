@@ -1,0 +1,584 @@
+// tcgen05 kernel for the two FORWARD walks of chunked retention on sm_100a:
+//   MODE_FWD : outputs O (+ final state, + block states for POP)        replaces fused_chunk_retention_fwd /
+//                                                                        fused_pop_retention_fwd of the reference
+//   MODE_DQ  : query gradients dQ (forward walk that recomputes states)  replaces fused_retention_bwd_dq
+//
+// One CTA walks one (batch, head) sequence chunk by chunk (C = 64 tokens) for one tile of the state:
+// R state rows (of dk) x CC state columns (of dv).  The fp32 state lives in the registers of the
+// "state" warps for the whole sequence; HBM traffic is the activations in and the result out.
+//
+// Per chunk of L <= 64 tokens, gamma = head decay, rs = 1/sqrt(dk), X = Q (FWD) or dO (DQ):
+//   Veta_j = gamma^(L-1-j) v_j                      scaled in place in shared memory (rows >= L zeroed)
+//   Sc     = X K^T            (FWD)   |  X Veta^T   (DQ)             tcgen05, 64x64 fp32 in tensor memory
+//   P'     = tril(Sc) * gamma^-L * rs  -> bf16      registers -> swizzled shared memory
+//   ACC    = X Sb + P' Veta   (FWD)   |  X Sb^T + P' K   (DQ)        Sb = bf16 copy of the chunk-start state
+//   out_i  = gamma^(i+1) * ACC_i                                      epilogue, TMA store
+//   dS     = K^T Veta ;  S <- gamma^L S + rs dS                       state warps, fp32 registers
+// which equals the reference's  O = (QK^T.D)V + zeta.(Q S),  S <- gamma^L S + (K.eta)^T V
+// (flash_pop/fused_retention/fused_chunk_fwd.py:35-52,75-90) because gamma^(i-j) =
+// gamma^(i+1) * gamma^-L * gamma^(L-1-j): the decay mask factors into a row scale, a constant and
+// the column scale already folded into Veta, so no [C,C] mask table is needed.
+//
+// Warp roles (448 threads): warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 "score" warps
+// (V scaling, P', output epilogue), warps 6-13 "state" warps.  All hand-offs are mbarriers; every wait
+// is bounded and reports through the status word instead of hanging.
+#include "fpb_common.cuh"
+#include "ptx_sm100.cuh"
+#include "tensormap.cuh"
+#include "umma_launch.h"
+
+namespace fpb {
+namespace {
+
+using namespace ptx;
+typedef __nv_bfloat16 bf16;
+
+constexpr int MODE_FWD = 0, MODE_DQ = 1;
+constexpr int C = 64;                 // chunk length
+constexpr int NTHREADS = 448;
+constexpr int SCORE_WARP0 = 2, STATE_WARP0 = 6;
+constexpr int N_SCORE = 128, N_STATE = 256;
+
+struct ScanParams {
+  CUtensorMap map_x, map_k, map_v, map_out;
+  bf16* out; int64_t out_sb, out_st, out_sh;
+  const bf16* s0; int64_t s0_sb, s0_sh;
+  bf16* s_out; int64_t so_sb, so_sh;
+  bf16* block_states;
+  const bf16* sfx_blocks; int32_t sfx_M, sfx_N;
+  int32_t T, H, dk, dv, block_size, n_blocks;
+  int32_t* status;
+  float log2g[FPB_MAX_HEADS];
+};
+
+template <int MODE, int R, int CC>
+struct Cfg {
+  static constexpr int W1 = MODE == MODE_FWD ? R : CC;       // width of X (and of the Sc contraction)
+  static constexpr int NOUT = MODE == MODE_FWD ? CC : R;     // width of the output tile
+  static constexpr int X_BYTES = C * W1 * 2, K_BYTES = C * R * 2, V_BYTES = C * CC * 2;
+  static constexpr int STAGE_BYTES = X_BYTES + K_BYTES + V_BYTES;
+  static constexpr int P_BYTES = C * C * 2;
+  static constexpr int SB_BYTES = R * CC * 2;
+  static constexpr int OUT_BYTES = C * NOUT * 2;
+  static constexpr int FIXED = 2 * P_BYTES + SB_BYTES + OUT_BYTES + 1024;
+  static constexpr int STAGES = (FIXED + 3 * STAGE_BYTES <= 225 * 1024) ? 3 : 2;
+  static constexpr int OFF_STAGE = 0;
+  static constexpr int OFF_P = STAGES * STAGE_BYTES;
+  static constexpr int OFF_SB = OFF_P + 2 * P_BYTES;
+  static constexpr int OFF_OUT = OFF_SB + SB_BYTES;
+  static constexpr int OFF_BAR = OFF_OUT + OUT_BYTES;
+  static constexpr int SMEM = OFF_BAR + 1024 + 1024;          // + alignment slack
+  // tensor-memory columns
+  static constexpr int TM_SC = 0, TM_ACC = 128, TM_DS = 128 + 2 * NOUT, TM_COLS = 512;
+  static_assert(TM_DS + CC <= 512, "tensor memory budget");
+  static_assert(FIXED + 2 * STAGE_BYTES <= 226 * 1024, "shared memory budget");
+  // registers of state per state-warp thread
+  static constexpr int NS = R == 128 ? CC / 2 : CC / 4;
+};
+
+// barrier slots (8 bytes each) inside the barrier page
+enum { B_FULL = 0, B_EMPTY = 3, B_VRDY = 6, B_SCFULL = 9, B_PRDY = 11, B_ACCFULL = 13, B_ACCFREE = 15, B_DSFULL = 17, B_SBRDY = 18, B_COUNT = 19 };
+
+struct Chunk { int a, L; };
+__device__ __forceinline__ bool next_chunk(Chunk& ck, int T, int bs) {
+  const int a = ck.a + ck.L;
+  if (a >= T) return false;
+  int b = min(a + C, T);
+  if (bs > 0) b = min(b, (a / bs + 1) * bs);
+  ck.a = a; ck.L = b - a;
+  return true;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+#define FPB_GIVE_UP(code)                                             \
+  do {                                                                \
+    atomicCAS(p.status, 0, (code));                                   \
+    abort_flag = 1;                                                   \
+  } while (0)
+
+template <int MODE, int R, int CC>
+__global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant__ ScanParams p) {
+  using G = Cfg<MODE, R, CC>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* sm = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t sbase = smem_u32(sm);
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int row0 = MODE == MODE_FWD ? 0 : tile * R;     // state rows [row0, row0+R) of dk
+  const int col0 = MODE == MODE_FWD ? tile * CC : 0;    // state cols [col0, col0+CC) of dv
+  const float lg = p.log2g[h];
+  const float rs = rsqrtf((float)p.dk);
+  auto bar = [&](int slot) { return sbase + G::OFF_BAR + slot * 8; };
+
+  if (tid == 0) {
+    for (int s = 0; s < 3; ++s) { mbar_init(bar(B_FULL + s), 1); mbar_init(bar(B_EMPTY + s), 1); mbar_init(bar(B_VRDY + s), N_SCORE); }
+    for (int j = 0; j < 2; ++j) {
+      mbar_init(bar(B_SCFULL + j), 1); mbar_init(bar(B_PRDY + j), N_SCORE);
+      mbar_init(bar(B_ACCFULL + j), 1); mbar_init(bar(B_ACCFREE + j), N_SCORE);
+    }
+    mbar_init(bar(B_DSFULL), 1); mbar_init(bar(B_SBRDY), N_STATE);
+    fence_mbar_init();
+    abort_flag = 0;
+    prefetch_tmap(&p.map_x); prefetch_tmap(&p.map_k); prefetch_tmap(&p.map_v); prefetch_tmap(&p.map_out);
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(&tmem_slot), G::TM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = tmem_slot;
+
+  Chunk first{0, 0};
+  const bool any = next_chunk(first, p.T, p.block_size);
+
+  // =============================================================================================
+  if (warp == 0) {                                   // ---------------- TMA producer
+    if (lane == 0 && any) {
+      Chunk ck = first;
+      int c = 0, issued = 0;
+      do {
+        const int s = c % G::STAGES;
+        if (!mbar_wait(bar(B_EMPTY + s), ((c / G::STAGES) & 1) ^ 1, &abort_flag)) { FPB_GIVE_UP(0x100 | B_EMPTY); break; }
+        const uint32_t st = sbase + G::OFF_STAGE + s * G::STAGE_BYTES;
+        mbar_arrive_expect_tx(bar(B_FULL + s), G::STAGE_BYTES);
+        const int xcol0 = MODE == MODE_FWD ? row0 : col0;
+#pragma unroll
+        for (int cb = 0; cb < G::W1 / 64; ++cb) tma_load_4d(st + cb * 8192, &p.map_x, bar(B_FULL + s), xcol0 + cb * 64, ck.a, h, b);
+#pragma unroll
+        for (int cb = 0; cb < R / 64; ++cb) tma_load_4d(st + G::X_BYTES + cb * 8192, &p.map_k, bar(B_FULL + s), row0 + cb * 64, ck.a, h, b);
+#pragma unroll
+        for (int cb = 0; cb < CC / 64; ++cb) tma_load_4d(st + G::X_BYTES + G::K_BYTES + cb * 8192, &p.map_v, bar(B_FULL + s), col0 + cb * 64, ck.a, h, b);
+        ++issued; ++c;
+      } while (next_chunk(ck, p.T, p.block_size));
+      if (abort_flag) {   // let the copies in flight land before the CTA's shared memory is released
+        for (int i = max(0, issued - G::STAGES); i < issued; ++i) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(bar(B_FULL + i % G::STAGES), (i / G::STAGES) & 1) && clock64() - t0 < kWaitCycles) {}
+        }
+      }
+    }
+  } else if (warp == 1) {                            // ---------------- MMA issuer
+    if (lane == 0 && any) {
+      constexpr uint32_t ID_SC = idesc_bf16(64, 64, 0, 0);
+      constexpr uint32_t ID_STATE = MODE == MODE_FWD ? idesc_bf16(64, CC, 0, 1) : idesc_bf16(64, R, 0, 0);
+      constexpr uint32_t ID_INTRA = idesc_bf16(64, G::NOUT, 0, 1);
+      constexpr uint32_t ID_DS = idesc_bf16(R, CC, 1, 1);
+      auto stage_x = [&](int s) { return sbase + G::OFF_STAGE + s * G::STAGE_BYTES; };
+      auto stage_k = [&](int s) { return stage_x(s) + G::X_BYTES; };
+      auto stage_v = [&](int s) { return stage_k(s) + G::K_BYTES; };
+      auto kmajor = [&](uint32_t base, int ks, uint32_t cb_stride) {   // K-major tile, k-step of 16 elements
+        return smem_desc(base + (ks >> 2) * cb_stride + (ks & 3) * 32, 16, 1024);
+      };
+      auto mnmajor = [&](uint32_t base, int ks, uint32_t cb_stride) {  // MN-major tile, k-step of 16 rows
+        return smem_desc(base + ks * 2048, cb_stride, 1024);
+      };
+      auto issue_sc = [&](int s, int j) {
+        const uint32_t d = tm + G::TM_SC + j * 64;
+#pragma unroll
+        for (int ks = 0; ks < G::W1 / 16; ++ks)
+          umma_bf16(d, kmajor(stage_x(s), ks, 8192), kmajor(MODE == MODE_FWD ? stage_k(s) : stage_v(s), ks, 8192), ID_SC, ks > 0);
+        umma_commit(bar(B_SCFULL + j));
+      };
+      bool ok = true;
+      Chunk ck = first;
+      int c = 0;
+      // first scores
+      ok = mbar_wait(bar(B_FULL + 0), 0, &abort_flag);
+      if (ok && MODE == MODE_DQ) ok = mbar_wait(bar(B_VRDY + 0), 0, &abort_flag);
+      if (!ok) FPB_GIVE_UP(0x200 | B_FULL);
+      if (ok) { tc_fence_after(); issue_sc(0, 0); }
+      while (ok) {
+        const int s = c % G::STAGES, j = c & 1;
+        Chunk nx = ck;
+        const bool has_next = next_chunk(nx, p.T, p.block_size);
+        if (has_next) {
+          const int s1 = (c + 1) % G::STAGES;
+          const uint32_t ph1 = ((c + 1) / G::STAGES) & 1;
+          ok = mbar_wait(bar(B_FULL + s1), ph1, &abort_flag);
+          if (ok && MODE == MODE_DQ) ok = mbar_wait(bar(B_VRDY + s1), ph1, &abort_flag);
+          if (!ok) { FPB_GIVE_UP(0x200 | B_FULL); break; }
+          tc_fence_after();
+          issue_sc(s1, (c + 1) & 1);
+        }
+        // state term: ACC = X Sb (FWD) | X Sb^T (DQ)
+        if (!mbar_wait(bar(B_SBRDY), c & 1, &abort_flag)) { FPB_GIVE_UP(0x200 | B_SBRDY); break; }
+        if (!mbar_wait(bar(B_ACCFREE + j), ((c >> 1) & 1) ^ 1, &abort_flag)) { FPB_GIVE_UP(0x200 | B_ACCFREE); break; }
+        tc_fence_after();
+        const uint32_t acc = tm + G::TM_ACC + j * G::NOUT;
+        if (MODE == MODE_FWD) {
+#pragma unroll
+          for (int ks = 0; ks < R / 16; ++ks)
+            umma_bf16(acc, kmajor(stage_x(s), ks, 8192), mnmajor(sbase + G::OFF_SB, ks, R * 128), ID_STATE, ks > 0);
+        } else {
+#pragma unroll
+          for (int ks = 0; ks < CC / 16; ++ks)
+            umma_bf16(acc, kmajor(stage_x(s), ks, 8192), kmajor(sbase + G::OFF_SB, ks, R * 128), ID_STATE, ks > 0);
+        }
+        // intra-chunk term: ACC += P' Veta (FWD) | P' K (DQ)
+        if (!mbar_wait(bar(B_PRDY + j), (c >> 1) & 1, &abort_flag)) { FPB_GIVE_UP(0x200 | B_PRDY); break; }
+        if (!mbar_wait(bar(B_VRDY + s), (c / G::STAGES) & 1, &abort_flag)) { FPB_GIVE_UP(0x200 | B_VRDY); break; }
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < C / 16; ++ks)
+          umma_bf16(acc, kmajor(sbase + G::OFF_P + j * G::P_BYTES, ks, 0),
+                    mnmajor(MODE == MODE_FWD ? stage_v(s) : stage_k(s), ks, 8192), ID_INTRA, 1);
+        umma_commit(bar(B_ACCFULL + j));
+        // state increment: dS = K^T Veta
+#pragma unroll
+        for (int ks = 0; ks < C / 16; ++ks)
+          umma_bf16(tm + G::TM_DS, mnmajor(stage_k(s), ks, 8192), mnmajor(stage_v(s), ks, 8192), ID_DS, ks > 0);
+        umma_commit(bar(B_DSFULL));
+        umma_commit(bar(B_EMPTY + s));
+        if (!has_next) break;
+        ck = nx; ++c;
+      }
+    }
+  } else if (warp < STATE_WARP0) {                   // ---------------- score warps
+    const int t = tid - SCORE_WARP0 * 32;            // 0..127
+    const int q4 = warp & 3;                         // tensor-memory sub-partition of this warp
+    const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
+    const int r_lo = q4 * 16 + (lane >> 2);          // this thread's two accumulator rows: r_lo, r_lo + 8
+    const int cpair = (lane & 3) * 2;
+
+    auto scale_v = [&](int s, int L) {
+      uint8_t* vt = sm + G::OFF_STAGE + s * G::STAGE_BYTES + G::X_BYTES + G::K_BYTES;
+      for (int idx = t; idx < C * CC / 8; idx += N_SCORE) {
+        const int row = (idx >> 3) & 63;
+        uint4* ptr = reinterpret_cast<uint4*>(vt + idx * 16);
+        uint4 val = make_uint4(0u, 0u, 0u, 0u);
+        if (row < L) {
+          const float e = exp2f((float)(L - 1 - row) * lg);
+          val = *ptr;
+          uint32_t* w = reinterpret_cast<uint32_t*>(&val);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&w[i]));
+            w[i] = pack_bf16(f.x * e, f.y * e);
+          }
+        }
+        *ptr = val;
+      }
+      fence_async_smem();
+      mbar_arrive(bar(B_VRDY + s));
+    };
+
+    auto epilogue = [&](int c, Chunk ck) -> bool {
+      const int j = c & 1;
+      bool fail = !mbar_wait(bar(B_ACCFULL + j), (c >> 1) & 1, &abort_flag);
+      if (fail) FPB_GIVE_UP(0x300 | B_ACCFULL);
+      // the previous TMA store must have finished reading the staging tile
+      if (t == 0) tma_store_wait_read0();
+      if (named_bar_or(1, N_SCORE, fail)) return false;   // all 128 threads leave together
+      tc_fence_after();
+      const float z_lo = exp2f((float)(r_lo + 1) * lg), z_hi = exp2f((float)(r_lo + 9) * lg);
+      uint8_t* stg = sm + G::OFF_OUT;
+#pragma unroll
+      for (int half = 0; half < G::NOUT / 64; ++half) {
+        uint32_t r[32];
+        tmem_ld_16x256b_x8(tm + lane_base + G::TM_ACC + j * G::NOUT + half * 64, r);
+        tmem_wait_ld();
+        if (half == G::NOUT / 64 - 1) { tc_fence_before(); mbar_arrive(bar(B_ACCFREE + j)); }
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const uint32_t lo = pack_bf16(__uint_as_float(r[4 * g]) * z_lo, __uint_as_float(r[4 * g + 1]) * z_lo);
+          const uint32_t hi = pack_bf16(__uint_as_float(r[4 * g + 2]) * z_hi, __uint_as_float(r[4 * g + 3]) * z_hi);
+          *reinterpret_cast<uint32_t*>(stg + half * 8192 + r_lo * 128 + ((g ^ (r_lo & 7)) << 4) + cpair * 2) = lo;
+          *reinterpret_cast<uint32_t*>(stg + half * 8192 + (r_lo + 8) * 128 + ((g ^ ((r_lo + 8) & 7)) << 4) + cpair * 2) = hi;
+        }
+      }
+      const bool whole_box = ck.L == C || ck.a + C >= p.T;   // no live rows beyond L inside the 64-row box
+      if (whole_box) fence_async_smem();
+      named_bar_sync(1, N_SCORE);
+      const int ocol0 = MODE == MODE_FWD ? col0 : row0;
+      if (whole_box) {
+        if (t == 0) {
+#pragma unroll
+          for (int cb = 0; cb < G::NOUT / 64; ++cb) tma_store_4d(&p.map_out, sbase + G::OFF_OUT + cb * 8192, ocol0 + cb * 64, ck.a, h, b);
+          tma_store_commit();
+        }
+      } else {   // chunk cut short by a block end: rows >= L belong to the next chunk, store rows < L only
+        bf16* go = p.out + (int64_t)b * p.out_sb + (int64_t)h * p.out_sh + ocol0;
+        for (int idx = t; idx < ck.L * (G::NOUT / 8); idx += N_SCORE) {
+          const int row = idx / (G::NOUT / 8), ch = idx % (G::NOUT / 8);
+          const uint4 val = *reinterpret_cast<const uint4*>(stg + (ch >> 3) * 8192 + row * 128 + (((ch & 7) ^ (row & 7)) << 4));
+          *reinterpret_cast<uint4*>(go + (int64_t)(ck.a + row) * p.out_st + ch * 8) = val;
+        }
+        named_bar_sync(1, N_SCORE);   // staging is read by generic loads here: finish before it is rewritten
+      }
+      return true;
+    };
+
+    if (any) {
+      Chunk ck = first, prev = first;
+      int c = 0;
+      bool ok = mbar_wait(bar(B_FULL + 0), 0, &abort_flag);
+      if (!ok) FPB_GIVE_UP(0x300 | B_FULL);
+      ok = !named_bar_or(2, N_SCORE, !ok);
+      if (ok) scale_v(0, ck.L);
+      while (ok) {
+        const int j = c & 1;
+        Chunk nx = ck;
+        const bool has_next = next_chunk(nx, p.T, p.block_size);
+        bool fail = false;
+        if (has_next) {
+          const int s1 = (c + 1) % G::STAGES;
+          fail = !mbar_wait(bar(B_FULL + s1), ((c + 1) / G::STAGES) & 1, &abort_flag);
+          if (fail) FPB_GIVE_UP(0x300 | B_FULL);
+          else scale_v(s1, nx.L);
+        }
+        // P' = tril(Sc) * gamma^-L * rs
+        if (!fail) {
+          fail = !mbar_wait(bar(B_SCFULL + j), (c >> 1) & 1, &abort_flag);
+          if (fail) FPB_GIVE_UP(0x300 | B_SCFULL);
+        }
+        if (!fail) {
+          tc_fence_after();
+          uint32_t r[32];
+          tmem_ld_16x256b_x8(tm + lane_base + G::TM_SC + j * 64, r);
+          tmem_wait_ld();
+          tc_fence_before();
+          const float cs = exp2f(-(float)ck.L * lg) * rs;
+          uint8_t* pt = sm + G::OFF_P + j * G::P_BYTES;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const int col = g * 8 + cpair;
+            const float a0 = col <= r_lo ? __uint_as_float(r[4 * g]) * cs : 0.f;
+            const float a1 = col + 1 <= r_lo ? __uint_as_float(r[4 * g + 1]) * cs : 0.f;
+            const float b0 = col <= r_lo + 8 ? __uint_as_float(r[4 * g + 2]) * cs : 0.f;
+            const float b1 = col + 1 <= r_lo + 8 ? __uint_as_float(r[4 * g + 3]) * cs : 0.f;
+            *reinterpret_cast<uint32_t*>(pt + r_lo * 128 + ((g ^ (r_lo & 7)) << 4) + cpair * 2) = pack_bf16(a0, a1);
+            *reinterpret_cast<uint32_t*>(pt + (r_lo + 8) * 128 + ((g ^ ((r_lo + 8) & 7)) << 4) + cpair * 2) = pack_bf16(b0, b1);
+          }
+          fence_async_smem();
+          mbar_arrive(bar(B_PRDY + j));
+        }
+        // a thread that gave up must not leave the others waiting at the epilogue's barriers
+        if (named_bar_or(2, N_SCORE, fail)) { ok = false; break; }
+        if (c > 0 && !epilogue(c - 1, prev)) { ok = false; break; }
+        if (!has_next) break;
+        prev = ck; ck = nx; ++c;
+      }
+      if (ok) epilogue(c, ck);
+      if (t == 0) tma_store_wait_all0();
+    }
+  } else {                                           // ---------------- state warps
+    const int t = tid - STATE_WARP0 * 32;            // 0..255
+    const int q4 = warp & 3;
+    const int half = (warp - STATE_WARP0) >> 2;      // which half of the CC state columns
+    const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
+    float S[G::NS];
+
+    // element enumeration of this thread's registers: i -> (row, col) inside the (R, CC) tile
+    //   R == 128: row = 32*q4 + lane, col = half*CC/2 + i
+    //   R ==  64: row = 16*q4 + lane/4 + 8*((i>>1)&1), col = half*CC/2 + 8*(i>>2) + 2*(lane&3) + (i&1)
+    auto row_of = [&](int i) { return R == 128 ? q4 * 32 + lane : q4 * 16 + (lane >> 2) + 8 * ((i >> 1) & 1); };
+    auto col_of = [&](int i) { return R == 128 ? half * (CC / 2) + i : half * (CC / 2) + 8 * (i >> 2) + 2 * (lane & 3) + (i & 1); };
+
+    const int64_t state_elems = (int64_t)p.dk * p.dv;
+    const bf16* s0 = nullptr;
+    if (p.sfx_M > 0) {
+      const int row = b / p.sfx_M, m = b % p.sfx_M;
+      if (m == 0) { if (p.s0) s0 = p.s0 + row * p.s0_sb + h * p.s0_sh; }
+      else s0 = p.sfx_blocks + (((int64_t)row * p.sfx_N + (m - 1)) * p.H + h) * state_elems;
+    } else if (p.s0) {
+      s0 = p.s0 + b * p.s0_sb + h * p.s0_sh;
+    }
+
+    auto load_global = [&](const bf16* src) {
+      if (R == 128) {
+        const bf16* rowp = src + (int64_t)(row0 + row_of(0)) * p.dv + col0 + half * (CC / 2);
+#pragma unroll
+        for (int i = 0; i < G::NS; i += 8) {
+          const uint4 val = *reinterpret_cast<const uint4*>(rowp + i);
+          const uint32_t* w = reinterpret_cast<const uint32_t*>(&val);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[e]));
+            S[i + 2 * e] = f.x; S[i + 2 * e + 1] = f.y;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < G::NS; i += 2) {
+          const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(src + (int64_t)(row0 + row_of(i)) * p.dv + col0 + col_of(i));
+          const float2 f = __bfloat1622float2(v2);
+          S[i] = f.x; S[i + 1] = f.y;
+        }
+      }
+    };
+    auto store_global = [&](bf16* dst) {
+      if (R == 128) {
+        bf16* rowp = dst + (int64_t)(row0 + row_of(0)) * p.dv + col0 + half * (CC / 2);
+#pragma unroll
+        for (int i = 0; i < G::NS; i += 8) {
+          uint4 val;
+          val.x = pack_bf16(S[i], S[i + 1]); val.y = pack_bf16(S[i + 2], S[i + 3]);
+          val.z = pack_bf16(S[i + 4], S[i + 5]); val.w = pack_bf16(S[i + 6], S[i + 7]);
+          *reinterpret_cast<uint4*>(rowp + i) = val;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < G::NS; i += 2)
+          *reinterpret_cast<uint32_t*>(dst + (int64_t)(row0 + row_of(i)) * p.dv + col0 + col_of(i)) = pack_bf16(S[i], S[i + 1]);
+      }
+    };
+    // bf16 copy of the state in shared memory: [CC/64 column blocks][R rows][128 bytes], 16-byte
+    // pieces XOR-swizzled by (row & 7) — an MN-major B operand (FWD) or a K-major B operand (DQ).
+    auto publish_sb = [&]() {
+      uint8_t* sb = sm + G::OFF_SB;
+      if (R == 128) {
+        const int row = row_of(0);
+#pragma unroll
+        for (int i = 0; i < G::NS; i += 8) {
+          const int col = col_of(i);
+          uint4 val;
+          val.x = pack_bf16(S[i], S[i + 1]); val.y = pack_bf16(S[i + 2], S[i + 3]);
+          val.z = pack_bf16(S[i + 4], S[i + 5]); val.w = pack_bf16(S[i + 6], S[i + 7]);
+          *reinterpret_cast<uint4*>(sb + (col >> 6) * (R * 128) + row * 128 + ((((col & 63) >> 3) ^ (row & 7)) << 4)) = val;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < G::NS; i += 2) {
+          const int row = row_of(i), col = col_of(i);
+          *reinterpret_cast<uint32_t*>(sb + (col >> 6) * (R * 128) + row * 128 + ((((col & 63) >> 3) ^ (row & 7)) << 4) + (col & 7) * 2) =
+              pack_bf16(S[i], S[i + 1]);
+        }
+      }
+      fence_async_smem();
+      mbar_arrive(bar(B_SBRDY));
+    };
+
+    if (s0) load_global(s0);
+    else {
+#pragma unroll
+      for (int i = 0; i < G::NS; ++i) S[i] = 0.f;
+    }
+    if (any) {
+      publish_sb();
+      Chunk ck = first;
+      int c = 0;
+      while (true) {
+        Chunk nx = ck;
+        const bool has_next = next_chunk(nx, p.T, p.block_size);
+        if (!mbar_wait(bar(B_DSFULL), c & 1, &abort_flag)) { FPB_GIVE_UP(0x400 | B_DSFULL); break; }
+        tc_fence_after();
+        const float gl = exp2f((float)ck.L * lg);
+        if (R == 128) {
+#pragma unroll
+          for (int i0 = 0; i0 < G::NS; i0 += 32) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(tm + lane_base + G::TM_DS + half * (CC / 2) + i0, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) S[i0 + i] = fmaf(gl, S[i0 + i], rs * __uint_as_float(r[i]));
+          }
+        } else if (G::NS >= 32) {
+#pragma unroll
+          for (int i0 = 0; i0 < G::NS; i0 += 32) {
+            uint32_t r[32];
+            tmem_ld_16x256b_x8(tm + lane_base + G::TM_DS + half * (CC / 2) + i0 * 2, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) S[i0 + i] = fmaf(gl, S[i0 + i], rs * __uint_as_float(r[i]));
+          }
+        } else {
+          uint32_t r[16];
+          tmem_ld_16x256b_x4(tm + lane_base + G::TM_DS + half * (CC / 2), r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) S[i] = fmaf(gl, S[i], rs * __uint_as_float(r[i]));
+        }
+        tc_fence_before();
+        const int end = ck.a + ck.L;
+        if (p.block_size > 0 && p.block_states && end % p.block_size == 0 && end / p.block_size - 1 < p.n_blocks)
+          store_global(p.block_states + (((int64_t)b * p.n_blocks + (end / p.block_size - 1)) * p.H + h) * state_elems);
+        if (!has_next) break;
+        publish_sb();
+        ck = nx; ++c;
+      }
+    }
+    if (p.s_out && !abort_flag) store_global(p.s_out + b * p.so_sb + h * p.so_sh);
+  }
+
+  // ---------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tm, G::TM_COLS); }
+}
+
+template <int MODE, int R, int CC>
+int launch_scan(const ScanParams& p, dim3 grid, cudaStream_t stream) {
+  using G = Cfg<MODE, R, CC>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    if (cudaFuncSetAttribute(scan_kernel<MODE, R, CC>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM) != cudaSuccess)
+      return FPB_ERR_LAUNCH;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  scan_kernel<MODE, R, CC><<<grid, NTHREADS, G::SMEM, stream>>>(p);
+  return FPB_OK;
+}
+
+bool aligned_state(const StateView& s) { return !s.data || ((uintptr_t)s.data % 16 == 0 && s.sb % 8 == 0 && s.sh % 8 == 0); }
+
+}  // namespace
+
+// Shared by the forward entry (MODE_FWD) and the backward entry's dQ pass (MODE_DQ).
+int launch_scan_pass(int mode, const SeqView& x, const SeqView& k, const SeqView& v, const SeqView& out, const StateView& s0,
+                     const StateView& s_out, void* block_states, const SuffixStates& sfx, const float* gamma, int B, int T,
+                     int H, int dk, int dv, int block_size, int n_blocks, cudaStream_t stream) {
+  const int xw = mode == MODE_FWD ? dk : dv, ow = mode == MODE_FWD ? dv : dk;
+  if (!tma_addressable(x, 2) || !tma_addressable(k, 2) || !tma_addressable(v, 2) || !tma_addressable(out, 2))
+    return FPB_UMMA_NOT_APPLICABLE;
+  if (!aligned_state(s0) || !aligned_state(s_out) || (uintptr_t)block_states % 16 || (uintptr_t)sfx.blocks % 16)
+    return FPB_UMMA_NOT_APPLICABLE;
+  if (B > 65535 || H > 65535) return FPB_UMMA_NOT_APPLICABLE;
+
+  ScanParams p;
+  int r;
+  if ((r = make_seq_map(&p.map_x, x, B, T, H, xw, C)) != FPB_OK) return r;
+  if ((r = make_seq_map(&p.map_k, k, B, T, H, dk, C)) != FPB_OK) return r;
+  if ((r = make_seq_map(&p.map_v, v, B, T, H, dv, C)) != FPB_OK) return r;
+  if ((r = make_seq_map(&p.map_out, out, B, T, H, ow, C)) != FPB_OK) return r;
+  p.out = (bf16*)out.data; p.out_sb = out.sb; p.out_st = out.st; p.out_sh = out.sh;
+  p.s0 = (const bf16*)s0.data; p.s0_sb = s0.sb; p.s0_sh = s0.sh;
+  p.s_out = (bf16*)s_out.data; p.so_sb = s_out.sb; p.so_sh = s_out.sh;
+  p.block_states = (bf16*)block_states;
+  p.sfx_blocks = (const bf16*)sfx.blocks; p.sfx_M = sfx.M; p.sfx_N = sfx.N;
+  p.T = T; p.H = H; p.dk = dk; p.dv = dv; p.block_size = block_size; p.n_blocks = n_blocks;
+  p.status = device_status_ptr();
+  if (!p.status) return FPB_ERR_LAUNCH;
+  for (int h = 0; h < H; ++h) p.log2g[h] = (float)std::log2((double)gamma[h]);
+
+#define FPB_SCAN_CASE(MODE_, R_, CC_, TILES_) return launch_scan<MODE_, R_, CC_>(p, dim3((TILES_), H, B), stream)
+  if (mode == MODE_FWD) {
+    if (dk == 128 && dv % 128 == 0) FPB_SCAN_CASE(MODE_FWD, 128, 128, dv / 128);
+    if (dk == 128 && dv == 64) FPB_SCAN_CASE(MODE_FWD, 128, 64, 1);
+    if (dk == 64 && dv % 128 == 0) FPB_SCAN_CASE(MODE_FWD, 64, 128, dv / 128);
+    if (dk == 64 && dv == 64) FPB_SCAN_CASE(MODE_FWD, 64, 64, 1);
+  } else {
+    if (dv == 128 && dk % 128 == 0) FPB_SCAN_CASE(MODE_DQ, 128, 128, dk / 128);
+    if (dv == 128 && dk == 64) FPB_SCAN_CASE(MODE_DQ, 64, 128, 1);
+    if (dv == 64 && dk % 128 == 0) FPB_SCAN_CASE(MODE_DQ, 128, 64, dk / 128);
+    if (dv == 64 && dk == 64) FPB_SCAN_CASE(MODE_DQ, 64, 64, 1);
+    if (dv == 256 && dk % 64 == 0) FPB_SCAN_CASE(MODE_DQ, 64, 256, dk / 64);
+  }
+#undef FPB_SCAN_CASE
+  return FPB_UMMA_NOT_APPLICABLE;
+}
+
+int launch_umma_fwd(const UmmaFwdArgs& a, cudaStream_t stream) {
+  if (a.dtype != FPB_BF16) return FPB_UMMA_NOT_APPLICABLE;
+  return launch_scan_pass(MODE_FWD, a.q, a.k, a.v, a.o, a.s0, a.s_out, a.block_states, a.sfx, a.gamma, a.B, a.T, a.H, a.dk,
+                          a.dv, a.block_size, a.n_blocks, stream);
+}
+
+}  // namespace fpb

@@ -1,5 +1,4 @@
 #include "umma_launch.h"
 namespace fpb {
-int launch_umma_fwd(const UmmaFwdArgs&, cudaStream_t) { return FPB_UMMA_NOT_APPLICABLE; }
 int launch_umma_bwd(const UmmaBwdArgs&, cudaStream_t, int*) { return FPB_UMMA_NOT_APPLICABLE; }
 }
