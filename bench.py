@@ -35,6 +35,8 @@ WORKLOADS = {
     "ns": dict(B=8, H=16, T=8192, dk=128, dv=128, block=0),
     "c3": dict(B=4, H=32, T=16384, dk=128, dv=256, block=0),
     "c4": dict(B=16, H=8, T=5120, dk=64, dv=64, block=80),
+    # a quarter of "ns" (still 4 x 67 MB of inputs, larger than L2): the case profiler captures run on
+    "small": dict(B=2, H=16, T=8192, dk=128, dv=128, block=0),
 }
 CHUNK = 64
 

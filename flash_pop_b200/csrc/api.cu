@@ -46,6 +46,14 @@ int check_device() {
   static std::atomic<int> ok[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return FPB_ERR_NO_DEVICE_CODE;
+  // Tensor maps are encoded through the driver API, which needs the device's primary context current
+  // on the calling host thread; a thread that has made no runtime call yet (an autograd worker, say)
+  // has none.  cudaSetDevice binds it.
+  thread_local int bound = -1;
+  if (bound != dev) {
+    if (cudaSetDevice(dev) != cudaSuccess) return FPB_ERR_NO_DEVICE_CODE;
+    bound = dev;
+  }
   if (dev >= 0 && dev < 64 && ok[dev].load()) return FPB_OK;
   int major = 0;
   if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess || major != 10)

@@ -1,7 +1,15 @@
-// tcgen05 kernel for the two FORWARD walks of chunked retention on sm_100a:
-//   MODE_FWD : outputs O (+ final state, + block states for POP)        replaces fused_chunk_retention_fwd /
-//                                                                        fused_pop_retention_fwd of the reference
-//   MODE_DQ  : query gradients dQ (forward walk that recomputes states)  replaces fused_retention_bwd_dq
+// tcgen05 kernel for the four walks of chunked retention on sm_100a (one template, four roles):
+//   MODE_FWD, forward walk : outputs O (+ final state, + POP block states)   replaces fused_chunk_retention_fwd /
+//                                                                            fused_pop_retention_fwd of the reference
+//   MODE_DQ,  forward walk : dQ (recomputes the states)                      replaces fused_retention_bwd_dq
+//   MODE_FWD, reverse walk : dV and dS_0, with (X, K, V) := (K, Q, dO)       replace fused_retention_bwd_dk_dv_ds /
+//   MODE_DQ,  reverse walk : dK,          with (X, K, V) := (V, Q, dO)       pop_retention_bwd_dk_dv_ds
+// The reverse walks carry G = d(loss)/d(state after the chunk) instead of the state and add the POP
+// block-state gradients where a block ends (flash_pop/pop_retention/pop_bwd.py:137-159).  In a
+// reverse walk the in-place row scale is zeta_i = gamma^(i+1) on dO, the mask is upper triangular and
+// the output row scale is eta_j * rs:
+//   dV_j = eta_j rs [ K Gb + triu(K Q^T) gamma^-L (zeta.dO) ]_j     dK_j = eta_j rs [ V Gb^T + triu(V (zeta.dO)^T) gamma^-L Q ]_j
+//   G <- gamma^L G + Q^T (zeta.dO)                                  (flash_pop/fused_retention/fused_chunk_bwd.py:180-215)
 //
 // One CTA walks one (batch, head) sequence chunk by chunk (C = 64 tokens) for one tile of the state:
 // R state rows (of dk) x CC state columns (of dv).  The fp32 state lives in the registers of the
@@ -44,8 +52,9 @@ struct ScanParams {
   bf16* out; int64_t out_sb, out_st, out_sh;
   const bf16* s0; int64_t s0_sb, s0_sh;
   bf16* s_out; int64_t so_sb, so_sh;
-  bf16* block_states;
-  const bf16* sfx_blocks; int32_t sfx_M, sfx_N;
+  bf16* block_states;            // forward walk: states after full blocks (written)
+  const bf16* block_grads;       // reverse walk: gradients of those states (read)
+  bf16* sfx_blocks; int32_t sfx_M, sfx_N;   // suffix calls: start states (forward) / their gradients (reverse)
   int32_t T, H, dk, dv, block_size, n_blocks;
   int32_t* status;
   float log2g[FPB_MAX_HEADS];
@@ -89,6 +98,19 @@ __device__ __forceinline__ bool next_chunk(Chunk& ck, int T, int bs) {
   return true;
 }
 
+// the same schedule walked from the end: ck.a is the start of the chunk processed before
+__device__ __forceinline__ bool prev_chunk(Chunk& ck, int bs) {
+  const int end = ck.a;
+  if (end <= 0) return false;
+  const int base = bs > 0 ? ((end - 1) / bs) * bs : 0;
+  const int start = base + ((end - base - 1) / C) * C;
+  ck.a = start; ck.L = end - start;
+  return true;
+}
+template <int REV> __device__ __forceinline__ bool advance(Chunk& ck, int T, int bs) {
+  return REV ? prev_chunk(ck, bs) : next_chunk(ck, T, bs);
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -100,7 +122,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     abort_flag = 1;                                                   \
   } while (0)
 
-template <int MODE, int R, int CC>
+template <int MODE, int REV, int R, int CC>
 __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant__ ScanParams p) {
   using G = Cfg<MODE, R, CC>;
   extern __shared__ uint8_t smem_raw[];
@@ -134,8 +156,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
   tc_fence_after();
   const uint32_t tm = tmem_slot;
 
-  Chunk first{0, 0};
-  const bool any = next_chunk(first, p.T, p.block_size);
+  Chunk first{REV ? p.T : 0, 0};
+  const bool any = advance<REV>(first, p.T, p.block_size);
 
   // =============================================================================================
   if (warp == 0) {                                   // ---------------- TMA producer
@@ -155,7 +177,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
 #pragma unroll
         for (int cb = 0; cb < CC / 64; ++cb) tma_load_4d(st + G::X_BYTES + G::K_BYTES + cb * 8192, &p.map_v, bar(B_FULL + s), col0 + cb * 64, ck.a, h, b);
         ++issued; ++c;
-      } while (next_chunk(ck, p.T, p.block_size));
+      } while (advance<REV>(ck, p.T, p.block_size));
       if (abort_flag) {   // let the copies in flight land before the CTA's shared memory is released
         for (int i = max(0, issued - G::STAGES); i < issued; ++i) {
           const long long t0 = clock64();
@@ -196,7 +218,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
       while (ok) {
         const int s = c % G::STAGES, j = c & 1;
         Chunk nx = ck;
-        const bool has_next = next_chunk(nx, p.T, p.block_size);
+        const bool has_next = advance<REV>(nx, p.T, p.block_size);
         if (has_next) {
           const int s1 = (c + 1) % G::STAGES;
           const uint32_t ph1 = ((c + 1) / G::STAGES) & 1;
@@ -253,7 +275,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
         uint4* ptr = reinterpret_cast<uint4*>(vt + idx * 16);
         uint4 val = make_uint4(0u, 0u, 0u, 0u);
         if (row < L) {
-          const float e = exp2f((float)(L - 1 - row) * lg);
+          const float e = exp2f((float)(REV ? row + 1 : L - 1 - row) * lg);
           val = *ptr;
           uint32_t* w = reinterpret_cast<uint32_t*>(&val);
 #pragma unroll
@@ -276,7 +298,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
       if (t == 0) tma_store_wait_read0();
       if (named_bar_or(1, N_SCORE, fail)) return false;   // all 128 threads leave together
       tc_fence_after();
-      const float z_lo = exp2f((float)(r_lo + 1) * lg), z_hi = exp2f((float)(r_lo + 9) * lg);
+      // row scale: zeta_i (forward walks) or eta_j * rs (reverse walks)
+      const float z_lo = REV ? exp2f((float)(ck.L - 1 - r_lo) * lg) * rs : exp2f((float)(r_lo + 1) * lg);
+      const float z_hi = REV ? exp2f((float)(ck.L - 9 - r_lo) * lg) * rs : exp2f((float)(r_lo + 9) * lg);
       uint8_t* stg = sm + G::OFF_OUT;
 #pragma unroll
       for (int half = 0; half < G::NOUT / 64; ++half) {
@@ -292,7 +316,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
           *reinterpret_cast<uint32_t*>(stg + half * 8192 + (r_lo + 8) * 128 + ((g ^ ((r_lo + 8) & 7)) << 4) + cpair * 2) = hi;
         }
       }
-      const bool whole_box = ck.L == C || ck.a + C >= p.T;   // no live rows beyond L inside the 64-row box
+      const bool whole_box = ck.L == C || ck.a + ck.L >= p.T;   // rows beyond L are past the sequence end: TMA clips them
       if (whole_box) fence_async_smem();
       named_bar_sync(1, N_SCORE);
       const int ocol0 = MODE == MODE_FWD ? col0 : row0;
@@ -324,7 +348,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
       while (ok) {
         const int j = c & 1;
         Chunk nx = ck;
-        const bool has_next = next_chunk(nx, p.T, p.block_size);
+        const bool has_next = advance<REV>(nx, p.T, p.block_size);
         bool fail = false;
         if (has_next) {
           const int s1 = (c + 1) % G::STAGES;
@@ -343,15 +367,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
           tmem_ld_16x256b_x8(tm + lane_base + G::TM_SC + j * 64, r);
           tmem_wait_ld();
           tc_fence_before();
-          const float cs = exp2f(-(float)ck.L * lg) * rs;
+          const float cs = REV ? exp2f(-(float)ck.L * lg) : exp2f(-(float)ck.L * lg) * rs;
           uint8_t* pt = sm + G::OFF_P + j * G::P_BYTES;
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             const int col = g * 8 + cpair;
-            const float a0 = col <= r_lo ? __uint_as_float(r[4 * g]) * cs : 0.f;
-            const float a1 = col + 1 <= r_lo ? __uint_as_float(r[4 * g + 1]) * cs : 0.f;
-            const float b0 = col <= r_lo + 8 ? __uint_as_float(r[4 * g + 2]) * cs : 0.f;
-            const float b1 = col + 1 <= r_lo + 8 ? __uint_as_float(r[4 * g + 3]) * cs : 0.f;
+            auto keep = [&](int cc, int rr) { return REV ? cc >= rr : cc <= rr; };   // causal side of the tile
+            const float a0 = keep(col, r_lo) ? __uint_as_float(r[4 * g]) * cs : 0.f;
+            const float a1 = keep(col + 1, r_lo) ? __uint_as_float(r[4 * g + 1]) * cs : 0.f;
+            const float b0 = keep(col, r_lo + 8) ? __uint_as_float(r[4 * g + 2]) * cs : 0.f;
+            const float b1 = keep(col + 1, r_lo + 8) ? __uint_as_float(r[4 * g + 3]) * cs : 0.f;
             *reinterpret_cast<uint32_t*>(pt + r_lo * 128 + ((g ^ (r_lo & 7)) << 4) + cpair * 2) = pack_bf16(a0, a1);
             *reinterpret_cast<uint32_t*>(pt + (r_lo + 8) * 128 + ((g ^ ((r_lo + 8) & 7)) << 4) + cpair * 2) = pack_bf16(b0, b1);
           }
@@ -368,7 +393,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
       if (t == 0) tma_store_wait_all0();
     }
   } else {                                           // ---------------- state warps
-    const int t = tid - STATE_WARP0 * 32;            // 0..255
     const int q4 = warp & 3;
     const int half = (warp - STATE_WARP0) >> 2;      // which half of the CC state columns
     const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
@@ -381,16 +405,24 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
     auto col_of = [&](int i) { return R == 128 ? half * (CC / 2) + i : half * (CC / 2) + 8 * (i >> 2) + 2 * (lane & 3) + (i & 1); };
 
     const int64_t state_elems = (int64_t)p.dk * p.dv;
-    const bf16* s0 = nullptr;
+    // where the walk's start value comes from and where its end value goes.  Forward walks start from the
+    // given state; reverse walks start from the gradient of the returned state and end in dS_0.  For a
+    // suffix call, batch index = (row, m): suffix m of a row starts from s0[row] (m == 0) or from block
+    // state m-1, its end state is dropped (zero gradient), and the reverse walk's end goes to the
+    // gradient of that start state.
+    const bf16* x_start = nullptr;
+    bf16* x_end = nullptr;
     if (p.sfx_M > 0) {
       const int row = b / p.sfx_M, m = b % p.sfx_M;
-      if (m == 0) { if (p.s0) s0 = p.s0 + row * p.s0_sb + h * p.s0_sh; }
-      else s0 = p.sfx_blocks + (((int64_t)row * p.sfx_N + (m - 1)) * p.H + h) * state_elems;
-    } else if (p.s0) {
-      s0 = p.s0 + b * p.s0_sb + h * p.s0_sh;
+      bf16* blk = (m > 0 && p.sfx_blocks) ? p.sfx_blocks + (((int64_t)row * p.sfx_N + (m - 1)) * p.H + h) * state_elems : nullptr;
+      if (!REV) x_start = m == 0 ? (p.s0 ? p.s0 + row * p.s0_sb + h * p.s0_sh : nullptr) : blk;
+      else x_end = m == 0 ? (p.s_out ? p.s_out + row * p.so_sb + h * p.so_sh : nullptr) : blk;
+    } else {
+      if (p.s0) x_start = p.s0 + b * p.s0_sb + h * p.s0_sh;
+      if (p.s_out) x_end = p.s_out + b * p.so_sb + h * p.so_sh;
     }
 
-    auto load_global = [&](const bf16* src) {
+    auto load_global = [&](const bf16* src, bool accumulate) {
       if (R == 128) {
         const bf16* rowp = src + (int64_t)(row0 + row_of(0)) * p.dv + col0 + half * (CC / 2);
 #pragma unroll
@@ -400,7 +432,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[e]));
-            S[i + 2 * e] = f.x; S[i + 2 * e + 1] = f.y;
+            S[i + 2 * e] = (accumulate ? S[i + 2 * e] : 0.f) + f.x;
+            S[i + 2 * e + 1] = (accumulate ? S[i + 2 * e + 1] : 0.f) + f.y;
           }
         }
       } else {
@@ -408,9 +441,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
         for (int i = 0; i < G::NS; i += 2) {
           const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(src + (int64_t)(row0 + row_of(i)) * p.dv + col0 + col_of(i));
           const float2 f = __bfloat1622float2(v2);
-          S[i] = f.x; S[i + 1] = f.y;
+          S[i] = (accumulate ? S[i] : 0.f) + f.x;
+          S[i + 1] = (accumulate ? S[i + 1] : 0.f) + f.y;
         }
       }
+    };
+    // reverse walks: add the gradient of block state n where block n ends (chunk end == (n+1) * block_size)
+    auto inject = [&](int end) {
+      if (REV && p.block_size > 0 && p.block_grads && end % p.block_size == 0 && end / p.block_size - 1 < p.n_blocks)
+        load_global(p.block_grads + (((int64_t)b * p.n_blocks + (end / p.block_size - 1)) * p.H + h) * state_elems, true);
     };
     auto store_global = [&](bf16* dst) {
       if (R == 128) {
@@ -454,18 +493,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
       mbar_arrive(bar(B_SBRDY));
     };
 
-    if (s0) load_global(s0);
+    if (x_start) load_global(x_start, false);
     else {
 #pragma unroll
       for (int i = 0; i < G::NS; ++i) S[i] = 0.f;
     }
+    const float ds_scale = REV ? 1.0f : rs;   // forward: S += rs K^T Veta;  reverse: G += Q^T (zeta.dO)
     if (any) {
+      inject(first.a + first.L);
       publish_sb();
       Chunk ck = first;
       int c = 0;
       while (true) {
         Chunk nx = ck;
-        const bool has_next = next_chunk(nx, p.T, p.block_size);
+        const bool has_next = advance<REV>(nx, p.T, p.block_size);
         if (!mbar_wait(bar(B_DSFULL), c & 1, &abort_flag)) { FPB_GIVE_UP(0x400 | B_DSFULL); break; }
         tc_fence_after();
         const float gl = exp2f((float)ck.L * lg);
@@ -476,7 +517,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
             tmem_ld_32x32b_x32(tm + lane_base + G::TM_DS + half * (CC / 2) + i0, r);
             tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) S[i0 + i] = fmaf(gl, S[i0 + i], rs * __uint_as_float(r[i]));
+            for (int i = 0; i < 32; ++i) S[i0 + i] = fmaf(gl, S[i0 + i], ds_scale * __uint_as_float(r[i]));
           }
         } else if (G::NS >= 32) {
 #pragma unroll
@@ -485,25 +526,26 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
             tmem_ld_16x256b_x8(tm + lane_base + G::TM_DS + half * (CC / 2) + i0 * 2, r);
             tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) S[i0 + i] = fmaf(gl, S[i0 + i], rs * __uint_as_float(r[i]));
+            for (int i = 0; i < 32; ++i) S[i0 + i] = fmaf(gl, S[i0 + i], ds_scale * __uint_as_float(r[i]));
           }
         } else {
           uint32_t r[16];
           tmem_ld_16x256b_x4(tm + lane_base + G::TM_DS + half * (CC / 2), r);
           tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) S[i] = fmaf(gl, S[i], rs * __uint_as_float(r[i]));
+          for (int i = 0; i < 16; ++i) S[i] = fmaf(gl, S[i], ds_scale * __uint_as_float(r[i]));
         }
         tc_fence_before();
         const int end = ck.a + ck.L;
-        if (p.block_size > 0 && p.block_states && end % p.block_size == 0 && end / p.block_size - 1 < p.n_blocks)
+        if (!REV && p.block_size > 0 && p.block_states && end % p.block_size == 0 && end / p.block_size - 1 < p.n_blocks)
           store_global(p.block_states + (((int64_t)b * p.n_blocks + (end / p.block_size - 1)) * p.H + h) * state_elems);
         if (!has_next) break;
+        inject(nx.a + nx.L);
         publish_sb();
         ck = nx; ++c;
       }
     }
-    if (p.s_out && !abort_flag) store_global(p.s_out + b * p.so_sb + h * p.so_sh);
+    if (x_end && !abort_flag) store_global(x_end);
   }
 
   // ---------------- teardown
@@ -512,73 +554,121 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tm, G::TM_COLS); }
 }
 
-template <int MODE, int R, int CC>
-int launch_scan(const ScanParams& p, dim3 grid, cudaStream_t stream) {
+template <int MODE, int REV, int R, int CC>
+int launch_scan_t(const ScanParams& p, dim3 grid, cudaStream_t stream) {
   using G = Cfg<MODE, R, CC>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    if (cudaFuncSetAttribute(scan_kernel<MODE, R, CC>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM) != cudaSuccess)
+    if (cudaFuncSetAttribute(scan_kernel<MODE, REV, R, CC>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM) != cudaSuccess)
       return FPB_ERR_LAUNCH;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  scan_kernel<MODE, R, CC><<<grid, NTHREADS, G::SMEM, stream>>>(p);
+  scan_kernel<MODE, REV, R, CC><<<grid, NTHREADS, G::SMEM, stream>>>(p);
   return FPB_OK;
+}
+template <int MODE, int R, int CC>
+int launch_scan(const ScanParams& p, bool rev, dim3 grid, cudaStream_t stream) {
+  return rev ? launch_scan_t<MODE, 1, R, CC>(p, grid, stream) : launch_scan_t<MODE, 0, R, CC>(p, grid, stream);
 }
 
 bool aligned_state(const StateView& s) { return !s.data || ((uintptr_t)s.data % 16 == 0 && s.sb % 8 == 0 && s.sh % 8 == 0); }
 
-}  // namespace
+// Which (mode, dk, dv) combinations the kernel is instantiated for.
+bool scan_supported(int mode, int dk, int dv) {
+  if (mode == MODE_FWD) return (dk == 64 || dk == 128) && (dv == 64 || dv == 128 || dv == 256);
+  return (dk == 64 || dk == 128) && (dv == 64 || dv == 128 || dv == 256);
+}
 
-// Shared by the forward entry (MODE_FWD) and the backward entry's dQ pass (MODE_DQ).
-int launch_scan_pass(int mode, const SeqView& x, const SeqView& k, const SeqView& v, const SeqView& out, const StateView& s0,
-                     const StateView& s_out, void* block_states, const SuffixStates& sfx, const float* gamma, int B, int T,
-                     int H, int dk, int dv, int block_size, int n_blocks, cudaStream_t stream) {
-  const int xw = mode == MODE_FWD ? dk : dv, ow = mode == MODE_FWD ? dv : dk;
-  if (!tma_addressable(x, 2) || !tma_addressable(k, 2) || !tma_addressable(v, 2) || !tma_addressable(out, 2))
-    return FPB_UMMA_NOT_APPLICABLE;
-  if (!aligned_state(s0) || !aligned_state(s_out) || (uintptr_t)block_states % 16 || (uintptr_t)sfx.blocks % 16)
-    return FPB_UMMA_NOT_APPLICABLE;
-  if (B > 65535 || H > 65535) return FPB_UMMA_NOT_APPLICABLE;
+struct PassArgs {
+  int mode; bool rev;
+  SeqView x, k, v, out;
+  StateView start, end;          // start value of the walk (read) and where its end value goes (written)
+  void* block_states; const void* block_grads;
+  SuffixStates sfx;
+  const float* gamma;
+  int B, T, H, dk, dv, block_size, n_blocks;
+};
 
+bool pass_applicable(const PassArgs& a) {
+  if (!scan_supported(a.mode, a.dk, a.dv)) return false;
+  if (!tma_addressable(a.x, 2) || !tma_addressable(a.k, 2) || !tma_addressable(a.v, 2) || !tma_addressable(a.out, 2)) return false;
+  if (!aligned_state(a.start) || !aligned_state(a.end)) return false;
+  if ((uintptr_t)a.block_states % 16 || (uintptr_t)a.block_grads % 16 || (uintptr_t)a.sfx.blocks % 16) return false;
+  return a.B <= 65535 && a.H <= 65535 && a.T > 0;
+}
+
+int launch_pass(const PassArgs& a, cudaStream_t stream) {
+  const int xw = a.mode == MODE_FWD ? a.dk : a.dv, ow = a.mode == MODE_FWD ? a.dv : a.dk;
+  const int B = a.B, T = a.T, H = a.H, dk = a.dk, dv = a.dv;
   ScanParams p;
   int r;
-  if ((r = make_seq_map(&p.map_x, x, B, T, H, xw, C)) != FPB_OK) return r;
-  if ((r = make_seq_map(&p.map_k, k, B, T, H, dk, C)) != FPB_OK) return r;
-  if ((r = make_seq_map(&p.map_v, v, B, T, H, dv, C)) != FPB_OK) return r;
-  if ((r = make_seq_map(&p.map_out, out, B, T, H, ow, C)) != FPB_OK) return r;
-  p.out = (bf16*)out.data; p.out_sb = out.sb; p.out_st = out.st; p.out_sh = out.sh;
-  p.s0 = (const bf16*)s0.data; p.s0_sb = s0.sb; p.s0_sh = s0.sh;
-  p.s_out = (bf16*)s_out.data; p.so_sb = s_out.sb; p.so_sh = s_out.sh;
-  p.block_states = (bf16*)block_states;
-  p.sfx_blocks = (const bf16*)sfx.blocks; p.sfx_M = sfx.M; p.sfx_N = sfx.N;
-  p.T = T; p.H = H; p.dk = dk; p.dv = dv; p.block_size = block_size; p.n_blocks = n_blocks;
+  if ((r = make_seq_map(&p.map_x, a.x, B, T, H, xw, C)) != FPB_OK) return r;
+  if ((r = make_seq_map(&p.map_k, a.k, B, T, H, dk, C)) != FPB_OK) return r;
+  if ((r = make_seq_map(&p.map_v, a.v, B, T, H, dv, C)) != FPB_OK) return r;
+  if ((r = make_seq_map(&p.map_out, a.out, B, T, H, ow, C)) != FPB_OK) return r;
+  p.out = (bf16*)a.out.data; p.out_sb = a.out.sb; p.out_st = a.out.st; p.out_sh = a.out.sh;
+  p.s0 = (const bf16*)a.start.data; p.s0_sb = a.start.sb; p.s0_sh = a.start.sh;
+  p.s_out = (bf16*)a.end.data; p.so_sb = a.end.sb; p.so_sh = a.end.sh;
+  p.block_states = (bf16*)a.block_states;
+  p.block_grads = (const bf16*)a.block_grads;
+  p.sfx_blocks = (bf16*)a.sfx.blocks; p.sfx_M = a.sfx.M; p.sfx_N = a.sfx.N;
+  p.T = T; p.H = H; p.dk = dk; p.dv = dv; p.block_size = a.block_size; p.n_blocks = a.n_blocks;
   p.status = device_status_ptr();
   if (!p.status) return FPB_ERR_LAUNCH;
-  for (int h = 0; h < H; ++h) p.log2g[h] = (float)std::log2((double)gamma[h]);
+  for (int h = 0; h < H; ++h) p.log2g[h] = (float)std::log2((double)a.gamma[h]);
 
-#define FPB_SCAN_CASE(MODE_, R_, CC_, TILES_) return launch_scan<MODE_, R_, CC_>(p, dim3((TILES_), H, B), stream)
-  if (mode == MODE_FWD) {
+#define FPB_SCAN_CASE(MODE_, R_, CC_, TILES_) return launch_scan<MODE_, R_, CC_>(p, a.rev, dim3((TILES_), H, B), stream)
+  if (a.mode == MODE_FWD) {       // state tile: all dk rows x CC columns of dv
     if (dk == 128 && dv % 128 == 0) FPB_SCAN_CASE(MODE_FWD, 128, 128, dv / 128);
     if (dk == 128 && dv == 64) FPB_SCAN_CASE(MODE_FWD, 128, 64, 1);
     if (dk == 64 && dv % 128 == 0) FPB_SCAN_CASE(MODE_FWD, 64, 128, dv / 128);
     if (dk == 64 && dv == 64) FPB_SCAN_CASE(MODE_FWD, 64, 64, 1);
-  } else {
-    if (dv == 128 && dk % 128 == 0) FPB_SCAN_CASE(MODE_DQ, 128, 128, dk / 128);
+  } else {                        // state tile: R rows of dk x all dv columns
+    if (dv == 128 && dk == 128) FPB_SCAN_CASE(MODE_DQ, 128, 128, 1);
     if (dv == 128 && dk == 64) FPB_SCAN_CASE(MODE_DQ, 64, 128, 1);
-    if (dv == 64 && dk % 128 == 0) FPB_SCAN_CASE(MODE_DQ, 128, 64, dk / 128);
+    if (dv == 64 && dk == 128) FPB_SCAN_CASE(MODE_DQ, 128, 64, 1);
     if (dv == 64 && dk == 64) FPB_SCAN_CASE(MODE_DQ, 64, 64, 1);
-    if (dv == 256 && dk % 64 == 0) FPB_SCAN_CASE(MODE_DQ, 64, 256, dk / 64);
+    if (dv == 256) FPB_SCAN_CASE(MODE_DQ, 64, 256, dk / 64);
   }
 #undef FPB_SCAN_CASE
-  return FPB_UMMA_NOT_APPLICABLE;
+  return FPB_ERR_BAD_SHAPE;
 }
+
+}  // namespace
 
 int launch_umma_fwd(const UmmaFwdArgs& a, cudaStream_t stream) {
   if (a.dtype != FPB_BF16) return FPB_UMMA_NOT_APPLICABLE;
-  return launch_scan_pass(MODE_FWD, a.q, a.k, a.v, a.o, a.s0, a.s_out, a.block_states, a.sfx, a.gamma, a.B, a.T, a.H, a.dk,
-                          a.dv, a.block_size, a.n_blocks, stream);
+  PassArgs f{MODE_FWD, false, a.q, a.k, a.v, a.o, a.s0, a.s_out, a.block_states, nullptr, a.sfx, a.gamma,
+             a.B, a.T, a.H, a.dk, a.dv, a.block_size, a.n_blocks};
+  if (!pass_applicable(f)) return FPB_UMMA_NOT_APPLICABLE;
+  return launch_pass(f, stream);
+}
+
+// Backward = three independent walks: dQ (forward walk over the states), dV + dS_0 and dK (reverse
+// walks over the state gradient).
+int launch_umma_bwd(const UmmaBwdArgs& a, cudaStream_t stream, int* n_launched) {
+  *n_launched = 0;
+  if (a.dtype != FPB_BF16) return FPB_UMMA_NOT_APPLICABLE;
+  const StateView none{nullptr, 0, 0};
+  PassArgs dq{MODE_DQ, false, a.dO, a.k, a.v, a.dQ, a.s0, none, nullptr, nullptr, a.sfx_in, a.gamma,
+              a.B, a.T, a.H, a.dk, a.dv, a.block_size, a.n_blocks};
+  PassArgs dv{MODE_FWD, true, a.k, a.q, a.dO, a.dV, a.d_s_out, a.d_s0, nullptr, a.d_block_states, a.sfx_grad, a.gamma,
+              a.B, a.T, a.H, a.dk, a.dv, a.block_size, a.n_blocks};
+  SuffixStates no_write = a.sfx_grad;
+  no_write.blocks = nullptr;
+  PassArgs dk{MODE_DQ, true, a.v, a.q, a.dO, a.dK, a.d_s_out, none, nullptr, a.d_block_states, no_write, a.gamma,
+              a.B, a.T, a.H, a.dk, a.dv, a.block_size, a.n_blocks};
+  if (!pass_applicable(dq) || !pass_applicable(dv) || !pass_applicable(dk)) return FPB_UMMA_NOT_APPLICABLE;
+  int r;
+  if ((r = launch_pass(dq, stream)) != FPB_OK) return r;
+  *n_launched = 1;
+  if ((r = launch_pass(dv, stream)) != FPB_OK) return r;
+  *n_launched = 2;
+  if ((r = launch_pass(dk, stream)) != FPB_OK) return r;
+  *n_launched = 3;
+  return FPB_OK;
 }
 
 }  // namespace fpb

@@ -5,6 +5,8 @@
 
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <cstdio>
+#include <cstdlib>
 
 #include "fpb_common.cuh"
 
@@ -48,6 +50,9 @@ inline int make_seq_map(CUtensorMap* out, const SeqView& s, int B, int T, int H,
   const CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, s.data, dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS && getenv("FPB_DEBUG"))
+    fprintf(stderr, "flash_pop_b200: cuTensorMapEncodeTiled -> %d for ptr %p dims (%d,%d,%d,%d) strides (t %lld, h %lld, b %lld) box rows %d\n",
+            (int)r, s.data, d, T, H, B, (long long)st, (long long)sh, (long long)sb, box_rows);
   return r == CUDA_SUCCESS ? FPB_OK : FPB_ERR_TENSOR_MAP;
 }
 
