@@ -27,9 +27,14 @@
 // gamma^(i+1) * gamma^-L * gamma^(L-1-j): the decay mask factors into a row scale, a constant and
 // the column scale already folded into Veta, so no [C,C] mask table is needed.
 //
-// Warp roles (448 threads): warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 "score" warps
-// (V scaling, P', output epilogue), warps 6-13 "state" warps.  All hand-offs are mbarriers; every wait
-// is bounded and reports through the status word instead of hanging.
+// Warp roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 "score" warps (P', output epilogue),
+// warps 6.. "state" warps (in-place row scaling of V, state update, bf16 state copy).  All hand-offs
+// are mbarriers; every wait is bounded and reports through the status word instead of hanging.
+//
+// A sequence is strictly serial chunk to chunk (dS_c -> state -> X Sb of chunk c+1 -> ...), so one CTA
+// cannot keep the tensor pipe busy by itself.  State tiles are therefore kept narrow (64 state columns
+// for the output walks, 64 state rows for the dQ/dK walks): 256 tensor-memory columns, ~112 KB of
+// shared memory and 320 threads per CTA, so that two CTAs share an SM and fill each other's bubbles.
 #include "fpb_common.cuh"
 #include "ptx_sm100.cuh"
 #include "tensormap.cuh"
@@ -43,9 +48,8 @@ typedef __nv_bfloat16 bf16;
 
 constexpr int MODE_FWD = 0, MODE_DQ = 1;
 constexpr int C = 64;                 // chunk length
-constexpr int NTHREADS = 448;
 constexpr int SCORE_WARP0 = 2, STATE_WARP0 = 6;
-constexpr int N_SCORE = 128, N_STATE = 256;
+constexpr int N_SCORE = 128;
 
 struct ScanParams {
   CUtensorMap map_x, map_k, map_v, map_out;
@@ -57,36 +61,48 @@ struct ScanParams {
   bf16* sfx_blocks; int32_t sfx_M, sfx_N;   // suffix calls: start states (forward) / their gradients (reverse)
   int32_t T, H, dk, dv, block_size, n_blocks;
   int32_t* status;
+  long long* trace;              // diagnostics: per-chunk clock64() stamps of CTA (0,0,0), or null
   float log2g[FPB_MAX_HEADS];
 };
 
+// barrier slots (8 bytes each) at the start of the barrier page, then two 4-byte words
+enum { B_FULL = 0, B_EMPTY = 3, B_VRDY = 6, B_SCFULL = 9, B_PRDY = 11, B_ACCFULL = 12, B_ACCFREE = 13, B_DSFULL = 14, B_DSFREE = 15, B_SBRDY = 16, B_SBFREE = 17, B_COUNT = 18 };
+constexpr int OFF_TMEM_SLOT = B_COUNT * 8, OFF_ABORT = OFF_TMEM_SLOT + 4, BAR_PAGE = 256;
+
 template <int MODE, int R, int CC>
 struct Cfg {
+  static constexpr bool BIG = CC == 256;                     // one CTA per SM; otherwise two
   static constexpr int W1 = MODE == MODE_FWD ? R : CC;       // width of X (and of the Sc contraction)
   static constexpr int NOUT = MODE == MODE_FWD ? CC : R;     // width of the output tile
+  static constexpr int STATE_WARPS = BIG ? 8 : 4;
+  static constexpr int N_STATE = 32 * STATE_WARPS;
+  static constexpr int NTHREADS = STATE_WARP0 * 32 + N_STATE;
+  static constexpr int MIN_CTAS = BIG ? 1 : 2;
   static constexpr int X_BYTES = C * W1 * 2, K_BYTES = C * R * 2, V_BYTES = C * CC * 2;
   static constexpr int STAGE_BYTES = X_BYTES + K_BYTES + V_BYTES;
   static constexpr int P_BYTES = C * C * 2;
   static constexpr int SB_BYTES = R * CC * 2;
   static constexpr int OUT_BYTES = C * NOUT * 2;
-  static constexpr int FIXED = 2 * P_BYTES + SB_BYTES + OUT_BYTES + 1024;
-  static constexpr int STAGES = (FIXED + 3 * STAGE_BYTES <= 225 * 1024) ? 3 : 2;
+  static constexpr int FIXED = P_BYTES + SB_BYTES + OUT_BYTES + BAR_PAGE;
+  static constexpr int SMEM_LIMIT = BIG ? 226 * 1024 : 115712;   // (233472 B per SM) / 2 - 1 KB system reserve
+  static constexpr int STAGES = (FIXED + 3 * STAGE_BYTES <= SMEM_LIMIT) ? 3 : 2;
   static constexpr int OFF_STAGE = 0;
   static constexpr int OFF_P = STAGES * STAGE_BYTES;
-  static constexpr int OFF_SB = OFF_P + 2 * P_BYTES;
+  static constexpr int OFF_SB = OFF_P + P_BYTES;
   static constexpr int OFF_OUT = OFF_SB + SB_BYTES;
   static constexpr int OFF_BAR = OFF_OUT + OUT_BYTES;
-  static constexpr int SMEM = OFF_BAR + 1024 + 1024;          // + alignment slack
-  // tensor-memory columns
-  static constexpr int TM_SC = 0, TM_ACC = 128, TM_DS = 128 + 2 * NOUT, TM_COLS = 512;
-  static_assert(TM_DS + CC <= 512, "tensor memory budget");
-  static_assert(FIXED + 2 * STAGE_BYTES <= 226 * 1024, "shared memory budget");
-  // registers of state per state-warp thread
-  static constexpr int NS = R == 128 ? CC / 2 : CC / 4;
+  static constexpr int SMEM = OFF_BAR + BAR_PAGE;
+  static_assert(SMEM <= SMEM_LIMIT, "shared memory budget");
+  // tensor-memory columns: score tile(s), one accumulator, the state increment
+  static constexpr int TM_COLS = BIG ? 512 : 256;
+  static constexpr int NSC = (2 * 64 + NOUT + CC <= TM_COLS) ? 2 : 1;
+  static constexpr int TM_SC = 0, TM_ACC = 64 * NSC, TM_DS = TM_ACC + NOUT;
+  static_assert(TM_DS + CC <= TM_COLS, "tensor memory budget");
+  // state registers per state-warp thread; NHALF warps share one tensor-memory sub-partition
+  static constexpr int NHALF = STATE_WARPS / 4;
+  static constexpr int WCOLS = CC / NHALF;                   // state columns handled by one warp
+  static constexpr int NS = R == 128 ? WCOLS : WCOLS / 2;
 };
-
-// barrier slots (8 bytes each) inside the barrier page
-enum { B_FULL = 0, B_EMPTY = 3, B_VRDY = 6, B_SCFULL = 9, B_PRDY = 11, B_ACCFULL = 13, B_ACCFREE = 15, B_DSFULL = 17, B_SBRDY = 18, B_COUNT = 19 };
 
 struct Chunk { int a, L; };
 __device__ __forceinline__ bool next_chunk(Chunk& ck, int T, int bs) {
@@ -97,7 +113,6 @@ __device__ __forceinline__ bool next_chunk(Chunk& ck, int T, int bs) {
   ck.a = a; ck.L = b - a;
   return true;
 }
-
 // the same schedule walked from the end: ck.a is the start of the chunk processed before
 __device__ __forceinline__ bool prev_chunk(Chunk& ck, int bs) {
   const int end = ck.a;
@@ -119,17 +134,27 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 #define FPB_GIVE_UP(code)                                             \
   do {                                                                \
     atomicCAS(p.status, 0, (code));                                   \
-    abort_flag = 1;                                                   \
+    *abort_flag = 1;                                                  \
+  } while (0)
+
+// diagnostics: stamp event `slot` (0..15) of chunk `c` for CTA (0,0,0) when a trace buffer is installed
+#define FPB_TRACE(slot, c)                                                                              \
+  do {                                                                                                  \
+    if (p.trace && (blockIdx.x | blockIdx.y | blockIdx.z) == 0 && (c) < 64) p.trace[(c) * 16 + (slot)] = clock64(); \
   } while (0)
 
 template <int MODE, int REV, int R, int CC>
-__global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant__ ScanParams p) {
+__global__ void __launch_bounds__(Cfg<MODE, R, CC>::NTHREADS, Cfg<MODE, R, CC>::MIN_CTAS)
+scan_kernel(const __grid_constant__ ScanParams p) {
   using G = Cfg<MODE, R, CC>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* sm = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  extern __shared__ __align__(1024) uint8_t sm[];
   const uint32_t sbase = smem_u32(sm);
-  __shared__ uint32_t tmem_slot;
-  __shared__ volatile int abort_flag;
+  if (sbase & 1023) {                                  // the swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, 0x7ff);
+    return;
+  }
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + G::OFF_BAR + OFF_ABORT);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + G::OFF_BAR + OFF_TMEM_SLOT);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -140,21 +165,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
   auto bar = [&](int slot) { return sbase + G::OFF_BAR + slot * 8; };
 
   if (tid == 0) {
-    for (int s = 0; s < 3; ++s) { mbar_init(bar(B_FULL + s), 1); mbar_init(bar(B_EMPTY + s), 1); mbar_init(bar(B_VRDY + s), N_SCORE); }
-    for (int j = 0; j < 2; ++j) {
-      mbar_init(bar(B_SCFULL + j), 1); mbar_init(bar(B_PRDY + j), N_SCORE);
-      mbar_init(bar(B_ACCFULL + j), 1); mbar_init(bar(B_ACCFREE + j), N_SCORE);
-    }
-    mbar_init(bar(B_DSFULL), 1); mbar_init(bar(B_SBRDY), N_STATE);
+    for (int s = 0; s < 3; ++s) { mbar_init(bar(B_FULL + s), 1); mbar_init(bar(B_EMPTY + s), 1); mbar_init(bar(B_VRDY + s), G::N_STATE); }
+    mbar_init(bar(B_SCFULL), 1); mbar_init(bar(B_SCFULL + 1), 1);
+    mbar_init(bar(B_PRDY), N_SCORE); mbar_init(bar(B_ACCFULL), 1); mbar_init(bar(B_ACCFREE), N_SCORE);
+    mbar_init(bar(B_DSFULL), 1); mbar_init(bar(B_DSFREE), G::N_STATE);
+    mbar_init(bar(B_SBRDY), G::N_STATE); mbar_init(bar(B_SBFREE), 1);
     fence_mbar_init();
-    abort_flag = 0;
+    *abort_flag = 0;
     prefetch_tmap(&p.map_x); prefetch_tmap(&p.map_k); prefetch_tmap(&p.map_v); prefetch_tmap(&p.map_out);
   }
-  if (warp == 1) { tmem_alloc(smem_u32(&tmem_slot), G::TM_COLS); tmem_relinquish(); }
+  if (warp == 1) { tmem_alloc(sbase + G::OFF_BAR + OFF_TMEM_SLOT, G::TM_COLS); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tm = tmem_slot;
+  const uint32_t tm = *tmem_slot;
 
   Chunk first{REV ? p.T : 0, 0};
   const bool any = advance<REV>(first, p.T, p.block_size);
@@ -166,7 +190,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
       int c = 0, issued = 0;
       do {
         const int s = c % G::STAGES;
-        if (!mbar_wait(bar(B_EMPTY + s), ((c / G::STAGES) & 1) ^ 1, &abort_flag)) { FPB_GIVE_UP(0x100 | B_EMPTY); break; }
+        if (!mbar_wait(bar(B_EMPTY + s), ((c / G::STAGES) & 1) ^ 1, abort_flag)) { FPB_GIVE_UP(0x100 | B_EMPTY); break; }
+        FPB_TRACE(14, c);
         const uint32_t st = sbase + G::OFF_STAGE + s * G::STAGE_BYTES;
         mbar_arrive_expect_tx(bar(B_FULL + s), G::STAGE_BYTES);
         const int xcol0 = MODE == MODE_FWD ? row0 : col0;
@@ -178,7 +203,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
         for (int cb = 0; cb < CC / 64; ++cb) tma_load_4d(st + G::X_BYTES + G::K_BYTES + cb * 8192, &p.map_v, bar(B_FULL + s), col0 + cb * 64, ck.a, h, b);
         ++issued; ++c;
       } while (advance<REV>(ck, p.T, p.block_size));
-      if (abort_flag) {   // let the copies in flight land before the CTA's shared memory is released
+      if (*abort_flag) {   // let the copies in flight land before the CTA's shared memory is released
         for (int i = max(0, issued - G::STAGES); i < issued; ++i) {
           const long long t0 = clock64();
           while (!mbar_try_wait(bar(B_FULL + i % G::STAGES), (i / G::STAGES) & 1) && clock64() - t0 < kWaitCycles) {}
@@ -200,39 +225,55 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
       auto mnmajor = [&](uint32_t base, int ks, uint32_t cb_stride) {  // MN-major tile, k-step of 16 rows
         return smem_desc(base + ks * 2048, cb_stride, 1024);
       };
-      auto issue_sc = [&](int s, int j) {
-        const uint32_t d = tm + G::TM_SC + j * 64;
+      // scores of chunk n (its tiles are in stage n % STAGES) into score buffer n % NSC; with block == false
+      // the call gives up at once (returns 0) when the tiles have not landed yet.  1 = issued, -1 = timed out
+      auto issue_sc = [&](int n, bool block) -> int {
+        const int s = n % G::STAGES;
+        const uint32_t ph = (n / G::STAGES) & 1;
+        if (!block) {
+          if (!mbar_try_wait(bar(B_FULL + s), ph)) return 0;
+          if (MODE == MODE_DQ && !mbar_try_wait(bar(B_VRDY + s), ph)) return 0;
+        } else {
+          if (!mbar_wait(bar(B_FULL + s), ph, abort_flag)) return -1;
+          if (MODE == MODE_DQ && !mbar_wait(bar(B_VRDY + s), ph, abort_flag)) return -1;
+        }
+        tc_fence_after();
+        const uint32_t d = tm + G::TM_SC + (n % G::NSC) * 64;
 #pragma unroll
         for (int ks = 0; ks < G::W1 / 16; ++ks)
           umma_bf16(d, kmajor(stage_x(s), ks, 8192), kmajor(MODE == MODE_FWD ? stage_k(s) : stage_v(s), ks, 8192), ID_SC, ks > 0);
-        umma_commit(bar(B_SCFULL + j));
+        umma_commit(bar(B_SCFULL + (n % G::NSC)));
+        return 1;
       };
-      bool ok = true;
       Chunk ck = first;
       int c = 0;
-      // first scores
-      ok = mbar_wait(bar(B_FULL + 0), 0, &abort_flag);
-      if (ok && MODE == MODE_DQ) ok = mbar_wait(bar(B_VRDY + 0), 0, &abort_flag);
+      bool ok = issue_sc(0, true) == 1;
       if (!ok) FPB_GIVE_UP(0x200 | B_FULL);
-      if (ok) { tc_fence_after(); issue_sc(0, 0); }
       while (ok) {
-        const int s = c % G::STAGES, j = c & 1;
+        const int s = c % G::STAGES;
         Chunk nx = ck;
         const bool has_next = advance<REV>(nx, p.T, p.block_size);
-        if (has_next) {
-          const int s1 = (c + 1) % G::STAGES;
-          const uint32_t ph1 = ((c + 1) / G::STAGES) & 1;
-          ok = mbar_wait(bar(B_FULL + s1), ph1, &abort_flag);
-          if (ok && MODE == MODE_DQ) ok = mbar_wait(bar(B_VRDY + s1), ph1, &abort_flag);
-          if (!ok) { FPB_GIVE_UP(0x200 | B_FULL); break; }
-          tc_fence_after();
-          issue_sc(s1, (c + 1) & 1);
-        }
-        // state term: ACC = X Sb (FWD) | X Sb^T (DQ)
-        if (!mbar_wait(bar(B_SBRDY), c & 1, &abort_flag)) { FPB_GIVE_UP(0x200 | B_SBRDY); break; }
-        if (!mbar_wait(bar(B_ACCFREE + j), ((c >> 1) & 1) ^ 1, &abort_flag)) { FPB_GIVE_UP(0x200 | B_ACCFREE); break; }
+        FPB_TRACE(0, c);
+        // 1. state increment dS = K^T Veta first: it depends on no other product of this chunk and feeds the
+        //    only chunk-to-chunk dependency (the state warps turn it into the next chunk's Sb)
+        if (!mbar_wait(bar(B_VRDY + s), (c / G::STAGES) & 1, abort_flag)) { FPB_GIVE_UP(0x200 | B_VRDY); break; }
+        if (!mbar_wait(bar(B_DSFREE), (c & 1) ^ 1, abort_flag)) { FPB_GIVE_UP(0x200 | B_DSFREE); break; }
+        FPB_TRACE(4, c);
         tc_fence_after();
-        const uint32_t acc = tm + G::TM_ACC + j * G::NOUT;
+#pragma unroll
+        for (int ks = 0; ks < C / 16; ++ks)
+          umma_bf16(tm + G::TM_DS, mnmajor(stage_k(s), ks, 8192), mnmajor(stage_v(s), ks, 8192), ID_DS, ks > 0);
+        umma_commit(bar(B_DSFULL));
+        // 2. scores of the next chunk as soon as its tiles are there (never wait for them here)
+        bool sc_next = !has_next;
+        if (G::NSC == 2 && !sc_next) sc_next = issue_sc(c + 1, false) == 1;
+        // 3. state term: ACC = X Sb (FWD) | X Sb^T (DQ)
+        if (!mbar_wait(bar(B_SBRDY), c & 1, abort_flag)) { FPB_GIVE_UP(0x200 | B_SBRDY); break; }
+        FPB_TRACE(1, c);
+        if (!mbar_wait(bar(B_ACCFREE), (c & 1) ^ 1, abort_flag)) { FPB_GIVE_UP(0x200 | B_ACCFREE); break; }
+        FPB_TRACE(2, c);
+        tc_fence_after();
+        const uint32_t acc = tm + G::TM_ACC;
         if (MODE == MODE_FWD) {
 #pragma unroll
           for (int ks = 0; ks < R / 16; ++ks)
@@ -242,22 +283,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
           for (int ks = 0; ks < CC / 16; ++ks)
             umma_bf16(acc, kmajor(stage_x(s), ks, 8192), kmajor(sbase + G::OFF_SB, ks, R * 128), ID_STATE, ks > 0);
         }
-        // intra-chunk term: ACC += P' Veta (FWD) | P' K (DQ)
-        if (!mbar_wait(bar(B_PRDY + j), (c >> 1) & 1, &abort_flag)) { FPB_GIVE_UP(0x200 | B_PRDY); break; }
-        if (!mbar_wait(bar(B_VRDY + s), (c / G::STAGES) & 1, &abort_flag)) { FPB_GIVE_UP(0x200 | B_VRDY); break; }
+        umma_commit(bar(B_SBFREE));      // Sb may be overwritten with the next state once this has run
+        if (G::NSC == 2 && !sc_next) sc_next = issue_sc(c + 1, false) == 1;
+        // 4. intra-chunk term: ACC += P' Veta (FWD) | P' K (DQ)
+        if (!mbar_wait(bar(B_PRDY), c & 1, abort_flag)) { FPB_GIVE_UP(0x200 | B_PRDY); break; }
+        FPB_TRACE(3, c);
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < C / 16; ++ks)
-          umma_bf16(acc, kmajor(sbase + G::OFF_P + j * G::P_BYTES, ks, 0),
-                    mnmajor(MODE == MODE_FWD ? stage_v(s) : stage_k(s), ks, 8192), ID_INTRA, 1);
-        umma_commit(bar(B_ACCFULL + j));
-        // state increment: dS = K^T Veta
-#pragma unroll
-        for (int ks = 0; ks < C / 16; ++ks)
-          umma_bf16(tm + G::TM_DS, mnmajor(stage_k(s), ks, 8192), mnmajor(stage_v(s), ks, 8192), ID_DS, ks > 0);
-        umma_commit(bar(B_DSFULL));
-        umma_commit(bar(B_EMPTY + s));
+          umma_bf16(acc, kmajor(sbase + G::OFF_P, ks, 0), mnmajor(MODE == MODE_FWD ? stage_v(s) : stage_k(s), ks, 8192), ID_INTRA, 1);
+        umma_commit(bar(B_ACCFULL));
+        umma_commit(bar(B_EMPTY + s));   // every product that reads this stage has been issued
+        FPB_TRACE(5, c);
         if (!has_next) break;
+        // with a single score buffer the next scores had to wait until P' of this chunk was taken out
+        if (!sc_next && issue_sc(c + 1, true) != 1) { FPB_GIVE_UP(0x200 | B_FULL); break; }
         ck = nx; ++c;
       }
     }
@@ -268,111 +308,28 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
     const int r_lo = q4 * 16 + (lane >> 2);          // this thread's two accumulator rows: r_lo, r_lo + 8
     const int cpair = (lane & 3) * 2;
 
-    auto scale_v = [&](int s, int L) {
-      uint8_t* vt = sm + G::OFF_STAGE + s * G::STAGE_BYTES + G::X_BYTES + G::K_BYTES;
-      for (int idx = t; idx < C * CC / 8; idx += N_SCORE) {
-        const int row = (idx >> 3) & 63;
-        uint4* ptr = reinterpret_cast<uint4*>(vt + idx * 16);
-        uint4 val = make_uint4(0u, 0u, 0u, 0u);
-        if (row < L) {
-          const float e = exp2f((float)(REV ? row + 1 : L - 1 - row) * lg);
-          val = *ptr;
-          uint32_t* w = reinterpret_cast<uint32_t*>(&val);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&w[i]));
-            w[i] = pack_bf16(f.x * e, f.y * e);
-          }
-        }
-        *ptr = val;
-      }
-      fence_async_smem();
-      mbar_arrive(bar(B_VRDY + s));
-    };
-
-    auto epilogue = [&](int c, Chunk ck) -> bool {
-      const int j = c & 1;
-      bool fail = !mbar_wait(bar(B_ACCFULL + j), (c >> 1) & 1, &abort_flag);
-      if (fail) FPB_GIVE_UP(0x300 | B_ACCFULL);
-      // the previous TMA store must have finished reading the staging tile
-      if (t == 0) tma_store_wait_read0();
-      if (named_bar_or(1, N_SCORE, fail)) return false;   // all 128 threads leave together
-      tc_fence_after();
-      // row scale: zeta_i (forward walks) or eta_j * rs (reverse walks)
-      const float z_lo = REV ? exp2f((float)(ck.L - 1 - r_lo) * lg) * rs : exp2f((float)(r_lo + 1) * lg);
-      const float z_hi = REV ? exp2f((float)(ck.L - 9 - r_lo) * lg) * rs : exp2f((float)(r_lo + 9) * lg);
-      uint8_t* stg = sm + G::OFF_OUT;
-#pragma unroll
-      for (int half = 0; half < G::NOUT / 64; ++half) {
-        uint32_t r[32];
-        tmem_ld_16x256b_x8(tm + lane_base + G::TM_ACC + j * G::NOUT + half * 64, r);
-        tmem_wait_ld();
-        if (half == G::NOUT / 64 - 1) { tc_fence_before(); mbar_arrive(bar(B_ACCFREE + j)); }
-#pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          const uint32_t lo = pack_bf16(__uint_as_float(r[4 * g]) * z_lo, __uint_as_float(r[4 * g + 1]) * z_lo);
-          const uint32_t hi = pack_bf16(__uint_as_float(r[4 * g + 2]) * z_hi, __uint_as_float(r[4 * g + 3]) * z_hi);
-          *reinterpret_cast<uint32_t*>(stg + half * 8192 + r_lo * 128 + ((g ^ (r_lo & 7)) << 4) + cpair * 2) = lo;
-          *reinterpret_cast<uint32_t*>(stg + half * 8192 + (r_lo + 8) * 128 + ((g ^ ((r_lo + 8) & 7)) << 4) + cpair * 2) = hi;
-        }
-      }
-      const bool whole_box = ck.L == C || ck.a + ck.L >= p.T;   // rows beyond L are past the sequence end: TMA clips them
-      if (whole_box) fence_async_smem();
-      named_bar_sync(1, N_SCORE);
-      const int ocol0 = MODE == MODE_FWD ? col0 : row0;
-      if (whole_box) {
-        if (t == 0) {
-#pragma unroll
-          for (int cb = 0; cb < G::NOUT / 64; ++cb) tma_store_4d(&p.map_out, sbase + G::OFF_OUT + cb * 8192, ocol0 + cb * 64, ck.a, h, b);
-          tma_store_commit();
-        }
-      } else {   // chunk cut short by a block end: rows >= L belong to the next chunk, store rows < L only
-        bf16* go = p.out + (int64_t)b * p.out_sb + (int64_t)h * p.out_sh + ocol0;
-        for (int idx = t; idx < ck.L * (G::NOUT / 8); idx += N_SCORE) {
-          const int row = idx / (G::NOUT / 8), ch = idx % (G::NOUT / 8);
-          const uint4 val = *reinterpret_cast<const uint4*>(stg + (ch >> 3) * 8192 + row * 128 + (((ch & 7) ^ (row & 7)) << 4));
-          *reinterpret_cast<uint4*>(go + (int64_t)(ck.a + row) * p.out_st + ch * 8) = val;
-        }
-        named_bar_sync(1, N_SCORE);   // staging is read by generic loads here: finish before it is rewritten
-      }
-      return true;
-    };
-
     if (any) {
-      Chunk ck = first, prev = first;
+      Chunk ck = first;
       int c = 0;
-      bool ok = mbar_wait(bar(B_FULL + 0), 0, &abort_flag);
-      if (!ok) FPB_GIVE_UP(0x300 | B_FULL);
-      ok = !named_bar_or(2, N_SCORE, !ok);
-      if (ok) scale_v(0, ck.L);
-      while (ok) {
-        const int j = c & 1;
+      while (true) {
         Chunk nx = ck;
         const bool has_next = advance<REV>(nx, p.T, p.block_size);
-        bool fail = false;
-        if (has_next) {
-          const int s1 = (c + 1) % G::STAGES;
-          fail = !mbar_wait(bar(B_FULL + s1), ((c + 1) / G::STAGES) & 1, &abort_flag);
-          if (fail) FPB_GIVE_UP(0x300 | B_FULL);
-          else scale_v(s1, nx.L);
-        }
-        // P' = tril(Sc) * gamma^-L * rs
-        if (!fail) {
-          fail = !mbar_wait(bar(B_SCFULL + j), (c >> 1) & 1, &abort_flag);
-          if (fail) FPB_GIVE_UP(0x300 | B_SCFULL);
-        }
+        // ---- P' = causal side of Sc, times gamma^-L (and rs in forward walks)
+        bool fail = !mbar_wait(bar(B_SCFULL + (c % G::NSC)), (c / G::NSC) & 1, abort_flag);
+        if (fail) FPB_GIVE_UP(0x300 | B_SCFULL);
+        if (t == 0) FPB_TRACE(6, c);
         if (!fail) {
           tc_fence_after();
           uint32_t r[32];
-          tmem_ld_16x256b_x8(tm + lane_base + G::TM_SC + j * 64, r);
+          tmem_ld_16x256b_x8(tm + lane_base + G::TM_SC + (c % G::NSC) * 64, r);
           tmem_wait_ld();
           tc_fence_before();
           const float cs = REV ? exp2f(-(float)ck.L * lg) : exp2f(-(float)ck.L * lg) * rs;
-          uint8_t* pt = sm + G::OFF_P + j * G::P_BYTES;
+          uint8_t* pt = sm + G::OFF_P;
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             const int col = g * 8 + cpair;
-            auto keep = [&](int cc, int rr) { return REV ? cc >= rr : cc <= rr; };   // causal side of the tile
+            auto keep = [&](int cc, int rr) { return REV ? cc >= rr : cc <= rr; };
             const float a0 = keep(col, r_lo) ? __uint_as_float(r[4 * g]) * cs : 0.f;
             const float a1 = keep(col + 1, r_lo) ? __uint_as_float(r[4 * g + 1]) * cs : 0.f;
             const float b0 = keep(col, r_lo + 8) ? __uint_as_float(r[4 * g + 2]) * cs : 0.f;
@@ -381,28 +338,76 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
             *reinterpret_cast<uint32_t*>(pt + (r_lo + 8) * 128 + ((g ^ ((r_lo + 8) & 7)) << 4) + cpair * 2) = pack_bf16(b0, b1);
           }
           fence_async_smem();
-          mbar_arrive(bar(B_PRDY + j));
+          mbar_arrive(bar(B_PRDY));
+          if (t == 0) FPB_TRACE(7, c);
+          // ---- epilogue: out_i = rowscale_i * ACC_i
+          fail = !mbar_wait(bar(B_ACCFULL), c & 1, abort_flag);
+          if (fail) FPB_GIVE_UP(0x300 | B_ACCFULL);
+          if (t == 0) FPB_TRACE(8, c);
         }
-        // a thread that gave up must not leave the others waiting at the epilogue's barriers
-        if (named_bar_or(2, N_SCORE, fail)) { ok = false; break; }
-        if (c > 0 && !epilogue(c - 1, prev)) { ok = false; break; }
+        // the previous TMA store must have finished reading the staging tile; the barrier also makes
+        // "some thread gave up" uniform, so that all 128 threads leave together
+        if (t == 0) tma_store_wait_read0();
+        if (named_bar_or(1, N_SCORE, fail)) break;
+        if (t == 0) FPB_TRACE(9, c);
+        tc_fence_after();
+        // row scale: zeta_i (forward walks) or eta_j * rs (reverse walks)
+        const float z_lo = REV ? exp2f((float)(ck.L - 1 - r_lo) * lg) * rs : exp2f((float)(r_lo + 1) * lg);
+        const float z_hi = REV ? exp2f((float)(ck.L - 9 - r_lo) * lg) * rs : exp2f((float)(r_lo + 9) * lg);
+        uint8_t* stg = sm + G::OFF_OUT;
+#pragma unroll
+        for (int half = 0; half < G::NOUT / 64; ++half) {
+          uint32_t r[32];
+          tmem_ld_16x256b_x8(tm + lane_base + G::TM_ACC + half * 64, r);
+          tmem_wait_ld();
+          if (half == G::NOUT / 64 - 1) { tc_fence_before(); mbar_arrive(bar(B_ACCFREE)); }
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const uint32_t lo = pack_bf16(__uint_as_float(r[4 * g]) * z_lo, __uint_as_float(r[4 * g + 1]) * z_lo);
+            const uint32_t hi = pack_bf16(__uint_as_float(r[4 * g + 2]) * z_hi, __uint_as_float(r[4 * g + 3]) * z_hi);
+            *reinterpret_cast<uint32_t*>(stg + half * 8192 + r_lo * 128 + ((g ^ (r_lo & 7)) << 4) + cpair * 2) = lo;
+            *reinterpret_cast<uint32_t*>(stg + half * 8192 + (r_lo + 8) * 128 + ((g ^ ((r_lo + 8) & 7)) << 4) + cpair * 2) = hi;
+          }
+        }
+        const bool whole_box = ck.L == C || ck.a + ck.L >= p.T;   // rows beyond L are past the sequence end: TMA clips them
+        if (whole_box) fence_async_smem();
+        named_bar_sync(2, N_SCORE);
+        const int ocol0 = MODE == MODE_FWD ? col0 : row0;
+        if (whole_box) {
+          if (t == 0) {
+#pragma unroll
+            for (int cb = 0; cb < G::NOUT / 64; ++cb) tma_store_4d(&p.map_out, sbase + G::OFF_OUT + cb * 8192, ocol0 + cb * 64, ck.a, h, b);
+            tma_store_commit();
+          }
+        } else {   // chunk cut short by a block end: rows >= L belong to another chunk, store rows < L only
+          bf16* go = p.out + (int64_t)b * p.out_sb + (int64_t)h * p.out_sh + ocol0;
+          for (int idx = t; idx < ck.L * (G::NOUT / 8); idx += N_SCORE) {
+            const int row = idx / (G::NOUT / 8), ch = idx % (G::NOUT / 8);
+            const uint4 val = *reinterpret_cast<const uint4*>(stg + (ch >> 3) * 8192 + row * 128 + (((ch & 7) ^ (row & 7)) << 4));
+            *reinterpret_cast<uint4*>(go + (int64_t)(ck.a + row) * p.out_st + ch * 8) = val;
+          }
+          // these generic reads of the staging tile are ordered before its next rewrite by the barrier at
+          // the top of the next epilogue
+        }
+        if (t == 0) FPB_TRACE(10, c);
         if (!has_next) break;
-        prev = ck; ck = nx; ++c;
+        ck = nx; ++c;
       }
-      if (ok) epilogue(c, ck);
       if (t == 0) tma_store_wait_all0();
     }
   } else {                                           // ---------------- state warps
+    const int t = tid - STATE_WARP0 * 32;            // 0..N_STATE-1
     const int q4 = warp & 3;
-    const int half = (warp - STATE_WARP0) >> 2;      // which half of the CC state columns
+    const int half = (warp - STATE_WARP0) >> 2;      // which slice of the CC state columns (BIG only)
     const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
+    const int wcol0 = half * G::WCOLS;
     float S[G::NS];
 
     // element enumeration of this thread's registers: i -> (row, col) inside the (R, CC) tile
-    //   R == 128: row = 32*q4 + lane, col = half*CC/2 + i
-    //   R ==  64: row = 16*q4 + lane/4 + 8*((i>>1)&1), col = half*CC/2 + 8*(i>>2) + 2*(lane&3) + (i&1)
+    //   R == 128: row = 32*q4 + lane, col = wcol0 + i
+    //   R ==  64: row = 16*q4 + lane/4 + 8*((i>>1)&1), col = wcol0 + 8*(i>>2) + 2*(lane&3) + (i&1)
     auto row_of = [&](int i) { return R == 128 ? q4 * 32 + lane : q4 * 16 + (lane >> 2) + 8 * ((i >> 1) & 1); };
-    auto col_of = [&](int i) { return R == 128 ? half * (CC / 2) + i : half * (CC / 2) + 8 * (i >> 2) + 2 * (lane & 3) + (i & 1); };
+    auto col_of = [&](int i) { return R == 128 ? wcol0 + i : wcol0 + 8 * (i >> 2) + 2 * (lane & 3) + (i & 1); };
 
     const int64_t state_elems = (int64_t)p.dk * p.dv;
     // where the walk's start value comes from and where its end value goes.  Forward walks start from the
@@ -424,7 +429,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
 
     auto load_global = [&](const bf16* src, bool accumulate) {
       if (R == 128) {
-        const bf16* rowp = src + (int64_t)(row0 + row_of(0)) * p.dv + col0 + half * (CC / 2);
+        const bf16* rowp = src + (int64_t)(row0 + row_of(0)) * p.dv + col0 + wcol0;
 #pragma unroll
         for (int i = 0; i < G::NS; i += 8) {
           const uint4 val = *reinterpret_cast<const uint4*>(rowp + i);
@@ -453,7 +458,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
     };
     auto store_global = [&](bf16* dst) {
       if (R == 128) {
-        bf16* rowp = dst + (int64_t)(row0 + row_of(0)) * p.dv + col0 + half * (CC / 2);
+        bf16* rowp = dst + (int64_t)(row0 + row_of(0)) * p.dv + col0 + wcol0;
 #pragma unroll
         for (int i = 0; i < G::NS; i += 8) {
           uint4 val;
@@ -492,6 +497,34 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
       fence_async_smem();
       mbar_arrive(bar(B_SBRDY));
     };
+    // in-place row scale of the V tile of chunk n: eta_j = gamma^(L-1-j) (forward walks) or
+    // zeta_i = gamma^(i+1) (reverse walks, the tile holds dO); rows >= L are zeroed
+    // returns 1 = done, 0 = tiles not there yet (only with block == false), -1 = timed out
+    auto scale_v = [&](int n, int L, bool block) -> int {
+      const int s = n % G::STAGES;
+      if (!block) { if (!mbar_try_wait(bar(B_FULL + s), (n / G::STAGES) & 1)) return 0; }
+      else if (!mbar_wait(bar(B_FULL + s), (n / G::STAGES) & 1, abort_flag)) return -1;
+      uint8_t* vt = sm + G::OFF_STAGE + s * G::STAGE_BYTES + G::X_BYTES + G::K_BYTES;
+      for (int idx = t; idx < C * CC / 8; idx += G::N_STATE) {
+        const int row = (idx >> 3) & 63;
+        uint4* ptr = reinterpret_cast<uint4*>(vt + idx * 16);
+        uint4 val = make_uint4(0u, 0u, 0u, 0u);
+        if (row < L) {
+          const float e = exp2f((float)(REV ? row + 1 : L - 1 - row) * lg);
+          val = *ptr;
+          uint32_t* w = reinterpret_cast<uint32_t*>(&val);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&w[i]));
+            w[i] = pack_bf16(f.x * e, f.y * e);
+          }
+        }
+        *ptr = val;
+      }
+      fence_async_smem();
+      mbar_arrive(bar(B_VRDY + s));
+      return 1;
+    };
 
     if (x_start) load_global(x_start, false);
     else {
@@ -500,52 +533,49 @@ __global__ void __launch_bounds__(NTHREADS, 1) scan_kernel(const __grid_constant
     }
     const float ds_scale = REV ? 1.0f : rs;   // forward: S += rs K^T Veta;  reverse: G += Q^T (zeta.dO)
     if (any) {
+      bool ok = scale_v(0, first.L, true) == 1;
+      if (!ok) FPB_GIVE_UP(0x400 | B_FULL);
       inject(first.a + first.L);
       publish_sb();
       Chunk ck = first;
       int c = 0;
-      while (true) {
+      while (ok) {
         Chunk nx = ck;
         const bool has_next = advance<REV>(nx, p.T, p.block_size);
-        if (!mbar_wait(bar(B_DSFULL), c & 1, &abort_flag)) { FPB_GIVE_UP(0x400 | B_DSFULL); break; }
+        if (t == 0) FPB_TRACE(15, c);
+        // scale the next chunk's V now if its tiles have landed; otherwise after this chunk's state work
+        bool v_next = !has_next || scale_v(c + 1, nx.L, false) == 1;
+        if (t == 0) FPB_TRACE(11, c);
+        if (!mbar_wait(bar(B_DSFULL), c & 1, abort_flag)) { FPB_GIVE_UP(0x400 | B_DSFULL); break; }
+        if (t == 0) FPB_TRACE(12, c);
         tc_fence_after();
         const float gl = exp2f((float)ck.L * lg);
-        if (R == 128) {
+        // 16 registers at a time keeps the state warps inside the register budget of two CTAs per SM
 #pragma unroll
-          for (int i0 = 0; i0 < G::NS; i0 += 32) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(tm + lane_base + G::TM_DS + half * (CC / 2) + i0, r);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) S[i0 + i] = fmaf(gl, S[i0 + i], ds_scale * __uint_as_float(r[i]));
-          }
-        } else if (G::NS >= 32) {
-#pragma unroll
-          for (int i0 = 0; i0 < G::NS; i0 += 32) {
-            uint32_t r[32];
-            tmem_ld_16x256b_x8(tm + lane_base + G::TM_DS + half * (CC / 2) + i0 * 2, r);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) S[i0 + i] = fmaf(gl, S[i0 + i], ds_scale * __uint_as_float(r[i]));
-          }
-        } else {
+        for (int i0 = 0; i0 < G::NS; i0 += 16) {
           uint32_t r[16];
-          tmem_ld_16x256b_x4(tm + lane_base + G::TM_DS + half * (CC / 2), r);
+          if (R == 128) tmem_ld_32x32b_x16(tm + lane_base + G::TM_DS + wcol0 + i0, r);
+          else tmem_ld_16x256b_x4(tm + lane_base + G::TM_DS + wcol0 + i0 * 2, r);
           tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) S[i] = fmaf(gl, S[i], ds_scale * __uint_as_float(r[i]));
+          for (int i = 0; i < 16; ++i) S[i0 + i] = fmaf(gl, S[i0 + i], ds_scale * __uint_as_float(r[i]));
         }
         tc_fence_before();
+        mbar_arrive(bar(B_DSFREE));          // the increment has been read: the next one may overwrite it
         const int end = ck.a + ck.L;
         if (!REV && p.block_size > 0 && p.block_states && end % p.block_size == 0 && end / p.block_size - 1 < p.n_blocks)
           store_global(p.block_states + (((int64_t)b * p.n_blocks + (end / p.block_size - 1)) * p.H + h) * state_elems);
         if (!has_next) break;
         inject(nx.a + nx.L);
+        // Sb still holds this chunk's start state until the state-term product that reads it has run
+        if (!mbar_wait(bar(B_SBFREE), c & 1, abort_flag)) { FPB_GIVE_UP(0x400 | B_SBFREE); break; }
         publish_sb();
+        if (t == 0) FPB_TRACE(13, c);
+        if (!v_next && scale_v(c + 1, nx.L, true) != 1) { FPB_GIVE_UP(0x400 | B_FULL); break; }
         ck = nx; ++c;
       }
     }
-    if (x_end && !abort_flag) store_global(x_end);
+    if (x_end && !*abort_flag) store_global(x_end);
   }
 
   // ---------------- teardown
@@ -565,13 +595,15 @@ int launch_scan_t(const ScanParams& p, dim3 grid, cudaStream_t stream) {
       return FPB_ERR_LAUNCH;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  scan_kernel<MODE, REV, R, CC><<<grid, NTHREADS, G::SMEM, stream>>>(p);
+  scan_kernel<MODE, REV, R, CC><<<grid, G::NTHREADS, G::SMEM, stream>>>(p);
   return FPB_OK;
 }
 template <int MODE, int R, int CC>
 int launch_scan(const ScanParams& p, bool rev, dim3 grid, cudaStream_t stream) {
   return rev ? launch_scan_t<MODE, 1, R, CC>(p, grid, stream) : launch_scan_t<MODE, 0, R, CC>(p, grid, stream);
 }
+
+long long* g_trace = nullptr;   // set by fpb_debug_trace
 
 bool aligned_state(const StateView& s) { return !s.data || ((uintptr_t)s.data % 16 == 0 && s.sb % 8 == 0 && s.sh % 8 == 0); }
 
@@ -616,20 +648,17 @@ int launch_pass(const PassArgs& a, cudaStream_t stream) {
   p.sfx_blocks = (bf16*)a.sfx.blocks; p.sfx_M = a.sfx.M; p.sfx_N = a.sfx.N;
   p.T = T; p.H = H; p.dk = dk; p.dv = dv; p.block_size = a.block_size; p.n_blocks = a.n_blocks;
   p.status = device_status_ptr();
+  p.trace = g_trace;
   if (!p.status) return FPB_ERR_LAUNCH;
   for (int h = 0; h < H; ++h) p.log2g[h] = (float)std::log2((double)a.gamma[h]);
 
 #define FPB_SCAN_CASE(MODE_, R_, CC_, TILES_) return launch_scan<MODE_, R_, CC_>(p, a.rev, dim3((TILES_), H, B), stream)
-  if (a.mode == MODE_FWD) {       // state tile: all dk rows x CC columns of dv
-    if (dk == 128 && dv % 128 == 0) FPB_SCAN_CASE(MODE_FWD, 128, 128, dv / 128);
-    if (dk == 128 && dv == 64) FPB_SCAN_CASE(MODE_FWD, 128, 64, 1);
-    if (dk == 64 && dv % 128 == 0) FPB_SCAN_CASE(MODE_FWD, 64, 128, dv / 128);
-    if (dk == 64 && dv == 64) FPB_SCAN_CASE(MODE_FWD, 64, 64, 1);
-  } else {                        // state tile: R rows of dk x all dv columns
-    if (dv == 128 && dk == 128) FPB_SCAN_CASE(MODE_DQ, 128, 128, 1);
-    if (dv == 128 && dk == 64) FPB_SCAN_CASE(MODE_DQ, 64, 128, 1);
-    if (dv == 64 && dk == 128) FPB_SCAN_CASE(MODE_DQ, 128, 64, 1);
-    if (dv == 64 && dk == 64) FPB_SCAN_CASE(MODE_DQ, 64, 64, 1);
+  if (a.mode == MODE_FWD) {       // state tile: all dk rows x 64 columns of dv
+    if (dk == 128) FPB_SCAN_CASE(MODE_FWD, 128, 64, dv / 64);
+    if (dk == 64) FPB_SCAN_CASE(MODE_FWD, 64, 64, dv / 64);
+  } else {                        // state tile: 64 rows of dk x all dv columns
+    if (dv == 64) FPB_SCAN_CASE(MODE_DQ, 64, 64, dk / 64);
+    if (dv == 128) FPB_SCAN_CASE(MODE_DQ, 64, 128, dk / 64);
     if (dv == 256) FPB_SCAN_CASE(MODE_DQ, 64, 256, dk / 64);
   }
 #undef FPB_SCAN_CASE
@@ -637,6 +666,10 @@ int launch_pass(const PassArgs& a, cudaStream_t stream) {
 }
 
 }  // namespace
+
+// Diagnostics hook (not part of the public header): install a device buffer of 64*16 int64 that the next
+// launches fill with clock64() stamps of their first CTA; null removes it.
+extern "C" void fpb_debug_trace(void* device_buffer) { g_trace = (long long*)device_buffer; }
 
 int launch_umma_fwd(const UmmaFwdArgs& a, cudaStream_t stream) {
   if (a.dtype != FPB_BF16) return FPB_UMMA_NOT_APPLICABLE;
