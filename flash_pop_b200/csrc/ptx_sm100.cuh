@@ -37,6 +37,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking phase test (try_wait may suspend the thread for a time slice when the phase is not complete,
+// which is what a blocking wait wants and what a polling loop must avoid).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Every wait in the kernels is bounded: after about a second of spinning (or as soon as another
 // thread of the CTA has given up, *abort_flag != 0) the wait returns false, and the caller records
 // which wait it was and leaves its loop.

@@ -31,10 +31,13 @@
 // warps 6.. "state" warps (in-place row scaling of V, state update, bf16 state copy).  All hand-offs
 // are mbarriers; every wait is bounded and reports through the status word instead of hanging.
 //
-// A sequence is strictly serial chunk to chunk (dS_c -> state -> X Sb of chunk c+1 -> ...), so one CTA
-// cannot keep the tensor pipe busy by itself.  State tiles are therefore kept narrow (64 state columns
-// for the output walks, 64 state rows for the dQ/dK walks): 256 tensor-memory columns, ~112 KB of
-// shared memory and 320 threads per CTA, so that two CTAs share an SM and fill each other's bubbles.
+// Scheduling.  Per chunk the work is a feed-forward chain (TMA -> V scaling -> Sc, dS -> P', state update
+// -> X Sb, P' V -> epilogue) whose every hand-off costs a few hundred cycles; only the fp32 state
+// recurrence in the state warps' registers is truly serial.  So no role walks the chunks in lock step:
+// the MMA issuer, the state warps and the score warps each POLL their input barriers and run whichever of
+// their tasks is ready (scores of chunk n+1 before the products of chunk n if that is what has arrived),
+// with the score tile, P' and the accumulator double-buffered where tensor/shared memory allows, so that
+// several chunks are in flight per SM and the chain latency is hidden.
 #include "fpb_common.cuh"
 #include "ptx_sm100.cuh"
 #include "tensormap.cuh"
@@ -62,41 +65,46 @@ struct ScanParams {
   int32_t T, H, dk, dv, block_size, n_blocks;
   int32_t* status;
   long long* trace;              // diagnostics: per-chunk clock64() stamps of CTA (0,0,0), or null
+  int32_t skip;                  // diagnostics (timing experiments only, results become wrong): bit mask of work to leave out
   float log2g[FPB_MAX_HEADS];
 };
 
 // barrier slots (8 bytes each) at the start of the barrier page, then two 4-byte words
-enum { B_FULL = 0, B_EMPTY = 3, B_VRDY = 6, B_SCFULL = 9, B_PRDY = 11, B_ACCFULL = 12, B_ACCFREE = 13, B_DSFULL = 14, B_DSFREE = 15, B_SBRDY = 16, B_SBFREE = 17, B_COUNT = 18 };
+enum { B_FULL = 0, B_EMPTY = 3, B_VRDY = 6, B_SCFULL = 9, B_PRDY = 11, B_ACCFULL = 13, B_ACCFREE = 15, B_DSFULL = 17,
+       B_DSFREE = 18, B_SBRDY = 19, B_SBFREE = 20, B_COUNT = 21 };
 constexpr int OFF_TMEM_SLOT = B_COUNT * 8, OFF_ABORT = OFF_TMEM_SLOT + 4, BAR_PAGE = 256;
 
 template <int MODE, int R, int CC>
 struct Cfg {
-  static constexpr bool BIG = CC == 256;                     // one CTA per SM; otherwise two
   static constexpr int W1 = MODE == MODE_FWD ? R : CC;       // width of X (and of the Sc contraction)
   static constexpr int NOUT = MODE == MODE_FWD ? CC : R;     // width of the output tile
-  static constexpr int STATE_WARPS = BIG ? 8 : 4;
+  // one CTA per SM for the large state tiles (128x128, 64x256), two for the small ones
+  static constexpr bool ONE = R * CC >= 128 * 128;
+  static constexpr int STATE_WARPS = ONE ? 8 : 4;
   static constexpr int N_STATE = 32 * STATE_WARPS;
   static constexpr int NTHREADS = STATE_WARP0 * 32 + N_STATE;
-  static constexpr int MIN_CTAS = BIG ? 1 : 2;
+  static constexpr int MIN_CTAS = ONE ? 1 : 2;
+  static constexpr int NP = ONE ? 2 : 1;                     // P' buffers
+  static constexpr int NACC = ONE ? 2 : 1;                   // accumulator buffers
   static constexpr int X_BYTES = C * W1 * 2, K_BYTES = C * R * 2, V_BYTES = C * CC * 2;
   static constexpr int STAGE_BYTES = X_BYTES + K_BYTES + V_BYTES;
   static constexpr int P_BYTES = C * C * 2;
   static constexpr int SB_BYTES = R * CC * 2;
   static constexpr int OUT_BYTES = C * NOUT * 2;
-  static constexpr int FIXED = P_BYTES + SB_BYTES + OUT_BYTES + BAR_PAGE;
-  static constexpr int SMEM_LIMIT = BIG ? 226 * 1024 : 115712;   // (233472 B per SM) / 2 - 1 KB system reserve
+  static constexpr int FIXED = NP * P_BYTES + SB_BYTES + OUT_BYTES + BAR_PAGE;
+  static constexpr int SMEM_LIMIT = ONE ? 226 * 1024 : 115712;   // (233472 B per SM) / 2 - 1 KB system reserve
   static constexpr int STAGES = (FIXED + 3 * STAGE_BYTES <= SMEM_LIMIT) ? 3 : 2;
   static constexpr int OFF_STAGE = 0;
   static constexpr int OFF_P = STAGES * STAGE_BYTES;
-  static constexpr int OFF_SB = OFF_P + P_BYTES;
+  static constexpr int OFF_SB = OFF_P + NP * P_BYTES;
   static constexpr int OFF_OUT = OFF_SB + SB_BYTES;
   static constexpr int OFF_BAR = OFF_OUT + OUT_BYTES;
   static constexpr int SMEM = OFF_BAR + BAR_PAGE;
   static_assert(SMEM <= SMEM_LIMIT, "shared memory budget");
-  // tensor-memory columns: score tile(s), one accumulator, the state increment
-  static constexpr int TM_COLS = BIG ? 512 : 256;
-  static constexpr int NSC = (2 * 64 + NOUT + CC <= TM_COLS) ? 2 : 1;
-  static constexpr int TM_SC = 0, TM_ACC = 64 * NSC, TM_DS = TM_ACC + NOUT;
+  // tensor-memory columns: score tile(s), accumulator(s), the state increment
+  static constexpr int TM_COLS = ONE ? 512 : 256;
+  static constexpr int NSC = (2 * 64 + NACC * NOUT + CC <= TM_COLS) ? 2 : 1;
+  static constexpr int TM_SC = 0, TM_ACC = 64 * NSC, TM_DS = TM_ACC + NACC * NOUT;
   static_assert(TM_DS + CC <= TM_COLS, "tensor memory budget");
   // state registers per state-warp thread; NHALF warps share one tensor-memory sub-partition
   static constexpr int NHALF = STATE_WARPS / 4;
@@ -125,6 +133,10 @@ __device__ __forceinline__ bool prev_chunk(Chunk& ck, int bs) {
 template <int REV> __device__ __forceinline__ bool advance(Chunk& ck, int T, int bs) {
   return REV ? prev_chunk(ck, bs) : next_chunk(ck, T, bs);
 }
+__device__ __forceinline__ int chunk_count(int T, int bs) {
+  if (bs <= 0) return (T + C - 1) / C;
+  return (T / bs) * ((bs + C - 1) / C) + (T % bs + C - 1) / C;
+}
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -142,6 +154,18 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   do {                                                                                                  \
     if (p.trace && (blockIdx.x | blockIdx.y | blockIdx.z) == 0 && (c) < 64) p.trace[(c) * 16 + (slot)] = clock64(); \
   } while (0)
+
+// A polling loop that made no progress: true when it should give up (another thread did, or ~1 s passed).
+struct Patience {
+  long long t_last;
+  int idle;
+  __device__ __forceinline__ void progress() { idle = 0; }
+  __device__ __forceinline__ bool exhausted(volatile int* abort_flag) {
+    if (idle == 0) t_last = clock64();
+    if ((++idle & 31) != 0) return false;
+    return *abort_flag != 0 || clock64() - t_last > kWaitCycles;
+  }
+};
 
 template <int MODE, int REV, int R, int CC>
 __global__ void __launch_bounds__(Cfg<MODE, R, CC>::NTHREADS, Cfg<MODE, R, CC>::MIN_CTAS)
@@ -162,12 +186,17 @@ scan_kernel(const __grid_constant__ ScanParams p) {
   const int col0 = MODE == MODE_FWD ? tile * CC : 0;    // state cols [col0, col0+CC) of dv
   const float lg = p.log2g[h];
   const float rs = rsqrtf((float)p.dk);
+  const int NC = chunk_count(p.T, p.block_size);
   auto bar = [&](int slot) { return sbase + G::OFF_BAR + slot * 8; };
+  auto stage_of = [&](int n) { return n % G::STAGES; };
+  auto stage_ph = [&](int n) { return (uint32_t)((n / G::STAGES) & 1); };
 
   if (tid == 0) {
     for (int s = 0; s < 3; ++s) { mbar_init(bar(B_FULL + s), 1); mbar_init(bar(B_EMPTY + s), 1); mbar_init(bar(B_VRDY + s), G::N_STATE); }
-    mbar_init(bar(B_SCFULL), 1); mbar_init(bar(B_SCFULL + 1), 1);
-    mbar_init(bar(B_PRDY), N_SCORE); mbar_init(bar(B_ACCFULL), 1); mbar_init(bar(B_ACCFREE), N_SCORE);
+    for (int j = 0; j < 2; ++j) {
+      mbar_init(bar(B_SCFULL + j), 1); mbar_init(bar(B_PRDY + j), N_SCORE);
+      mbar_init(bar(B_ACCFULL + j), 1); mbar_init(bar(B_ACCFREE + j), N_SCORE);
+    }
     mbar_init(bar(B_DSFULL), 1); mbar_init(bar(B_DSFREE), G::N_STATE);
     mbar_init(bar(B_SBRDY), G::N_STATE); mbar_init(bar(B_SBFREE), 1);
     fence_mbar_init();
@@ -181,16 +210,16 @@ scan_kernel(const __grid_constant__ ScanParams p) {
   const uint32_t tm = *tmem_slot;
 
   Chunk first{REV ? p.T : 0, 0};
-  const bool any = advance<REV>(first, p.T, p.block_size);
+  advance<REV>(first, p.T, p.block_size);
 
   // =============================================================================================
   if (warp == 0) {                                   // ---------------- TMA producer
-    if (lane == 0 && any) {
+    if (lane == 0 && NC > 0) {
       Chunk ck = first;
-      int c = 0, issued = 0;
-      do {
-        const int s = c % G::STAGES;
-        if (!mbar_wait(bar(B_EMPTY + s), ((c / G::STAGES) & 1) ^ 1, abort_flag)) { FPB_GIVE_UP(0x100 | B_EMPTY); break; }
+      int issued = 0;
+      for (int c = 0; c < NC; ++c) {
+        const int s = stage_of(c);
+        if (!mbar_wait(bar(B_EMPTY + s), stage_ph(c) ^ 1, abort_flag)) { FPB_GIVE_UP(0x100 | B_EMPTY); break; }
         FPB_TRACE(14, c);
         const uint32_t st = sbase + G::OFF_STAGE + s * G::STAGE_BYTES;
         mbar_arrive_expect_tx(bar(B_FULL + s), G::STAGE_BYTES);
@@ -201,104 +230,124 @@ scan_kernel(const __grid_constant__ ScanParams p) {
         for (int cb = 0; cb < R / 64; ++cb) tma_load_4d(st + G::X_BYTES + cb * 8192, &p.map_k, bar(B_FULL + s), row0 + cb * 64, ck.a, h, b);
 #pragma unroll
         for (int cb = 0; cb < CC / 64; ++cb) tma_load_4d(st + G::X_BYTES + G::K_BYTES + cb * 8192, &p.map_v, bar(B_FULL + s), col0 + cb * 64, ck.a, h, b);
-        ++issued; ++c;
-      } while (advance<REV>(ck, p.T, p.block_size));
+        ++issued;
+        advance<REV>(ck, p.T, p.block_size);
+      }
       if (*abort_flag) {   // let the copies in flight land before the CTA's shared memory is released
         for (int i = max(0, issued - G::STAGES); i < issued; ++i) {
           const long long t0 = clock64();
-          while (!mbar_try_wait(bar(B_FULL + i % G::STAGES), (i / G::STAGES) & 1) && clock64() - t0 < kWaitCycles) {}
+          while (!mbar_try_wait(bar(B_FULL + stage_of(i)), stage_ph(i)) && clock64() - t0 < kWaitCycles) {}
         }
       }
     }
   } else if (warp == 1) {                            // ---------------- MMA issuer
-    if (lane == 0 && any) {
+    if (lane == 0 && NC > 0) {
       constexpr uint32_t ID_SC = idesc_bf16(64, 64, 0, 0);
       constexpr uint32_t ID_STATE = MODE == MODE_FWD ? idesc_bf16(64, CC, 0, 1) : idesc_bf16(64, R, 0, 0);
       constexpr uint32_t ID_INTRA = idesc_bf16(64, G::NOUT, 0, 1);
       constexpr uint32_t ID_DS = idesc_bf16(R, CC, 1, 1);
-      auto stage_x = [&](int s) { return sbase + G::OFF_STAGE + s * G::STAGE_BYTES; };
-      auto stage_k = [&](int s) { return stage_x(s) + G::X_BYTES; };
-      auto stage_v = [&](int s) { return stage_k(s) + G::K_BYTES; };
-      auto kmajor = [&](uint32_t base, int ks, uint32_t cb_stride) {   // K-major tile, k-step of 16 elements
-        return smem_desc(base + (ks >> 2) * cb_stride + (ks & 3) * 32, 16, 1024);
-      };
-      auto mnmajor = [&](uint32_t base, int ks, uint32_t cb_stride) {  // MN-major tile, k-step of 16 rows
-        return smem_desc(base + ks * 2048, cb_stride, 1024);
-      };
-      // scores of chunk n (its tiles are in stage n % STAGES) into score buffer n % NSC; with block == false
-      // the call gives up at once (returns 0) when the tiles have not landed yet.  1 = issued, -1 = timed out
-      auto issue_sc = [&](int n, bool block) -> int {
-        const int s = n % G::STAGES;
-        const uint32_t ph = (n / G::STAGES) & 1;
-        if (!block) {
-          if (!mbar_try_wait(bar(B_FULL + s), ph)) return 0;
-          if (MODE == MODE_DQ && !mbar_try_wait(bar(B_VRDY + s), ph)) return 0;
-        } else {
-          if (!mbar_wait(bar(B_FULL + s), ph, abort_flag)) return -1;
-          if (MODE == MODE_DQ && !mbar_wait(bar(B_VRDY + s), ph, abort_flag)) return -1;
+      // Descriptors are built once; inside the issue loops an operand address advances by adding to the
+      // 14-bit address field (16-byte units), so one tcgen05.mma costs this thread two additions.
+      //   K-major tile [cb][64 rows][128 B]: k-step ks (16 elements) -> + (ks/4) * (column-block stride) + (ks%4) * 32 bytes
+      //   MN-major tile: k-step ks (16 rows) -> + ks * 2048 bytes; lbo = column-block stride
+      constexpr uint32_t STAGE16 = G::STAGE_BYTES >> 4;
+      const uint64_t d_x = smem_desc(sbase + G::OFF_STAGE, 16, 1024);                                  // X, K-major
+      const uint64_t d_kk = smem_desc(sbase + G::OFF_STAGE + G::X_BYTES, 16, 1024);                    // K, K-major
+      const uint64_t d_km = smem_desc(sbase + G::OFF_STAGE + G::X_BYTES, 8192, 1024);                  // K, MN-major
+      const uint64_t d_vk = smem_desc(sbase + G::OFF_STAGE + G::X_BYTES + G::K_BYTES, 16, 1024);       // V, K-major
+      const uint64_t d_vm = smem_desc(sbase + G::OFF_STAGE + G::X_BYTES + G::K_BYTES, 8192, 1024);     // V, MN-major
+      const uint64_t d_sb = MODE == MODE_FWD ? smem_desc(sbase + G::OFF_SB, R * 128, 1024)             // Sb: MN-major (FWD)
+                                             : smem_desc(sbase + G::OFF_SB, 16, 1024);                 //     K-major (DQ)
+      const uint64_t d_p = smem_desc(sbase + G::OFF_P, 16, 1024);                                       // P', K-major
+      auto kstep = [](int ks, uint32_t cb_stride) { return (uint64_t)((ks >> 2) * (cb_stride >> 4) + (ks & 3) * 2); };
+      auto mstep = [](int ks) { return (uint64_t)(ks * 128); };
+      auto ready = [&](int slot, uint32_t parity) { return mbar_test_wait(bar(slot), parity); };
+      // Next chunk to issue for each of the four products, and the next stage to hand back to the producer.
+      // Each product of chunk n is issued when its inputs are there; the tensor pipe runs them in issue order.
+      int n_sc = 0, n_ds = 0, n_qs = 0, n_pv = 0, n_rel = 0;
+      // a stage goes back to the producer as soon as all four products of its chunk have been issued (issuing
+      // blocks while the tensor pipe is busy, so this is checked after every group, not once per round)
+      auto release = [&]() {
+        while (n_rel < n_pv && n_rel < n_ds && n_rel < n_sc) {
+          umma_commit(bar(B_EMPTY + stage_of(n_rel)));
+          FPB_TRACE(5, n_rel);
+          ++n_rel;
         }
-        tc_fence_after();
-        const uint32_t d = tm + G::TM_SC + (n % G::NSC) * 64;
-#pragma unroll
-        for (int ks = 0; ks < G::W1 / 16; ++ks)
-          umma_bf16(d, kmajor(stage_x(s), ks, 8192), kmajor(MODE == MODE_FWD ? stage_k(s) : stage_v(s), ks, 8192), ID_SC, ks > 0);
-        umma_commit(bar(B_SCFULL + (n % G::NSC)));
-        return 1;
       };
-      Chunk ck = first;
-      int c = 0;
-      bool ok = issue_sc(0, true) == 1;
-      if (!ok) FPB_GIVE_UP(0x200 | B_FULL);
-      while (ok) {
-        const int s = c % G::STAGES;
-        Chunk nx = ck;
-        const bool has_next = advance<REV>(nx, p.T, p.block_size);
-        FPB_TRACE(0, c);
-        // 1. state increment dS = K^T Veta first: it depends on no other product of this chunk and feeds the
-        //    only chunk-to-chunk dependency (the state warps turn it into the next chunk's Sb)
-        if (!mbar_wait(bar(B_VRDY + s), (c / G::STAGES) & 1, abort_flag)) { FPB_GIVE_UP(0x200 | B_VRDY); break; }
-        if (!mbar_wait(bar(B_DSFREE), (c & 1) ^ 1, abort_flag)) { FPB_GIVE_UP(0x200 | B_DSFREE); break; }
-        FPB_TRACE(4, c);
-        tc_fence_after();
+      // A barrier test costs this thread on the order of a hundred cycles while the tensor pipe is streaming
+      // operands out of shared memory, so each barrier phase is tested until it has been seen complete once and
+      // never again.  "V scaled" implies "tiles landed" (the state warps waited for them), so the products wait
+      // for that one barrier only.
+      int n_data = 0;
+      auto data_ready = [&](int n) {
+        if (n < n_data) return true;
+        if (!ready(B_VRDY + stage_of(n_data), stage_ph(n_data))) return false;
+        ++n_data;
+        return n < n_data;
+      };
+      Patience patience{0, 0};
+      while (n_pv < NC) {
+        bool progress = false;
+        // intra-chunk term: ACC += P' Veta (FWD) | P' K (DQ); needs the state term of the same chunk issued before
+        if (n_pv < n_qs && ready(B_PRDY + n_pv % G::NP, (n_pv / G::NP) & 1)) {   // the state term has seen the data
+          const uint64_t so = (uint64_t)(stage_of(n_pv) * STAGE16);
+          FPB_TRACE(15, n_pv);
+          tc_fence_after();
+          const uint32_t acc = tm + G::TM_ACC + (n_pv % G::NACC) * G::NOUT;
+          const uint64_t a = d_p + (uint64_t)((n_pv % G::NP) * (G::P_BYTES >> 4));
+          const uint64_t bm = (MODE == MODE_FWD ? d_vm : d_km) + so;
 #pragma unroll
-        for (int ks = 0; ks < C / 16; ++ks)
-          umma_bf16(tm + G::TM_DS, mnmajor(stage_k(s), ks, 8192), mnmajor(stage_v(s), ks, 8192), ID_DS, ks > 0);
-        umma_commit(bar(B_DSFULL));
-        // 2. scores of the next chunk as soon as its tiles are there (never wait for them here)
-        bool sc_next = !has_next;
-        if (G::NSC == 2 && !sc_next) sc_next = issue_sc(c + 1, false) == 1;
-        // 3. state term: ACC = X Sb (FWD) | X Sb^T (DQ)
-        if (!mbar_wait(bar(B_SBRDY), c & 1, abort_flag)) { FPB_GIVE_UP(0x200 | B_SBRDY); break; }
-        FPB_TRACE(1, c);
-        if (!mbar_wait(bar(B_ACCFREE), (c & 1) ^ 1, abort_flag)) { FPB_GIVE_UP(0x200 | B_ACCFREE); break; }
-        FPB_TRACE(2, c);
-        tc_fence_after();
-        const uint32_t acc = tm + G::TM_ACC;
-        if (MODE == MODE_FWD) {
-#pragma unroll
-          for (int ks = 0; ks < R / 16; ++ks)
-            umma_bf16(acc, kmajor(stage_x(s), ks, 8192), mnmajor(sbase + G::OFF_SB, ks, R * 128), ID_STATE, ks > 0);
-        } else {
-#pragma unroll
-          for (int ks = 0; ks < CC / 16; ++ks)
-            umma_bf16(acc, kmajor(stage_x(s), ks, 8192), kmajor(sbase + G::OFF_SB, ks, R * 128), ID_STATE, ks > 0);
+          for (int ks = 0; ks < ((p.skip & 32) ? 0 : C / 16); ++ks) umma_bf16(acc, a + kstep(ks, 0), bm + mstep(ks), ID_INTRA, 1);
+          umma_commit(bar(B_ACCFULL + n_pv % G::NACC));
+          FPB_TRACE(3, n_pv);
+          ++n_pv; progress = true;
+          release();
         }
-        umma_commit(bar(B_SBFREE));      // Sb may be overwritten with the next state once this has run
-        if (G::NSC == 2 && !sc_next) sc_next = issue_sc(c + 1, false) == 1;
-        // 4. intra-chunk term: ACC += P' Veta (FWD) | P' K (DQ)
-        if (!mbar_wait(bar(B_PRDY), c & 1, abort_flag)) { FPB_GIVE_UP(0x200 | B_PRDY); break; }
-        FPB_TRACE(3, c);
-        tc_fence_after();
+        // state term: ACC = X Sb (FWD) | X Sb^T (DQ)
+        if (n_qs < NC && data_ready(n_qs) && (n_qs < G::NACC || ready(B_ACCFREE + n_qs % G::NACC, ((n_qs / G::NACC) & 1) ^ 1)) &&
+            ready(B_SBRDY, n_qs & 1)) {
+          const uint64_t so = (uint64_t)(stage_of(n_qs) * STAGE16);
+          FPB_TRACE(2, n_qs);
+          tc_fence_after();
+          const uint32_t acc = tm + G::TM_ACC + (n_qs % G::NACC) * G::NOUT;
+          if (MODE == MODE_FWD) {
 #pragma unroll
-        for (int ks = 0; ks < C / 16; ++ks)
-          umma_bf16(acc, kmajor(sbase + G::OFF_P, ks, 0), mnmajor(MODE == MODE_FWD ? stage_v(s) : stage_k(s), ks, 8192), ID_INTRA, 1);
-        umma_commit(bar(B_ACCFULL));
-        umma_commit(bar(B_EMPTY + s));   // every product that reads this stage has been issued
-        FPB_TRACE(5, c);
-        if (!has_next) break;
-        // with a single score buffer the next scores had to wait until P' of this chunk was taken out
-        if (!sc_next && issue_sc(c + 1, true) != 1) { FPB_GIVE_UP(0x200 | B_FULL); break; }
-        ck = nx; ++c;
+            for (int ks = 0; ks < ((p.skip & 32) ? 0 : R / 16); ++ks) umma_bf16(acc, d_x + so + kstep(ks, 8192), d_sb + mstep(ks), ID_STATE, ks > 0);
+          } else {
+#pragma unroll
+            for (int ks = 0; ks < CC / 16; ++ks) umma_bf16(acc, d_x + so + kstep(ks, 8192), d_sb + kstep(ks, R * 128), ID_STATE, ks > 0);
+          }
+          umma_commit(bar(B_SBFREE));    // Sb may be overwritten with the next state once this has run
+          FPB_TRACE(1, n_qs);
+          ++n_qs; progress = true;
+        }
+        // state increment dS = K^T Veta: depends on no other product and feeds the only chunk-to-chunk dependency
+        if (n_ds < NC && data_ready(n_ds) && (n_ds == 0 || ready(B_DSFREE, (n_ds & 1) ^ 1))) {
+          const uint64_t so = (uint64_t)(stage_of(n_ds) * STAGE16);
+          tc_fence_after();
+#pragma unroll
+          for (int ks = 0; ks < ((p.skip & 32) ? 0 : C / 16); ++ks) umma_bf16(tm + G::TM_DS, d_km + so + mstep(ks), d_vm + so + mstep(ks), ID_DS, ks > 0);
+          umma_commit(bar(B_DSFULL));
+          FPB_TRACE(4, n_ds);
+          ++n_ds; progress = true;
+          release();
+        }
+        // scores Sc = X K^T (FWD) | X Veta^T (DQ); its buffer is free once P' of chunk n - NSC has been taken out,
+        // which the intra-chunk term of that chunk has waited for
+        if (n_sc < NC && n_sc < n_pv + G::NSC && data_ready(n_sc)) {
+          const uint64_t so = (uint64_t)(stage_of(n_sc) * STAGE16);
+          tc_fence_after();
+          const uint32_t d = tm + G::TM_SC + (n_sc % G::NSC) * 64;
+          const uint64_t bk = (MODE == MODE_FWD ? d_kk : d_vk) + so;
+#pragma unroll
+          for (int ks = 0; ks < ((p.skip & 32) ? 0 : G::W1 / 16); ++ks) umma_bf16(d, d_x + so + kstep(ks, 8192), bk + kstep(ks, 8192), ID_SC, ks > 0);
+          umma_commit(bar(B_SCFULL + n_sc % G::NSC));
+          FPB_TRACE(0, n_sc);
+          ++n_sc; progress = true;
+        }
+        release();
+        if (progress) patience.progress();
+        else if (patience.exhausted(abort_flag)) { FPB_GIVE_UP(0x200 | (n_pv & 0xff)); break; }
       }
     }
   } else if (warp < STATE_WARP0) {                   // ---------------- score warps
@@ -308,97 +357,111 @@ scan_kernel(const __grid_constant__ ScanParams p) {
     const int r_lo = q4 * 16 + (lane >> 2);          // this thread's two accumulator rows: r_lo, r_lo + 8
     const int cpair = (lane & 3) * 2;
 
-    if (any) {
-      Chunk ck = first;
-      int c = 0;
-      while (true) {
-        Chunk nx = ck;
-        const bool has_next = advance<REV>(nx, p.T, p.block_size);
-        // ---- P' = causal side of Sc, times gamma^-L (and rs in forward walks)
-        bool fail = !mbar_wait(bar(B_SCFULL + (c % G::NSC)), (c / G::NSC) & 1, abort_flag);
-        if (fail) FPB_GIVE_UP(0x300 | B_SCFULL);
-        if (t == 0) FPB_TRACE(6, c);
-        if (!fail) {
-          tc_fence_after();
-          uint32_t r[32];
-          tmem_ld_16x256b_x8(tm + lane_base + G::TM_SC + (c % G::NSC) * 64, r);
-          tmem_wait_ld();
-          tc_fence_before();
-          const float cs = REV ? exp2f(-(float)ck.L * lg) : exp2f(-(float)ck.L * lg) * rs;
-          uint8_t* pt = sm + G::OFF_P;
+    // P'(n): causal side of Sc times gamma^-L (and rs in forward walks), bf16, swizzled K-major tile
+    auto make_p = [&](int n, int L) {
+      tc_fence_after();
+      uint32_t r[32];
+      if (!(p.skip & 16)) { tmem_ld_16x256b_x8(tm + lane_base + G::TM_SC + (n % G::NSC) * 64, r); tmem_wait_ld(); }
+      tc_fence_before();
+      const float cs = REV ? exp2f(-(float)L * lg) : exp2f(-(float)L * lg) * rs;
+      uint8_t* pt = sm + G::OFF_P + (n % G::NP) * G::P_BYTES;
 #pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            const int col = g * 8 + cpair;
-            auto keep = [&](int cc, int rr) { return REV ? cc >= rr : cc <= rr; };
-            const float a0 = keep(col, r_lo) ? __uint_as_float(r[4 * g]) * cs : 0.f;
-            const float a1 = keep(col + 1, r_lo) ? __uint_as_float(r[4 * g + 1]) * cs : 0.f;
-            const float b0 = keep(col, r_lo + 8) ? __uint_as_float(r[4 * g + 2]) * cs : 0.f;
-            const float b1 = keep(col + 1, r_lo + 8) ? __uint_as_float(r[4 * g + 3]) * cs : 0.f;
-            *reinterpret_cast<uint32_t*>(pt + r_lo * 128 + ((g ^ (r_lo & 7)) << 4) + cpair * 2) = pack_bf16(a0, a1);
-            *reinterpret_cast<uint32_t*>(pt + (r_lo + 8) * 128 + ((g ^ ((r_lo + 8) & 7)) << 4) + cpair * 2) = pack_bf16(b0, b1);
-          }
-          fence_async_smem();
-          mbar_arrive(bar(B_PRDY));
-          if (t == 0) FPB_TRACE(7, c);
-          // ---- epilogue: out_i = rowscale_i * ACC_i
-          fail = !mbar_wait(bar(B_ACCFULL), c & 1, abort_flag);
-          if (fail) FPB_GIVE_UP(0x300 | B_ACCFULL);
-          if (t == 0) FPB_TRACE(8, c);
+      for (int g = 0; g < ((p.skip & 8) ? 0 : 8); ++g) {
+        const int col = g * 8 + cpair;
+        auto keep = [&](int cc, int rr) { return REV ? cc >= rr : cc <= rr; };
+        const float a0 = keep(col, r_lo) ? __uint_as_float(r[4 * g]) * cs : 0.f;
+        const float a1 = keep(col + 1, r_lo) ? __uint_as_float(r[4 * g + 1]) * cs : 0.f;
+        const float b0 = keep(col, r_lo + 8) ? __uint_as_float(r[4 * g + 2]) * cs : 0.f;
+        const float b1 = keep(col + 1, r_lo + 8) ? __uint_as_float(r[4 * g + 3]) * cs : 0.f;
+        *reinterpret_cast<uint32_t*>(pt + r_lo * 128 + ((g ^ (r_lo & 7)) << 4) + cpair * 2) = pack_bf16(a0, a1);
+        *reinterpret_cast<uint32_t*>(pt + (r_lo + 8) * 128 + ((g ^ ((r_lo + 8) & 7)) << 4) + cpair * 2) = pack_bf16(b0, b1);
+      }
+      fence_async_smem();
+      mbar_arrive(bar(B_PRDY + n % G::NP));
+      if (t == 0) FPB_TRACE(7, n);
+    };
+
+    // E(n): out_i = rowscale_i * ACC_i -> staging tile -> TMA store.  `fail` makes all 128 threads leave
+    // together at the first barrier when some thread's polling gave up.  Returns false when leaving.
+    auto epilogue = [&](int n, Chunk ck, bool fail) -> bool {
+      // the previous TMA store must have finished reading the staging tile
+      if (t == 0) tma_store_wait_read0();
+      if (named_bar_or(1, N_SCORE, fail)) return false;
+      if (t == 0) FPB_TRACE(9, n);
+      tc_fence_after();
+      // row scale: zeta_i (forward walks) or eta_j * rs (reverse walks)
+      const float z_lo = REV ? exp2f((float)(ck.L - 1 - r_lo) * lg) * rs : exp2f((float)(r_lo + 1) * lg);
+      const float z_hi = REV ? exp2f((float)(ck.L - 9 - r_lo) * lg) * rs : exp2f((float)(r_lo + 9) * lg);
+      uint8_t* stg = sm + G::OFF_OUT;
+#pragma unroll
+      for (int half = 0; half < G::NOUT / 64; ++half) {
+        uint32_t r[32];
+        if (!(p.skip & 16)) { tmem_ld_16x256b_x8(tm + lane_base + G::TM_ACC + (n % G::NACC) * G::NOUT + half * 64, r); tmem_wait_ld(); }
+        if (half == G::NOUT / 64 - 1) { tc_fence_before(); mbar_arrive(bar(B_ACCFREE + n % G::NACC)); }
+        if (p.skip & 2) continue;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const uint32_t lo = pack_bf16(__uint_as_float(r[4 * g]) * z_lo, __uint_as_float(r[4 * g + 1]) * z_lo);
+          const uint32_t hi = pack_bf16(__uint_as_float(r[4 * g + 2]) * z_hi, __uint_as_float(r[4 * g + 3]) * z_hi);
+          *reinterpret_cast<uint32_t*>(stg + half * 8192 + r_lo * 128 + ((g ^ (r_lo & 7)) << 4) + cpair * 2) = lo;
+          *reinterpret_cast<uint32_t*>(stg + half * 8192 + (r_lo + 8) * 128 + ((g ^ ((r_lo + 8) & 7)) << 4) + cpair * 2) = hi;
         }
-        // the previous TMA store must have finished reading the staging tile; the barrier also makes
-        // "some thread gave up" uniform, so that all 128 threads leave together
-        if (t == 0) tma_store_wait_read0();
-        if (named_bar_or(1, N_SCORE, fail)) break;
-        if (t == 0) FPB_TRACE(9, c);
-        tc_fence_after();
-        // row scale: zeta_i (forward walks) or eta_j * rs (reverse walks)
-        const float z_lo = REV ? exp2f((float)(ck.L - 1 - r_lo) * lg) * rs : exp2f((float)(r_lo + 1) * lg);
-        const float z_hi = REV ? exp2f((float)(ck.L - 9 - r_lo) * lg) * rs : exp2f((float)(r_lo + 9) * lg);
-        uint8_t* stg = sm + G::OFF_OUT;
+      }
+      const bool whole_box = ck.L == C || ck.a + ck.L >= p.T;   // rows beyond L are past the sequence end: TMA clips them
+      if (whole_box) fence_async_smem();
+      named_bar_sync(2, N_SCORE);
+      const int ocol0 = MODE == MODE_FWD ? col0 : row0;
+      if (whole_box) {
+        if (t == 0 && !(p.skip & 2)) {
 #pragma unroll
-        for (int half = 0; half < G::NOUT / 64; ++half) {
-          uint32_t r[32];
-          tmem_ld_16x256b_x8(tm + lane_base + G::TM_ACC + half * 64, r);
-          tmem_wait_ld();
-          if (half == G::NOUT / 64 - 1) { tc_fence_before(); mbar_arrive(bar(B_ACCFREE)); }
-#pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            const uint32_t lo = pack_bf16(__uint_as_float(r[4 * g]) * z_lo, __uint_as_float(r[4 * g + 1]) * z_lo);
-            const uint32_t hi = pack_bf16(__uint_as_float(r[4 * g + 2]) * z_hi, __uint_as_float(r[4 * g + 3]) * z_hi);
-            *reinterpret_cast<uint32_t*>(stg + half * 8192 + r_lo * 128 + ((g ^ (r_lo & 7)) << 4) + cpair * 2) = lo;
-            *reinterpret_cast<uint32_t*>(stg + half * 8192 + (r_lo + 8) * 128 + ((g ^ ((r_lo + 8) & 7)) << 4) + cpair * 2) = hi;
-          }
+          for (int cb = 0; cb < G::NOUT / 64; ++cb) tma_store_4d(&p.map_out, sbase + G::OFF_OUT + cb * 8192, ocol0 + cb * 64, ck.a, h, b);
+          tma_store_commit();
         }
-        const bool whole_box = ck.L == C || ck.a + ck.L >= p.T;   // rows beyond L are past the sequence end: TMA clips them
-        if (whole_box) fence_async_smem();
-        named_bar_sync(2, N_SCORE);
-        const int ocol0 = MODE == MODE_FWD ? col0 : row0;
-        if (whole_box) {
-          if (t == 0) {
-#pragma unroll
-            for (int cb = 0; cb < G::NOUT / 64; ++cb) tma_store_4d(&p.map_out, sbase + G::OFF_OUT + cb * 8192, ocol0 + cb * 64, ck.a, h, b);
-            tma_store_commit();
-          }
-        } else {   // chunk cut short by a block end: rows >= L belong to another chunk, store rows < L only
-          bf16* go = p.out + (int64_t)b * p.out_sb + (int64_t)h * p.out_sh + ocol0;
-          for (int idx = t; idx < ck.L * (G::NOUT / 8); idx += N_SCORE) {
-            const int row = idx / (G::NOUT / 8), ch = idx % (G::NOUT / 8);
-            const uint4 val = *reinterpret_cast<const uint4*>(stg + (ch >> 3) * 8192 + row * 128 + (((ch & 7) ^ (row & 7)) << 4));
-            *reinterpret_cast<uint4*>(go + (int64_t)(ck.a + row) * p.out_st + ch * 8) = val;
-          }
-          // these generic reads of the staging tile are ordered before its next rewrite by the barrier at
-          // the top of the next epilogue
+      } else {   // chunk cut short by a block end: rows >= L belong to another chunk, store rows < L only
+        bf16* go = p.out + (int64_t)b * p.out_sb + (int64_t)h * p.out_sh + ocol0;
+        for (int idx = t; idx < ck.L * (G::NOUT / 8); idx += N_SCORE) {
+          const int row = idx / (G::NOUT / 8), ch = idx % (G::NOUT / 8);
+          const uint4 val = *reinterpret_cast<const uint4*>(stg + (ch >> 3) * 8192 + row * 128 + (((ch & 7) ^ (row & 7)) << 4));
+          *reinterpret_cast<uint4*>(go + (int64_t)(ck.a + row) * p.out_st + ch * 8) = val;
         }
-        if (t == 0) FPB_TRACE(10, c);
-        if (!has_next) break;
-        ck = nx; ++c;
+        // these generic reads of the staging tile are ordered before its next rewrite by the barrier at
+        // the top of the next epilogue
+      }
+      if (t == 0) FPB_TRACE(10, n);
+      return true;
+    };
+
+    if (NC > 0) {
+      // P' may run ahead of the epilogues by the number of P' buffers: buffer n % NP is free again once the
+      // intra-chunk product of chunk n - NP has run, which epilogue n - NP has waited for
+      int n_p = 0, n_e = 0;
+      Chunk ck_p = first, ck_e = first;
+      Patience patience{0, 0};
+      while (n_e < NC) {
+        if (n_p < NC && n_p < n_e + G::NP && mbar_test_wait(bar(B_SCFULL + n_p % G::NSC), (n_p / G::NSC) & 1)) {
+          if (t == 0) FPB_TRACE(6, n_p);
+          make_p(n_p, ck_p.L);
+          ++n_p; advance<REV>(ck_p, p.T, p.block_size);
+          patience.progress();
+        } else if (n_e < n_p && mbar_test_wait(bar(B_ACCFULL + n_e % G::NACC), (n_e / G::NACC) & 1)) {
+          if (t == 0) FPB_TRACE(8, n_e);
+          if (!epilogue(n_e, ck_e, false)) break;
+          ++n_e; advance<REV>(ck_e, p.T, p.block_size);
+          patience.progress();
+        } else if (patience.exhausted(abort_flag)) {
+          FPB_GIVE_UP(0x300 | (n_e & 0xff));
+          epilogue(n_e, ck_e, true);     // meet the others at the epilogue's first barrier and leave with them
+          break;
+        } else {
+          __nanosleep(40);               // idle: leave the issue slots to the warps that have work
+        }
       }
       if (t == 0) tma_store_wait_all0();
     }
   } else {                                           // ---------------- state warps
     const int t = tid - STATE_WARP0 * 32;            // 0..N_STATE-1
     const int q4 = warp & 3;
-    const int half = (warp - STATE_WARP0) >> 2;      // which slice of the CC state columns (BIG only)
+    const int half = (warp - STATE_WARP0) >> 2;      // which slice of the CC state columns
     const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
     const int wcol0 = half * G::WCOLS;
     float S[G::NS];
@@ -476,7 +539,8 @@ scan_kernel(const __grid_constant__ ScanParams p) {
     // pieces XOR-swizzled by (row & 7) — an MN-major B operand (FWD) or a K-major B operand (DQ).
     auto publish_sb = [&]() {
       uint8_t* sb = sm + G::OFF_SB;
-      if (R == 128) {
+      if (p.skip & 4) {
+      } else if (R == 128) {
         const int row = row_of(0);
 #pragma unroll
         for (int i = 0; i < G::NS; i += 8) {
@@ -499,13 +563,10 @@ scan_kernel(const __grid_constant__ ScanParams p) {
     };
     // in-place row scale of the V tile of chunk n: eta_j = gamma^(L-1-j) (forward walks) or
     // zeta_i = gamma^(i+1) (reverse walks, the tile holds dO); rows >= L are zeroed
-    // returns 1 = done, 0 = tiles not there yet (only with block == false), -1 = timed out
-    auto scale_v = [&](int n, int L, bool block) -> int {
-      const int s = n % G::STAGES;
-      if (!block) { if (!mbar_try_wait(bar(B_FULL + s), (n / G::STAGES) & 1)) return 0; }
-      else if (!mbar_wait(bar(B_FULL + s), (n / G::STAGES) & 1, abort_flag)) return -1;
+    auto scale_v = [&](int n, int L) {
+      const int s = stage_of(n);
       uint8_t* vt = sm + G::OFF_STAGE + s * G::STAGE_BYTES + G::X_BYTES + G::K_BYTES;
-      for (int idx = t; idx < C * CC / 8; idx += G::N_STATE) {
+      for (int idx = t; idx < ((p.skip & 1) ? 0 : C * CC / 8); idx += G::N_STATE) {
         const int row = (idx >> 3) & 63;
         uint4* ptr = reinterpret_cast<uint4*>(vt + idx * 16);
         uint4 val = make_uint4(0u, 0u, 0u, 0u);
@@ -523,7 +584,6 @@ scan_kernel(const __grid_constant__ ScanParams p) {
       }
       fence_async_smem();
       mbar_arrive(bar(B_VRDY + s));
-      return 1;
     };
 
     if (x_start) load_global(x_start, false);
@@ -532,47 +592,63 @@ scan_kernel(const __grid_constant__ ScanParams p) {
       for (int i = 0; i < G::NS; ++i) S[i] = 0.f;
     }
     const float ds_scale = REV ? 1.0f : rs;   // forward: S += rs K^T Veta;  reverse: G += Q^T (zeta.dO)
-    if (any) {
-      bool ok = scale_v(0, first.L, true) == 1;
-      if (!ok) FPB_GIVE_UP(0x400 | B_FULL);
+    if (NC > 0) {
+      // three tasks, each in chunk order, run as their inputs arrive:
+      //   V(n)  scale the V tile of chunk n                         (needs the tiles of chunk n)
+      //   U(n)  S <- gamma^L S + dS(n)                              (needs the increment of chunk n)
+      //   Sb(n) publish the bf16 copy of the state at the start of chunk n; it must happen between U(n-1) and U(n),
+      //         and after the state-term product of chunk n-1 has finished reading the previous copy
+      int n_v = 0, n_u = 0;
+      bool publish_due = true;
+      Chunk ck_v = first, ck_u = first;
       inject(first.a + first.L);
-      publish_sb();
-      Chunk ck = first;
-      int c = 0;
-      while (ok) {
-        Chunk nx = ck;
-        const bool has_next = advance<REV>(nx, p.T, p.block_size);
-        if (t == 0) FPB_TRACE(15, c);
-        // scale the next chunk's V now if its tiles have landed; otherwise after this chunk's state work
-        bool v_next = !has_next || scale_v(c + 1, nx.L, false) == 1;
-        if (t == 0) FPB_TRACE(11, c);
-        if (!mbar_wait(bar(B_DSFULL), c & 1, abort_flag)) { FPB_GIVE_UP(0x400 | B_DSFULL); break; }
-        if (t == 0) FPB_TRACE(12, c);
-        tc_fence_after();
-        const float gl = exp2f((float)ck.L * lg);
-        // 16 registers at a time keeps the state warps inside the register budget of two CTAs per SM
-#pragma unroll
-        for (int i0 = 0; i0 < G::NS; i0 += 16) {
-          uint32_t r[16];
-          if (R == 128) tmem_ld_32x32b_x16(tm + lane_base + G::TM_DS + wcol0 + i0, r);
-          else tmem_ld_16x256b_x4(tm + lane_base + G::TM_DS + wcol0 + i0 * 2, r);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) S[i0 + i] = fmaf(gl, S[i0 + i], ds_scale * __uint_as_float(r[i]));
+      Patience patience{0, 0};
+      while (n_u < NC) {
+        bool progress = false;
+        if (n_v < NC && mbar_test_wait(bar(B_FULL + stage_of(n_v)), stage_ph(n_v))) {
+          scale_v(n_v, ck_v.L);
+          if (t == 0) FPB_TRACE(11, n_v);
+          ++n_v; advance<REV>(ck_v, p.T, p.block_size);
+          progress = true;
         }
-        tc_fence_before();
-        mbar_arrive(bar(B_DSFREE));          // the increment has been read: the next one may overwrite it
-        const int end = ck.a + ck.L;
-        if (!REV && p.block_size > 0 && p.block_states && end % p.block_size == 0 && end / p.block_size - 1 < p.n_blocks)
-          store_global(p.block_states + (((int64_t)b * p.n_blocks + (end / p.block_size - 1)) * p.H + h) * state_elems);
-        if (!has_next) break;
-        inject(nx.a + nx.L);
-        // Sb still holds this chunk's start state until the state-term product that reads it has run
-        if (!mbar_wait(bar(B_SBFREE), c & 1, abort_flag)) { FPB_GIVE_UP(0x400 | B_SBFREE); break; }
-        publish_sb();
-        if (t == 0) FPB_TRACE(13, c);
-        if (!v_next && scale_v(c + 1, nx.L, true) != 1) { FPB_GIVE_UP(0x400 | B_FULL); break; }
-        ck = nx; ++c;
+        if (publish_due) {
+          if (n_u == 0 || mbar_test_wait(bar(B_SBFREE), (n_u - 1) & 1)) {
+            publish_sb();
+            if (t == 0) FPB_TRACE(13, n_u);
+            publish_due = false; progress = true;
+          }
+        } else if (mbar_test_wait(bar(B_DSFULL), n_u & 1)) {
+          if (t == 0) FPB_TRACE(12, n_u);
+          tc_fence_after();
+          const float gl = exp2f((float)ck_u.L * lg);
+          // 16 registers at a time keeps the state warps inside the register budget
+#pragma unroll
+          for (int i0 = 0; i0 < G::NS; i0 += 16) {
+            uint32_t r[16];
+            if (!(p.skip & 16)) {
+              if (R == 128) tmem_ld_32x32b_x16(tm + lane_base + G::TM_DS + wcol0 + i0, r);
+              else tmem_ld_16x256b_x4(tm + lane_base + G::TM_DS + wcol0 + i0 * 2, r);
+              tmem_wait_ld();
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) S[i0 + i] = fmaf(gl, S[i0 + i], ds_scale * __uint_as_float(r[i]));
+          }
+          tc_fence_before();
+          mbar_arrive(bar(B_DSFREE));        // the increment has been read: the next one may overwrite it
+          const int end = ck_u.a + ck_u.L;
+          if (!REV && p.block_size > 0 && p.block_states && end % p.block_size == 0 && end / p.block_size - 1 < p.n_blocks)
+            store_global(p.block_states + (((int64_t)b * p.n_blocks + (end / p.block_size - 1)) * p.H + h) * state_elems);
+          ++n_u;
+          if (n_u < NC) {
+            advance<REV>(ck_u, p.T, p.block_size);
+            inject(ck_u.a + ck_u.L);
+            publish_due = true;
+          }
+          progress = true;
+        }
+        if (progress) patience.progress();
+        else if (patience.exhausted(abort_flag)) { FPB_GIVE_UP(0x400 | (n_u & 0xff)); break; }
+        else __nanosleep(40);            // idle: leave the issue slots to the warps that have work
       }
     }
     if (x_end && !*abort_flag) store_global(x_end);
@@ -603,7 +679,9 @@ int launch_scan(const ScanParams& p, bool rev, dim3 grid, cudaStream_t stream) {
   return rev ? launch_scan_t<MODE, 1, R, CC>(p, grid, stream) : launch_scan_t<MODE, 0, R, CC>(p, grid, stream);
 }
 
+int g_tile_pref = 1;            // 1: 128x128 state tiles where they apply; 0: 64-wide tiles (two CTAs per SM)
 long long* g_trace = nullptr;   // set by fpb_debug_trace
+int g_skip = 0;                 // set by fpb_debug_skip
 
 bool aligned_state(const StateView& s) { return !s.data || ((uintptr_t)s.data % 16 == 0 && s.sb % 8 == 0 && s.sh % 8 == 0); }
 
@@ -649,14 +727,17 @@ int launch_pass(const PassArgs& a, cudaStream_t stream) {
   p.T = T; p.H = H; p.dk = dk; p.dv = dv; p.block_size = a.block_size; p.n_blocks = a.n_blocks;
   p.status = device_status_ptr();
   p.trace = g_trace;
+  p.skip = g_skip;
   if (!p.status) return FPB_ERR_LAUNCH;
   for (int h = 0; h < H; ++h) p.log2g[h] = (float)std::log2((double)a.gamma[h]);
 
 #define FPB_SCAN_CASE(MODE_, R_, CC_, TILES_) return launch_scan<MODE_, R_, CC_>(p, a.rev, dim3((TILES_), H, B), stream)
-  if (a.mode == MODE_FWD) {       // state tile: all dk rows x 64 columns of dv
+  if (a.mode == MODE_FWD) {       // state tile: all dk rows x CC columns of dv
+    if (dk == 128 && dv % 128 == 0 && g_tile_pref) FPB_SCAN_CASE(MODE_FWD, 128, 128, dv / 128);
     if (dk == 128) FPB_SCAN_CASE(MODE_FWD, 128, 64, dv / 64);
     if (dk == 64) FPB_SCAN_CASE(MODE_FWD, 64, 64, dv / 64);
-  } else {                        // state tile: 64 rows of dk x all dv columns
+  } else {                        // state tile: R rows of dk x all dv columns
+    if (dv == 128 && dk % 128 == 0 && g_tile_pref) FPB_SCAN_CASE(MODE_DQ, 128, 128, dk / 128);
     if (dv == 64) FPB_SCAN_CASE(MODE_DQ, 64, 64, dk / 64);
     if (dv == 128) FPB_SCAN_CASE(MODE_DQ, 64, 128, dk / 64);
     if (dv == 256) FPB_SCAN_CASE(MODE_DQ, 64, 256, dk / 64);
@@ -670,6 +751,11 @@ int launch_pass(const PassArgs& a, cudaStream_t stream) {
 // Diagnostics hook (not part of the public header): install a device buffer of 64*16 int64 that the next
 // launches fill with clock64() stamps of their first CTA; null removes it.
 extern "C" void fpb_debug_trace(void* device_buffer) { g_trace = (long long*)device_buffer; }
+// Diagnostics hook: choose between the 128x128 state tiles (1, default) and the 64-wide ones (0).
+extern "C" void fpb_debug_tile_pref(int wide) { g_tile_pref = wide; }
+// Diagnostics hook for timing experiments: leave out parts of the work (1 V scaling, 2 output staging/store,
+// 4 state copy, 8 P' writes).  Results are wrong while any bit is set.
+extern "C" void fpb_debug_skip(int mask) { g_skip = mask; }
 
 int launch_umma_fwd(const UmmaFwdArgs& a, cudaStream_t stream) {
   if (a.dtype != FPB_BF16) return FPB_UMMA_NOT_APPLICABLE;
