@@ -241,7 +241,10 @@ scan_kernel(const __grid_constant__ ScanParams p) {
       }
     }
   } else if (warp == 1) {                            // ---------------- MMA issuer
-    if (lane == 0 && NC > 0) {
+    // The whole warp runs this loop with warp-uniform control flow and data (barrier tests are made uniform by a
+    // vote), so that descriptors and counters stay in the uniform datapath; one elected lane issues.
+    if (NC > 0) {
+      const bool leader = elect_one();
       constexpr uint32_t ID_SC = idesc_bf16(64, 64, 0, 0);
       constexpr uint32_t ID_STATE = MODE == MODE_FWD ? idesc_bf16(64, CC, 0, 1) : idesc_bf16(64, R, 0, 0);
       constexpr uint32_t ID_INTRA = idesc_bf16(64, G::NOUT, 0, 1);
@@ -261,7 +264,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
       const uint64_t d_p = smem_desc(sbase + G::OFF_P, 16, 1024);                                       // P', K-major
       auto kstep = [](int ks, uint32_t cb_stride) { return (uint64_t)((ks >> 2) * (cb_stride >> 4) + (ks & 3) * 2); };
       auto mstep = [](int ks) { return (uint64_t)(ks * 128); };
-      auto ready = [&](int slot, uint32_t parity) { return mbar_test_wait(bar(slot), parity); };
+      auto ready = [&](int slot, uint32_t parity) { return __all_sync(0xffffffffu, mbar_test_wait(bar(slot), parity)) != 0; };
       // Next chunk to issue for each of the four products, and the next stage to hand back to the producer.
       // Each product of chunk n is issued when its inputs are there; the tensor pipe runs them in issue order.
       int n_sc = 0, n_ds = 0, n_qs = 0, n_pv = 0, n_rel = 0;
@@ -269,8 +272,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
       // blocks while the tensor pipe is busy, so this is checked after every group, not once per round)
       auto release = [&]() {
         while (n_rel < n_pv && n_rel < n_ds && n_rel < n_sc) {
-          umma_commit(bar(B_EMPTY + stage_of(n_rel)));
-          FPB_TRACE(5, n_rel);
+          if (leader) { umma_commit(bar(B_EMPTY + stage_of(n_rel))); FPB_TRACE(5, n_rel); }
           ++n_rel;
         }
       };
@@ -291,15 +293,17 @@ scan_kernel(const __grid_constant__ ScanParams p) {
         // intra-chunk term: ACC += P' Veta (FWD) | P' K (DQ); needs the state term of the same chunk issued before
         if (n_pv < n_qs && ready(B_PRDY + n_pv % G::NP, (n_pv / G::NP) & 1)) {   // the state term has seen the data
           const uint64_t so = (uint64_t)(stage_of(n_pv) * STAGE16);
-          FPB_TRACE(15, n_pv);
+          if (leader) FPB_TRACE(15, n_pv);
           tc_fence_after();
           const uint32_t acc = tm + G::TM_ACC + (n_pv % G::NACC) * G::NOUT;
           const uint64_t a = d_p + (uint64_t)((n_pv % G::NP) * (G::P_BYTES >> 4));
           const uint64_t bm = (MODE == MODE_FWD ? d_vm : d_km) + so;
+          if (leader) {
 #pragma unroll
-          for (int ks = 0; ks < ((p.skip & 32) ? 0 : C / 16); ++ks) umma_bf16(acc, a + kstep(ks, 0), bm + mstep(ks), ID_INTRA, 1);
-          umma_commit(bar(B_ACCFULL + n_pv % G::NACC));
-          FPB_TRACE(3, n_pv);
+            for (int ks = 0; ks < ((p.skip & 32) ? 0 : C / 16); ++ks) umma_bf16(acc, a + kstep(ks, 0), bm + mstep(ks), ID_INTRA, 1);
+            umma_commit(bar(B_ACCFULL + n_pv % G::NACC));
+            FPB_TRACE(3, n_pv);
+          }
           ++n_pv; progress = true;
           release();
         }
@@ -307,28 +311,32 @@ scan_kernel(const __grid_constant__ ScanParams p) {
         if (n_qs < NC && data_ready(n_qs) && (n_qs < G::NACC || ready(B_ACCFREE + n_qs % G::NACC, ((n_qs / G::NACC) & 1) ^ 1)) &&
             ready(B_SBRDY, n_qs & 1)) {
           const uint64_t so = (uint64_t)(stage_of(n_qs) * STAGE16);
-          FPB_TRACE(2, n_qs);
+          if (leader) FPB_TRACE(2, n_qs);
           tc_fence_after();
           const uint32_t acc = tm + G::TM_ACC + (n_qs % G::NACC) * G::NOUT;
-          if (MODE == MODE_FWD) {
+          if (leader) {
+            if (MODE == MODE_FWD) {
 #pragma unroll
-            for (int ks = 0; ks < ((p.skip & 32) ? 0 : R / 16); ++ks) umma_bf16(acc, d_x + so + kstep(ks, 8192), d_sb + mstep(ks), ID_STATE, ks > 0);
-          } else {
+              for (int ks = 0; ks < ((p.skip & 32) ? 0 : R / 16); ++ks) umma_bf16(acc, d_x + so + kstep(ks, 8192), d_sb + mstep(ks), ID_STATE, ks > 0);
+            } else {
 #pragma unroll
-            for (int ks = 0; ks < CC / 16; ++ks) umma_bf16(acc, d_x + so + kstep(ks, 8192), d_sb + kstep(ks, R * 128), ID_STATE, ks > 0);
+              for (int ks = 0; ks < CC / 16; ++ks) umma_bf16(acc, d_x + so + kstep(ks, 8192), d_sb + kstep(ks, R * 128), ID_STATE, ks > 0);
+            }
+            umma_commit(bar(B_SBFREE));    // Sb may be overwritten with the next state once this has run
+            FPB_TRACE(1, n_qs);
           }
-          umma_commit(bar(B_SBFREE));    // Sb may be overwritten with the next state once this has run
-          FPB_TRACE(1, n_qs);
           ++n_qs; progress = true;
         }
         // state increment dS = K^T Veta: depends on no other product and feeds the only chunk-to-chunk dependency
         if (n_ds < NC && data_ready(n_ds) && (n_ds == 0 || ready(B_DSFREE, (n_ds & 1) ^ 1))) {
           const uint64_t so = (uint64_t)(stage_of(n_ds) * STAGE16);
           tc_fence_after();
+          if (leader) {
 #pragma unroll
-          for (int ks = 0; ks < ((p.skip & 32) ? 0 : C / 16); ++ks) umma_bf16(tm + G::TM_DS, d_km + so + mstep(ks), d_vm + so + mstep(ks), ID_DS, ks > 0);
-          umma_commit(bar(B_DSFULL));
-          FPB_TRACE(4, n_ds);
+            for (int ks = 0; ks < ((p.skip & 32) ? 0 : C / 16); ++ks) umma_bf16(tm + G::TM_DS, d_km + so + mstep(ks), d_vm + so + mstep(ks), ID_DS, ks > 0);
+            umma_commit(bar(B_DSFULL));
+            FPB_TRACE(4, n_ds);
+          }
           ++n_ds; progress = true;
           release();
         }
@@ -339,15 +347,17 @@ scan_kernel(const __grid_constant__ ScanParams p) {
           tc_fence_after();
           const uint32_t d = tm + G::TM_SC + (n_sc % G::NSC) * 64;
           const uint64_t bk = (MODE == MODE_FWD ? d_kk : d_vk) + so;
+          if (leader) {
 #pragma unroll
-          for (int ks = 0; ks < ((p.skip & 32) ? 0 : G::W1 / 16); ++ks) umma_bf16(d, d_x + so + kstep(ks, 8192), bk + kstep(ks, 8192), ID_SC, ks > 0);
-          umma_commit(bar(B_SCFULL + n_sc % G::NSC));
-          FPB_TRACE(0, n_sc);
+            for (int ks = 0; ks < ((p.skip & 32) ? 0 : G::W1 / 16); ++ks) umma_bf16(d, d_x + so + kstep(ks, 8192), bk + kstep(ks, 8192), ID_SC, ks > 0);
+            umma_commit(bar(B_SCFULL + n_sc % G::NSC));
+            FPB_TRACE(0, n_sc);
+          }
           ++n_sc; progress = true;
         }
         release();
         if (progress) patience.progress();
-        else if (patience.exhausted(abort_flag)) { FPB_GIVE_UP(0x200 | (n_pv & 0xff)); break; }
+        else if (__any_sync(0xffffffffu, patience.exhausted(abort_flag))) { if (leader) FPB_GIVE_UP(0x200 | (n_pv & 0xff)); break; }
       }
     }
   } else if (warp < STATE_WARP0) {                   // ---------------- score warps
@@ -453,7 +463,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
           epilogue(n_e, ck_e, true);     // meet the others at the epilogue's first barrier and leave with them
           break;
         } else {
-          __nanosleep(40);               // idle: leave the issue slots to the warps that have work
+          __nanosleep(20);               // idle: leave the issue slots to the warps that have work
         }
       }
       if (t == 0) tma_store_wait_all0();
@@ -648,7 +658,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
         }
         if (progress) patience.progress();
         else if (patience.exhausted(abort_flag)) { FPB_GIVE_UP(0x400 | (n_u & 0xff)); break; }
-        else __nanosleep(40);            // idle: leave the issue slots to the warps that have work
+        else __nanosleep(20);            // idle: leave the issue slots to the warps that have work
       }
     }
     if (x_end && !*abort_flag) store_global(x_end);
