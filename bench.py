@@ -291,11 +291,12 @@ def main():
             peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
             peak_src = "fallback"
         value = total_flop / (ms * 1e-3) / 1e12
-        # the backward takes the larger share of a step: it is the dominant launch group
-        dom_bytes, dom_ms, dom_name = (bb * units, ms_bwd, "backward (dK/dV/dS + dQ kernels)")
-        if ms_fwd > ms_bwd:
-            dom_bytes, dom_ms, dom_name = (bf * units, ms_fwd, "forward kernel")
-        achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
+        # Top kernel of the launch list (profiles/scan_kernel_ns_launch_list.md): the forward scan launch; its
+        # duration is the CUDA-event time of forward-only calls (one launch each).  DRAM traffic per launch from the
+        # ncu capture in profiles/scan_kernel_forward_small_full.md (workload "ns" only).
+        fwd_traffic = {"ns": 806.8e6 + 248.7e6}.get(args.workload)
+        achieved = bf * units / (ms_fwd * 1e-3) / 1e9
+        step_gbs = (bf + bb) * units / (ms * 1e-3) / 1e9
         line = {
             "metric": "chunked_retention_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
@@ -308,8 +309,12 @@ def main():
             "path": {1: "cuda-core", 2: "tcgen05"}.get(path, "none"),
             "config": {"workload": workload_name(args, w), "l2": "inputs (1 GB+) larger than the 126 MB L2; no flush",
                        "flop_count": "algorithmic, causal half of intra-chunk tiles (C=64)"},
-            "roofline": {"bound": "hbm", "kernel": dom_name, "achieved": achieved, "peak": peaks["hbm_gbs"],
-                         "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peak_src, "traffic": None},
+            "roofline": {"bound": "hbm", "kernel": "scan_kernel<MODE_FWD, forward> (one launch per step, largest share)",
+                         "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                         "peak_source": peak_src, "traffic": fwd_traffic, "algorithmic_bytes": bf * units},
+            "roofline_step": {"bound": "hbm", "kernels": "all four scan launches of a step", "achieved": step_gbs,
+                              "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": step_gbs / peaks["hbm_gbs"],
+                              "algorithmic_bytes": (bf + bb) * units},
             "clocks": clocks,
             "gpu_launches": launches,
         }
