@@ -51,6 +51,21 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// try_wait with a suspend-time hint (nanoseconds): the thread may sleep in hardware until the phase completes or
+// about `ns` have passed, whichever comes first.  For the idle branch of a polling loop: wake at once on the
+// barrier most likely to complete next, without missing the others for long.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Every wait in the kernels is bounded: after about a second of spinning (or as soon as another
 // thread of the CTA has given up, *abort_flag != 0) the wait returns false, and the caller records
 // which wait it was and leaves its loop.

@@ -71,7 +71,7 @@ struct ScanParams {
 
 // barrier slots (8 bytes each) at the start of the barrier page, then two 4-byte words
 enum { B_FULL = 0, B_EMPTY = 3, B_VRDY = 6, B_SCFULL = 9, B_PRDY = 11, B_ACCFULL = 13, B_ACCFREE = 15, B_DSFULL = 17,
-       B_DSFREE = 18, B_SBRDY = 19, B_SBFREE = 20, B_COUNT = 21 };
+       B_DSFREE = 19, B_SBRDY = 21, B_SBFREE = 22, B_COUNT = 23 };
 constexpr int OFF_TMEM_SLOT = B_COUNT * 8, OFF_ABORT = OFF_TMEM_SLOT + 4, BAR_PAGE = 256;
 
 template <int MODE, int R, int CC>
@@ -85,7 +85,6 @@ struct Cfg {
   static constexpr int NTHREADS = STATE_WARP0 * 32 + N_STATE;
   static constexpr int MIN_CTAS = ONE ? 1 : 2;
   static constexpr int NP = ONE ? 2 : 1;                     // P' buffers
-  static constexpr int NACC = ONE ? 2 : 1;                   // accumulator buffers
   static constexpr int X_BYTES = C * W1 * 2, K_BYTES = C * R * 2, V_BYTES = C * CC * 2;
   static constexpr int STAGE_BYTES = X_BYTES + K_BYTES + V_BYTES;
   static constexpr int P_BYTES = C * C * 2;
@@ -101,11 +100,17 @@ struct Cfg {
   static constexpr int OFF_BAR = OFF_OUT + OUT_BYTES;
   static constexpr int SMEM = OFF_BAR + BAR_PAGE;
   static_assert(SMEM <= SMEM_LIMIT, "shared memory budget");
-  // tensor-memory columns: score tile(s), accumulator(s), the state increment
-  static constexpr int TM_COLS = ONE ? 512 : 256;
-  static constexpr int NSC = (2 * 64 + NACC * NOUT + CC <= TM_COLS) ? 2 : 1;
-  static constexpr int TM_SC = 0, TM_ACC = 64 * NSC, TM_DS = TM_ACC + NACC * NOUT;
-  static_assert(TM_DS + CC <= TM_COLS, "tensor memory budget");
+  // Tensor memory.  An M = 64 accumulator occupies lanes 0-15 of each 32-lane sub-partition, so two of them share
+  // the same columns (second one at lane offset 16): both score tiles in 64 columns, both accumulators in NOUT
+  // columns.  The state increment is double-buffered too: in lanes when R == 64, in columns when R == 128.
+  static constexpr int NSC = 2;
+  static constexpr int NACC = 2;
+  static constexpr int TM_SC = 0, TM_ACC = 64, TM_DS = 64 + NOUT;
+  static constexpr int DS_COLS = R == 128 ? 2 * CC : CC;
+  static constexpr int TM_USED = TM_DS + DS_COLS;
+  static constexpr int TM_COLS = TM_USED <= 256 ? 256 : 512;
+  static_assert(TM_USED <= 512, "tensor memory budget");
+  static_assert(ONE || TM_COLS == 256, "two CTAs per SM need at most 256 columns each");
   // state registers per state-warp thread; NHALF warps share one tensor-memory sub-partition
   static constexpr int NHALF = STATE_WARPS / 4;
   static constexpr int WCOLS = CC / NHALF;                   // state columns handled by one warp
@@ -190,6 +195,10 @@ scan_kernel(const __grid_constant__ ScanParams p) {
   auto bar = [&](int slot) { return sbase + G::OFF_BAR + slot * 8; };
   auto stage_of = [&](int n) { return n % G::STAGES; };
   auto stage_ph = [&](int n) { return (uint32_t)((n / G::STAGES) & 1); };
+  // tensor-memory address (lane offset in the upper half-word) of buffer n & 1 of each accumulator kind
+  auto tm_sc = [&](int n) { return (uint32_t)(G::TM_SC + ((n & 1) ? (16u << 16) : 0u)); };
+  auto tm_acc = [&](int n) { return (uint32_t)(G::TM_ACC + ((n & 1) ? (16u << 16) : 0u)); };
+  auto tm_ds = [&](int n) { return R == 128 ? (uint32_t)(G::TM_DS + (n & 1) * CC) : (uint32_t)(G::TM_DS + ((n & 1) ? (16u << 16) : 0u)); };
 
   if (tid == 0) {
     for (int s = 0; s < 3; ++s) { mbar_init(bar(B_FULL + s), 1); mbar_init(bar(B_EMPTY + s), 1); mbar_init(bar(B_VRDY + s), G::N_STATE); }
@@ -197,7 +206,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
       mbar_init(bar(B_SCFULL + j), 1); mbar_init(bar(B_PRDY + j), N_SCORE);
       mbar_init(bar(B_ACCFULL + j), 1); mbar_init(bar(B_ACCFREE + j), N_SCORE);
     }
-    mbar_init(bar(B_DSFULL), 1); mbar_init(bar(B_DSFREE), G::N_STATE);
+    for (int j = 0; j < 2; ++j) { mbar_init(bar(B_DSFULL + j), 1); mbar_init(bar(B_DSFREE + j), G::N_STATE); }
     mbar_init(bar(B_SBRDY), G::N_STATE); mbar_init(bar(B_SBFREE), 1);
     fence_mbar_init();
     *abort_flag = 0;
@@ -288,23 +297,36 @@ scan_kernel(const __grid_constant__ ScanParams p) {
         return n < n_data;
       };
       Patience patience{0, 0};
-      while (n_pv < NC) {
+      while (n_rel < NC) {             // until every product of every chunk has been issued
         bool progress = false;
-        // intra-chunk term: ACC += P' Veta (FWD) | P' K (DQ); needs the state term of the same chunk issued before
-        if (n_pv < n_qs && ready(B_PRDY + n_pv % G::NP, (n_pv / G::NP) & 1)) {   // the state term has seen the data
-          const uint64_t so = (uint64_t)(stage_of(n_pv) * STAGE16);
-          if (leader) FPB_TRACE(15, n_pv);
+        // Order of the tests = priority: the products that feed the longest chains first (scores -> P' -> intra term;
+        // increment -> state -> next chunk's state term).
+        // scores Sc = X K^T (FWD) | X Veta^T (DQ); its buffer is free once P' of chunk n - NSC has been taken out,
+        // which the intra-chunk term of that chunk has waited for
+        if (n_sc < NC && n_sc < n_pv + G::NSC && data_ready(n_sc)) {
+          const uint64_t so = (uint64_t)(stage_of(n_sc) * STAGE16);
           tc_fence_after();
-          const uint32_t acc = tm + G::TM_ACC + (n_pv % G::NACC) * G::NOUT;
-          const uint64_t a = d_p + (uint64_t)((n_pv % G::NP) * (G::P_BYTES >> 4));
-          const uint64_t bm = (MODE == MODE_FWD ? d_vm : d_km) + so;
+          const uint32_t d = tm + tm_sc(n_sc);
+          const uint64_t bk = (MODE == MODE_FWD ? d_kk : d_vk) + so;
           if (leader) {
 #pragma unroll
-            for (int ks = 0; ks < ((p.skip & 32) ? 0 : C / 16); ++ks) umma_bf16(acc, a + kstep(ks, 0), bm + mstep(ks), ID_INTRA, 1);
-            umma_commit(bar(B_ACCFULL + n_pv % G::NACC));
-            FPB_TRACE(3, n_pv);
+            for (int ks = 0; ks < ((p.skip & 32) ? 0 : G::W1 / 16); ++ks) umma_bf16(d, d_x + so + kstep(ks, 8192), bk + kstep(ks, 8192), ID_SC, ks > 0);
+            umma_commit(bar(B_SCFULL + n_sc % G::NSC));
+            FPB_TRACE(0, n_sc);
           }
-          ++n_pv; progress = true;
+          ++n_sc; progress = true;
+        }
+        // state increment dS = K^T Veta: depends on no other product and feeds the only chunk-to-chunk dependency
+        if (n_ds < NC && data_ready(n_ds) && (n_ds < 2 || ready(B_DSFREE + (n_ds & 1), ((n_ds >> 1) & 1) ^ 1))) {
+          const uint64_t so = (uint64_t)(stage_of(n_ds) * STAGE16);
+          tc_fence_after();
+          if (leader) {
+#pragma unroll
+            for (int ks = 0; ks < ((p.skip & 32) ? 0 : C / 16); ++ks) umma_bf16(tm + tm_ds(n_ds), d_km + so + mstep(ks), d_vm + so + mstep(ks), ID_DS, ks > 0);
+            umma_commit(bar(B_DSFULL + (n_ds & 1)));
+            FPB_TRACE(4, n_ds);
+          }
+          ++n_ds; progress = true;
           release();
         }
         // state term: ACC = X Sb (FWD) | X Sb^T (DQ)
@@ -313,7 +335,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
           const uint64_t so = (uint64_t)(stage_of(n_qs) * STAGE16);
           if (leader) FPB_TRACE(2, n_qs);
           tc_fence_after();
-          const uint32_t acc = tm + G::TM_ACC + (n_qs % G::NACC) * G::NOUT;
+          const uint32_t acc = tm + tm_acc(n_qs);
           if (leader) {
             if (MODE == MODE_FWD) {
 #pragma unroll
@@ -327,33 +349,22 @@ scan_kernel(const __grid_constant__ ScanParams p) {
           }
           ++n_qs; progress = true;
         }
-        // state increment dS = K^T Veta: depends on no other product and feeds the only chunk-to-chunk dependency
-        if (n_ds < NC && data_ready(n_ds) && (n_ds == 0 || ready(B_DSFREE, (n_ds & 1) ^ 1))) {
-          const uint64_t so = (uint64_t)(stage_of(n_ds) * STAGE16);
+        // intra-chunk term: ACC += P' Veta (FWD) | P' K (DQ); needs the state term of the same chunk issued before
+        if (n_pv < n_qs && ready(B_PRDY + n_pv % G::NP, (n_pv / G::NP) & 1)) {   // the state term has seen the data
+          const uint64_t so = (uint64_t)(stage_of(n_pv) * STAGE16);
+          if (leader) FPB_TRACE(15, n_pv);
           tc_fence_after();
+          const uint32_t acc = tm + tm_acc(n_pv);
+          const uint64_t a = d_p + (uint64_t)((n_pv % G::NP) * (G::P_BYTES >> 4));
+          const uint64_t bm = (MODE == MODE_FWD ? d_vm : d_km) + so;
           if (leader) {
 #pragma unroll
-            for (int ks = 0; ks < ((p.skip & 32) ? 0 : C / 16); ++ks) umma_bf16(tm + G::TM_DS, d_km + so + mstep(ks), d_vm + so + mstep(ks), ID_DS, ks > 0);
-            umma_commit(bar(B_DSFULL));
-            FPB_TRACE(4, n_ds);
+            for (int ks = 0; ks < ((p.skip & 32) ? 0 : C / 16); ++ks) umma_bf16(acc, a + kstep(ks, 0), bm + mstep(ks), ID_INTRA, 1);
+            umma_commit(bar(B_ACCFULL + n_pv % G::NACC));
+            FPB_TRACE(3, n_pv);
           }
-          ++n_ds; progress = true;
+          ++n_pv; progress = true;
           release();
-        }
-        // scores Sc = X K^T (FWD) | X Veta^T (DQ); its buffer is free once P' of chunk n - NSC has been taken out,
-        // which the intra-chunk term of that chunk has waited for
-        if (n_sc < NC && n_sc < n_pv + G::NSC && data_ready(n_sc)) {
-          const uint64_t so = (uint64_t)(stage_of(n_sc) * STAGE16);
-          tc_fence_after();
-          const uint32_t d = tm + G::TM_SC + (n_sc % G::NSC) * 64;
-          const uint64_t bk = (MODE == MODE_FWD ? d_kk : d_vk) + so;
-          if (leader) {
-#pragma unroll
-            for (int ks = 0; ks < ((p.skip & 32) ? 0 : G::W1 / 16); ++ks) umma_bf16(d, d_x + so + kstep(ks, 8192), bk + kstep(ks, 8192), ID_SC, ks > 0);
-            umma_commit(bar(B_SCFULL + n_sc % G::NSC));
-            FPB_TRACE(0, n_sc);
-          }
-          ++n_sc; progress = true;
         }
         release();
         if (progress) patience.progress();
@@ -371,7 +382,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
     auto make_p = [&](int n, int L) {
       tc_fence_after();
       uint32_t r[32];
-      if (!(p.skip & 16)) { tmem_ld_16x256b_x8(tm + lane_base + G::TM_SC + (n % G::NSC) * 64, r); tmem_wait_ld(); }
+      if (!(p.skip & 16)) { tmem_ld_16x256b_x8(tm + lane_base + tm_sc(n), r); tmem_wait_ld(); }
       tc_fence_before();
       const float cs = REV ? exp2f(-(float)L * lg) : exp2f(-(float)L * lg) * rs;
       uint8_t* pt = sm + G::OFF_P + (n % G::NP) * G::P_BYTES;
@@ -406,7 +417,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
 #pragma unroll
       for (int half = 0; half < G::NOUT / 64; ++half) {
         uint32_t r[32];
-        if (!(p.skip & 16)) { tmem_ld_16x256b_x8(tm + lane_base + G::TM_ACC + (n % G::NACC) * G::NOUT + half * 64, r); tmem_wait_ld(); }
+        if (!(p.skip & 16)) { tmem_ld_16x256b_x8(tm + lane_base + tm_acc(n) + half * 64, r); tmem_wait_ld(); }
         if (half == G::NOUT / 64 - 1) { tc_fence_before(); mbar_arrive(bar(B_ACCFREE + n % G::NACC)); }
         if (p.skip & 2) continue;
 #pragma unroll
@@ -463,7 +474,11 @@ scan_kernel(const __grid_constant__ ScanParams p) {
           epilogue(n_e, ck_e, true);     // meet the others at the epilogue's first barrier and leave with them
           break;
         } else {
-          __nanosleep(20);               // idle: leave the issue slots to the warps that have work
+          // idle: sleep in hardware on the barrier most likely to complete next (leaves the issue slots to the
+          // warps that have work, wakes at once when that barrier completes)
+          const bool want_p = n_p < NC && n_p < n_e + G::NP;
+          if (want_p) mbar_try_wait_hint(bar(B_SCFULL + n_p % G::NSC), (n_p / G::NSC) & 1, 200);
+          else mbar_try_wait_hint(bar(B_ACCFULL + n_e % G::NACC), (n_e / G::NACC) & 1, 200);
         }
       }
       if (t == 0) tma_store_wait_all0();
@@ -627,7 +642,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
             if (t == 0) FPB_TRACE(13, n_u);
             publish_due = false; progress = true;
           }
-        } else if (mbar_test_wait(bar(B_DSFULL), n_u & 1)) {
+        } else if (mbar_test_wait(bar(B_DSFULL + (n_u & 1)), (n_u >> 1) & 1)) {
           if (t == 0) FPB_TRACE(12, n_u);
           tc_fence_after();
           const float gl = exp2f((float)ck_u.L * lg);
@@ -636,15 +651,15 @@ scan_kernel(const __grid_constant__ ScanParams p) {
           for (int i0 = 0; i0 < G::NS; i0 += 16) {
             uint32_t r[16];
             if (!(p.skip & 16)) {
-              if (R == 128) tmem_ld_32x32b_x16(tm + lane_base + G::TM_DS + wcol0 + i0, r);
-              else tmem_ld_16x256b_x4(tm + lane_base + G::TM_DS + wcol0 + i0 * 2, r);
+              if (R == 128) tmem_ld_32x32b_x16(tm + lane_base + tm_ds(n_u) + wcol0 + i0, r);
+              else tmem_ld_16x256b_x4(tm + lane_base + tm_ds(n_u) + wcol0 + i0 * 2, r);
               tmem_wait_ld();
             }
 #pragma unroll
             for (int i = 0; i < 16; ++i) S[i0 + i] = fmaf(gl, S[i0 + i], ds_scale * __uint_as_float(r[i]));
           }
           tc_fence_before();
-          mbar_arrive(bar(B_DSFREE));        // the increment has been read: the next one may overwrite it
+          mbar_arrive(bar(B_DSFREE + (n_u & 1)));   // the increment has been read: the one after next may overwrite it
           const int end = ck_u.a + ck_u.L;
           if (!REV && p.block_size > 0 && p.block_states && end % p.block_size == 0 && end / p.block_size - 1 < p.n_blocks)
             store_global(p.block_states + (((int64_t)b * p.n_blocks + (end / p.block_size - 1)) * p.H + h) * state_elems);
@@ -658,7 +673,8 @@ scan_kernel(const __grid_constant__ ScanParams p) {
         }
         if (progress) patience.progress();
         else if (patience.exhausted(abort_flag)) { FPB_GIVE_UP(0x400 | (n_u & 0xff)); break; }
-        else __nanosleep(20);            // idle: leave the issue slots to the warps that have work
+        else if (publish_due) mbar_try_wait_hint(bar(B_SBFREE), (n_u - 1) & 1, 200);   // idle: sleep on the likely next
+        else mbar_try_wait_hint(bar(B_DSFULL + (n_u & 1)), (n_u >> 1) & 1, 200);
       }
     }
     if (x_end && !*abort_flag) store_global(x_end);
