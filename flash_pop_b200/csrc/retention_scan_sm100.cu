@@ -40,6 +40,7 @@
 // several chunks are in flight per SM and the chain latency is hidden.
 #include "fpb_common.cuh"
 #include "ptx_sm100.cuh"
+#include "scan_common.cuh"
 #include "tensormap.cuh"
 #include "umma_launch.h"
 
@@ -47,10 +48,10 @@ namespace fpb {
 namespace {
 
 using namespace ptx;
+using namespace scan;
 typedef __nv_bfloat16 bf16;
 
 constexpr int MODE_FWD = 0, MODE_DQ = 1;
-constexpr int C = 64;                 // chunk length
 constexpr int SCORE_WARP0 = 2, STATE_WARP0 = 6;
 constexpr int N_SCORE = 128;
 
@@ -115,61 +116,6 @@ struct Cfg {
   static constexpr int NHALF = STATE_WARPS / 4;
   static constexpr int WCOLS = CC / NHALF;                   // state columns handled by one warp
   static constexpr int NS = R == 128 ? WCOLS : WCOLS / 2;
-};
-
-struct Chunk { int a, L; };
-__device__ __forceinline__ bool next_chunk(Chunk& ck, int T, int bs) {
-  const int a = ck.a + ck.L;
-  if (a >= T) return false;
-  int b = min(a + C, T);
-  if (bs > 0) b = min(b, (a / bs + 1) * bs);
-  ck.a = a; ck.L = b - a;
-  return true;
-}
-// the same schedule walked from the end: ck.a is the start of the chunk processed before
-__device__ __forceinline__ bool prev_chunk(Chunk& ck, int bs) {
-  const int end = ck.a;
-  if (end <= 0) return false;
-  const int base = bs > 0 ? ((end - 1) / bs) * bs : 0;
-  const int start = base + ((end - base - 1) / C) * C;
-  ck.a = start; ck.L = end - start;
-  return true;
-}
-template <int REV> __device__ __forceinline__ bool advance(Chunk& ck, int T, int bs) {
-  return REV ? prev_chunk(ck, bs) : next_chunk(ck, T, bs);
-}
-__device__ __forceinline__ int chunk_count(int T, int bs) {
-  if (bs <= 0) return (T + C - 1) / C;
-  return (T / bs) * ((bs + C - 1) / C) + (T % bs + C - 1) / C;
-}
-
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
-
-#define FPB_GIVE_UP(code)                                             \
-  do {                                                                \
-    atomicCAS(p.status, 0, (code));                                   \
-    *abort_flag = 1;                                                  \
-  } while (0)
-
-// diagnostics: stamp event `slot` (0..15) of chunk `c` for CTA (0,0,0) when a trace buffer is installed
-#define FPB_TRACE(slot, c)                                                                              \
-  do {                                                                                                  \
-    if (p.trace && (blockIdx.x | blockIdx.y | blockIdx.z) == 0 && (c) < 64) p.trace[(c) * 16 + (slot)] = clock64(); \
-  } while (0)
-
-// A polling loop that made no progress: true when it should give up (another thread did, or ~1 s passed).
-struct Patience {
-  long long t_last;
-  int idle;
-  __device__ __forceinline__ void progress() { idle = 0; }
-  __device__ __forceinline__ bool exhausted(volatile int* abort_flag) {
-    if (idle == 0) t_last = clock64();
-    if ((++idle & 31) != 0) return false;
-    return *abort_flag != 0 || clock64() - t_last > kWaitCycles;
-  }
 };
 
 template <int MODE, int REV, int R, int CC>
@@ -706,6 +652,7 @@ int launch_scan(const ScanParams& p, bool rev, dim3 grid, cudaStream_t stream) {
 }
 
 int g_tile_pref = 1;            // 1: 128x128 state tiles where they apply; 0: 64-wide tiles (two CTAs per SM)
+int g_fused_bwd = 1;            // 1: dK, dV, dS_0 in one fused reverse walk where it applies; 0: two separate walks
 long long* g_trace = nullptr;   // set by fpb_debug_trace
 int g_skip = 0;                 // set by fpb_debug_skip
 
@@ -774,6 +721,8 @@ int launch_pass(const PassArgs& a, cudaStream_t stream) {
 
 }  // namespace
 
+long long* debug_trace_ptr() { return g_trace; }
+
 // Diagnostics hook (not part of the public header): install a device buffer of 64*16 int64 that the next
 // launches fill with clock64() stamps of their first CTA; null removes it.
 extern "C" void fpb_debug_trace(void* device_buffer) { g_trace = (long long*)device_buffer; }
@@ -782,6 +731,8 @@ extern "C" void fpb_debug_tile_pref(int wide) { g_tile_pref = wide; }
 // Diagnostics hook for timing experiments: leave out parts of the work (1 V scaling, 2 output staging/store,
 // 4 state copy, 8 P' writes).  Results are wrong while any bit is set.
 extern "C" void fpb_debug_skip(int mask) { g_skip = mask; }
+// Diagnostics hook: 0 runs the dV and dK walks as two launches instead of the fused reverse kernel.
+extern "C" void fpb_debug_fused_bwd(int on) { g_fused_bwd = on; }
 
 int launch_umma_fwd(const UmmaFwdArgs& a, cudaStream_t stream) {
   if (a.dtype != FPB_BF16) return FPB_UMMA_NOT_APPLICABLE;
@@ -809,6 +760,11 @@ int launch_umma_bwd(const UmmaBwdArgs& a, cudaStream_t stream, int* n_launched) 
   int r;
   if ((r = launch_pass(dq, stream)) != FPB_OK) return r;
   *n_launched = 1;
+  if (g_fused_bwd) {
+    r = launch_bwd_fused(a, stream);
+    if (r == FPB_OK) { *n_launched = 2; return FPB_OK; }
+    if (r != FPB_UMMA_NOT_APPLICABLE) return r;
+  }
   if ((r = launch_pass(dv, stream)) != FPB_OK) return r;
   *n_launched = 2;
   if ((r = launch_pass(dk, stream)) != FPB_OK) return r;

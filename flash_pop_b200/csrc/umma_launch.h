@@ -29,5 +29,9 @@ struct UmmaBwdArgs {
 
 int launch_umma_fwd(const UmmaFwdArgs& a, cudaStream_t stream);
 int launch_umma_bwd(const UmmaBwdArgs& a, cudaStream_t stream, int* n_launched);
+// dK, dV, dS_0 in one reverse walk (retention_bwd_fused_sm100.cu)
+int launch_bwd_fused(const UmmaBwdArgs& a, cudaStream_t stream);
+// diagnostics: device buffer for per-chunk time stamps, or null
+long long* debug_trace_ptr();
 
 }  // namespace fpb
