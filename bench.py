@@ -247,9 +247,19 @@ def main():
     launches = _lib.launch_count() - launches0
     clocks = sampler.stop() if sampler else None
 
-    # per-entry-point device times for the roofline (same inputs, > L2, so no flush needed)
+    # per-launch device times for the roofline (same inputs, > L2, so no flush needed): the forward launch, and
+    # the two backward launches singled out by asking for only dQ / only dK,dV (the operator skips the other walk)
     ms_fwd = event_time_ms(fwd_only, max(args.steps, 5))
     ms_bwd = max(ms - ms_fwd, 1e-6)
+
+    def only_grads(of):
+        leaves = [t.detach().requires_grad_(i in of) for i, t in enumerate((q, k, v))]
+        o = op(*leaves)
+        wanted = [leaves[i] for i in of]
+        return lambda: torch.autograd.grad(o, wanted, dO, retain_graph=True)
+
+    ms_dq = event_time_ms(only_grads((0,)), max(args.steps, 5))
+    ms_rev = event_time_ms(only_grads((1, 2)), max(args.steps, 5))
 
     # end to end: host (pinned) -> device, forward+backward, every result back to the host
     e2e_ms = None
@@ -272,10 +282,10 @@ def main():
         e2e_ms = event_time_ms(e2e_step, max(3, min(args.steps, 5)))
         barrier()
 
-    t_ms = torch.tensor([ms, ms_fwd, ms_bwd, e2e_ms or 0.0], device=dev, dtype=torch.float64)
+    t_ms = torch.tensor([ms, ms_fwd, ms_bwd, e2e_ms or 0.0, ms_dq, ms_rev], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
-    ms, ms_fwd, ms_bwd, e2e_max = t_ms.tolist()
+    ms, ms_fwd, ms_bwd, e2e_max, ms_dq, ms_rev = t_ms.tolist()
     _lib.device_status(dev)
 
     if rank == 0:
@@ -291,11 +301,11 @@ def main():
             peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
             peak_src = "fallback"
         value = total_flop / (ms * 1e-3) / 1e12
-        # Top kernel of the launch list (profiles/scan_kernel_ns_launch_list.md): the forward scan launch; its
-        # duration is the CUDA-event time of forward-only calls (one launch each).  DRAM traffic per launch from the
-        # ncu capture in profiles/scan_kernel_forward_small_full.md (workload "ns" only).
-        fwd_traffic = {"ns": 806.8e6 + 248.7e6}.get(args.workload)
-        achieved = bf * units / (ms_fwd * 1e-3) / 1e9
+        # Top kernel of the launch list (profiles/): the fused reverse walk (dK, dV, dS_0), one launch per step.  It
+        # reads Q, K, V, dO and writes dK, dV; DRAM traffic per launch from the ncu capture in profiles/ ("ns" only).
+        rev_bytes = 2 * (2 * dk + 2 * dv) * units + 2 * (dk + dv) * units
+        rev_traffic = {"ns": 1074.3e6 + 506.4e6}.get(args.workload)
+        achieved = rev_bytes / (ms_rev * 1e-3) / 1e9
         step_gbs = (bf + bb) * units / (ms * 1e-3) / 1e9
         line = {
             "metric": "chunked_retention_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s",
@@ -305,14 +315,20 @@ def main():
             "pct_bf16_peak_nominal": 100 * value / world / 2250.0,
             "pct_bf16_peak_measured": 100 * value / world / peaks.get("bf16_tflops", 1590.0),
             "hbm_gbs_algorithmic": (bf + bb) * units / (ms * 1e-3) / 1e9,
-            "ms_fwd": ms_fwd, "ms_bwd": ms_bwd,
+            "ms_fwd": ms_fwd, "ms_bwd": ms_bwd, "ms_bwd_dq": ms_dq, "ms_bwd_dkdv": ms_rev,
             "path": {1: "cuda-core", 2: "tcgen05"}.get(path, "none"),
             "config": {"workload": workload_name(args, w), "l2": "inputs (1 GB+) larger than the 126 MB L2; no flush",
                        "flop_count": "algorithmic, causal half of intra-chunk tiles (C=64)"},
-            "roofline": {"bound": "hbm", "kernel": "scan_kernel<MODE_FWD, forward> (one launch per step, largest share)",
+            "roofline": {"bound": "hbm", "kernel": "bwd_fused_kernel (reverse walk: dK, dV, dS0; one launch per step, largest share)",
                          "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                         "peak_source": peak_src, "traffic": fwd_traffic, "algorithmic_bytes": bf * units},
-            "roofline_step": {"bound": "hbm", "kernels": "all four scan launches of a step", "achieved": step_gbs,
+                         "peak_source": peak_src, "traffic": rev_traffic, "algorithmic_bytes": rev_bytes, "ms_per_launch": ms_rev},
+            "roofline_fwd": {"bound": "hbm", "kernel": "scan_kernel<MODE_FWD, forward>", "achieved": bf * units / (ms_fwd * 1e-3) / 1e9,
+                             "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": bf * units / (ms_fwd * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                             "algorithmic_bytes": bf * units, "ms_per_launch": ms_fwd},
+            "roofline_dq": {"bound": "hbm", "kernel": "scan_kernel<MODE_DQ, forward>", "achieved": bf * units / (ms_dq * 1e-3) / 1e9,
+                            "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": bf * units / (ms_dq * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                            "algorithmic_bytes": bf * units, "ms_per_launch": ms_dq},
+            "roofline_step": {"bound": "hbm", "kernels": "the three launches of a step (forward, dQ, fused reverse)", "achieved": step_gbs,
                               "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": step_gbs / peaks["hbm_gbs"],
                               "algorithmic_bytes": (bf + bb) * units},
             "clocks": clocks,

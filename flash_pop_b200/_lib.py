@@ -28,7 +28,7 @@ NVCC_FLAGS = [
 
 FPB_BF16, FPB_F32 = 0, 1
 PATH_NONE, PATH_SIMT, PATH_TCGEN05 = 0, 1, 2
-FLAG_FORCE_SIMT = 1
+FLAG_FORCE_SIMT, FLAG_SKIP_DQ, FLAG_SKIP_DKDV = 1, 2, 4
 
 
 class _Seq(ctypes.Structure):
@@ -174,7 +174,9 @@ def unit_inner(t: torch.Tensor) -> torch.Tensor:
     return t if t.stride(-1) == 1 or t.size(-1) == 1 and t.is_contiguous() else t.contiguous()
 
 
-def seq(t: torch.Tensor) -> _Seq:
+def seq(t: Optional[torch.Tensor]) -> _Seq:
+    if t is None:
+        return _Seq(None, 0, 0, 0)
     assert t.dim() == 4
     return _Seq(t.data_ptr(), t.stride(0), t.stride(1), t.stride(2))
 

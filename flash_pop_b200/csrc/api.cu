@@ -83,7 +83,8 @@ int check_dims(const fpb_dims* d, bool pop, Call* c) {
   return FPB_OK;
 }
 
-int check_seq(const Call& c, const fpb_seq* s, int d, int64_t batch) {
+int check_seq(const Call& c, const fpb_seq* s, int d, int64_t batch, bool optional = false) {
+  if (optional && (!s || !s->data)) return FPB_OK;
   if (!s) return FPB_ERR_NULL_POINTER;
   const bool empty = batch == 0 || c.T == 0 || c.H == 0;
   if (!s->data) return empty ? FPB_OK : FPB_ERR_NULL_POINTER;
@@ -155,33 +156,40 @@ int backward(const Call& c, int64_t batch, SeqView q, SeqView k, SeqView v, Stat
     a.sfx_in = sfx_in; a.sfx_grad = sfx_grad;
     a.B = (int)batch; a.T = c.T; a.H = c.H; a.dk = c.dk; a.dv = c.dv; a.dtype = c.dtype;
     a.block_size = c.block_size; a.n_blocks = c.n_blocks; a.gamma = c.gamma;
+    a.skip_dq = (c.flags & FPB_FLAG_SKIP_DQ) != 0; a.skip_dkdv = (c.flags & FPB_FLAG_SKIP_DKDV) != 0;
     int n_launched = 0;
     const int r = launch_umma_bwd(a, stream, &n_launched);
     if (r == FPB_OK) return finish_launches(n_launched, FPB_PATH_TCGEN05);
     if (r != FPB_UMMA_NOT_APPLICABLE) return r;
   }
   WalkParams p;
-  int r;
-  // dQ: forward walk over the states
-  fill_common(p, c, +1, sfx_in);
-  own_is_dk(p, c);
-  p.u = k; p.w = v; p.r = dO; p.out = dQ; p.scale_u = rs; p.x0 = s0;
-  if ((r = launch_walk(p, c.dtype, (int)batch, stream)) != FPB_OK) return r;
-  // dV and dS_0: reverse walk over the state gradient
-  fill_common(p, c, -1, sfx_grad);
-  own_is_dv(p, c);
-  p.u = dO; p.w = q; p.r = k; p.out = dV; p.scale_r = rs;
-  p.x0 = d_s_out; p.x_out = d_s0; p.block_in = d_block_states;
-  if ((r = launch_walk(p, c.dtype, (int)batch, stream)) != FPB_OK) return r;
-  // dK: reverse walk, transposed ownership
-  SuffixStates no_write = sfx_grad;
-  no_write.blocks = nullptr;
-  fill_common(p, c, -1, no_write);
-  own_is_dk(p, c);
-  p.u = q; p.w = dO; p.r = v; p.out = dK; p.scale_out = rs;
-  p.x0 = d_s_out; p.block_in = d_block_states;
-  if ((r = launch_walk(p, c.dtype, (int)batch, stream)) != FPB_OK) return r;
-  return finish_launches(3, FPB_PATH_SIMT);
+  int r, n = 0;
+  if (!(c.flags & FPB_FLAG_SKIP_DQ)) {
+    // dQ: forward walk over the states
+    fill_common(p, c, +1, sfx_in);
+    own_is_dk(p, c);
+    p.u = k; p.w = v; p.r = dO; p.out = dQ; p.scale_u = rs; p.x0 = s0;
+    if ((r = launch_walk(p, c.dtype, (int)batch, stream)) != FPB_OK) return r;
+    ++n;
+  }
+  if (!(c.flags & FPB_FLAG_SKIP_DKDV)) {
+    // dV and dS_0: reverse walk over the state gradient
+    fill_common(p, c, -1, sfx_grad);
+    own_is_dv(p, c);
+    p.u = dO; p.w = q; p.r = k; p.out = dV; p.scale_r = rs;
+    p.x0 = d_s_out; p.x_out = d_s0; p.block_in = d_block_states;
+    if ((r = launch_walk(p, c.dtype, (int)batch, stream)) != FPB_OK) return r;
+    // dK: reverse walk, transposed ownership
+    SuffixStates no_write = sfx_grad;
+    no_write.blocks = nullptr;
+    fill_common(p, c, -1, no_write);
+    own_is_dk(p, c);
+    p.u = q; p.w = dO; p.r = v; p.out = dK; p.scale_out = rs;
+    p.x0 = d_s_out; p.block_in = d_block_states;
+    if ((r = launch_walk(p, c.dtype, (int)batch, stream)) != FPB_OK) return r;
+    n += 2;
+  }
+  return finish_launches(n, FPB_PATH_SIMT);
 }
 
 }  // namespace
@@ -213,7 +221,8 @@ int fpb_retention_bwd(const fpb_dims* dims, const fpb_seq* q, const fpb_seq* k, 
   FPB_TRY(check_dims(dims, false, &c));
   FPB_TRY(check_seq(c, q, c.dk, c.B)); FPB_TRY(check_seq(c, k, c.dk, c.B)); FPB_TRY(check_seq(c, v, c.dv, c.B));
   FPB_TRY(check_seq(c, d_o, c.dv, c.B));
-  FPB_TRY(check_seq(c, d_q, c.dk, c.B)); FPB_TRY(check_seq(c, d_k, c.dk, c.B)); FPB_TRY(check_seq(c, d_v, c.dv, c.B));
+  FPB_TRY(check_seq(c, d_q, c.dk, c.B, c.flags & FPB_FLAG_SKIP_DQ));
+  FPB_TRY(check_seq(c, d_k, c.dk, c.B, c.flags & FPB_FLAG_SKIP_DKDV)); FPB_TRY(check_seq(c, d_v, c.dv, c.B, c.flags & FPB_FLAG_SKIP_DKDV));
   FPB_TRY(check_state(s0, c)); FPB_TRY(check_state(d_s_out, c)); FPB_TRY(check_state(d_s0, c));
   FPB_TRY(check_device());
   const SuffixStates none{0, 0, nullptr};
@@ -242,7 +251,8 @@ int fpb_pop_retention_bwd(const fpb_dims* dims, const fpb_seq* q, const fpb_seq*
   FPB_TRY(check_dims(dims, true, &c));
   FPB_TRY(check_seq(c, q, c.dk, c.B)); FPB_TRY(check_seq(c, k, c.dk, c.B)); FPB_TRY(check_seq(c, v, c.dv, c.B));
   FPB_TRY(check_seq(c, d_o, c.dv, c.B));
-  FPB_TRY(check_seq(c, d_q, c.dk, c.B)); FPB_TRY(check_seq(c, d_k, c.dk, c.B)); FPB_TRY(check_seq(c, d_v, c.dv, c.B));
+  FPB_TRY(check_seq(c, d_q, c.dk, c.B, c.flags & FPB_FLAG_SKIP_DQ));
+  FPB_TRY(check_seq(c, d_k, c.dk, c.B, c.flags & FPB_FLAG_SKIP_DKDV)); FPB_TRY(check_seq(c, d_v, c.dv, c.B, c.flags & FPB_FLAG_SKIP_DKDV));
   FPB_TRY(check_state(s0, c)); FPB_TRY(check_state(d_s0, c));
   FPB_TRY(check_device());
   const SuffixStates none{0, 0, nullptr};
@@ -279,7 +289,8 @@ int fpb_pop_suffix_bwd(const fpb_dims* dims, int32_t M, int32_t N, const fpb_seq
   if (batch > 0x7fffffff) return FPB_ERR_TOO_LARGE;
   FPB_TRY(check_seq(c, q, c.dk, batch)); FPB_TRY(check_seq(c, k, c.dk, batch)); FPB_TRY(check_seq(c, v, c.dv, batch));
   FPB_TRY(check_seq(c, d_o, c.dv, batch));
-  FPB_TRY(check_seq(c, d_q, c.dk, batch)); FPB_TRY(check_seq(c, d_k, c.dk, batch)); FPB_TRY(check_seq(c, d_v, c.dv, batch));
+  FPB_TRY(check_seq(c, d_q, c.dk, batch, c.flags & FPB_FLAG_SKIP_DQ));
+  FPB_TRY(check_seq(c, d_k, c.dk, batch, c.flags & FPB_FLAG_SKIP_DKDV)); FPB_TRY(check_seq(c, d_v, c.dv, batch, c.flags & FPB_FLAG_SKIP_DKDV));
   FPB_TRY(check_state(s0, c)); FPB_TRY(check_state(d_s0, c));
   if (M > 1 && c.B > 0 && c.H > 0 && (!block_states || !d_block_states)) return FPB_ERR_NULL_POINTER;
   FPB_TRY(check_device());

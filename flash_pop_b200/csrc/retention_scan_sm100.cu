@@ -756,19 +756,23 @@ int launch_umma_bwd(const UmmaBwdArgs& a, cudaStream_t stream, int* n_launched) 
   no_write.blocks = nullptr;
   PassArgs dk{MODE_DQ, true, a.v, a.q, a.dO, a.dK, a.d_s_out, none, nullptr, a.d_block_states, no_write, a.gamma,
               a.B, a.T, a.H, a.dk, a.dv, a.block_size, a.n_blocks};
-  if (!pass_applicable(dq) || !pass_applicable(dv) || !pass_applicable(dk)) return FPB_UMMA_NOT_APPLICABLE;
+  if ((!a.skip_dq && !pass_applicable(dq)) || (!a.skip_dkdv && (!pass_applicable(dv) || !pass_applicable(dk))))
+    return FPB_UMMA_NOT_APPLICABLE;
   int r;
-  if ((r = launch_pass(dq, stream)) != FPB_OK) return r;
-  *n_launched = 1;
+  if (!a.skip_dq) {
+    if ((r = launch_pass(dq, stream)) != FPB_OK) return r;
+    ++*n_launched;
+  }
+  if (a.skip_dkdv) return FPB_OK;
   if (g_fused_bwd) {
     r = launch_bwd_fused(a, stream);
-    if (r == FPB_OK) { *n_launched = 2; return FPB_OK; }
+    if (r == FPB_OK) { ++*n_launched; return FPB_OK; }
     if (r != FPB_UMMA_NOT_APPLICABLE) return r;
   }
   if ((r = launch_pass(dv, stream)) != FPB_OK) return r;
-  *n_launched = 2;
+  ++*n_launched;
   if ((r = launch_pass(dk, stream)) != FPB_OK) return r;
-  *n_launched = 3;
+  ++*n_launched;
   return FPB_OK;
 }
 

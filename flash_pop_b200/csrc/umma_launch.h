@@ -25,6 +25,7 @@ struct UmmaBwdArgs {
   SuffixStates sfx_in, sfx_grad;
   const float* gamma;
   int B, T, H, dk, dv, dtype, block_size, n_blocks;
+  bool skip_dq, skip_dkdv;
 };
 
 int launch_umma_fwd(const UmmaFwdArgs& a, cudaStream_t stream);

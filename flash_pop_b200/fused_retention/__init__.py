@@ -80,13 +80,21 @@ class FusedChunkRetention(torch.autograd.Function):
             dO = torch.zeros((B, T, H, dv), device=q.device, dtype=q.dtype)
         dO = _lib.unit_inner(dO.to(q.dtype))
         dS_new = _lib.state_tensor(None if dS_new is None else dS_new.to(q.dtype))
-        dQ, dK, dV = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-        dS = torch.empty((B, H, dk, dv), device=q.device, dtype=q.dtype) if (s is not None and ctx.needs_input_grad[3]) else None
-        with torch.cuda.device(q.device):
-            d = _lib.dims(q, dv, ctx.head_decays, flags=ctx.flags)
-            _lib.check(_lib.lib().fpb_retention_bwd(d, _lib.seq(q), _lib.seq(k), _lib.seq(v), _lib.state(s),
-                                                    _lib.seq(dO), _lib.state(dS_new), _lib.seq(dQ), _lib.seq(dK),
-                                                    _lib.seq(dV), _lib.state(dS), _lib.stream_ptr(q.device)))
+        # leave out the walk nobody needs: dQ is one launch, dK/dV/dS_0 the other
+        need_q = ctx.needs_input_grad[0]
+        need_s = s is not None and ctx.needs_input_grad[3]
+        need_kv = ctx.needs_input_grad[1] or ctx.needs_input_grad[2] or need_s
+        flags = ctx.flags | (0 if need_q else _lib.FLAG_SKIP_DQ) | (0 if need_kv else _lib.FLAG_SKIP_DKDV)
+        dQ = torch.empty_like(q) if need_q else None
+        dK = torch.empty_like(k) if need_kv else None
+        dV = torch.empty_like(v) if need_kv else None
+        dS = torch.empty((B, H, dk, dv), device=q.device, dtype=q.dtype) if need_s else None
+        if need_q or need_kv:
+            with torch.cuda.device(q.device):
+                d = _lib.dims(q, dv, ctx.head_decays, flags=flags)
+                _lib.check(_lib.lib().fpb_retention_bwd(d, _lib.seq(q), _lib.seq(k), _lib.seq(v), _lib.state(s),
+                                                        _lib.seq(dO), _lib.state(dS_new), _lib.seq(dQ), _lib.seq(dK),
+                                                        _lib.seq(dV), _lib.state(dS), _lib.stream_ptr(q.device)))
         return dQ, dK, dV, dS, None
 
 

@@ -52,14 +52,21 @@ class FlashPOPRetention(torch.autograd.Function):
         dO = _lib.unit_inner(dO.to(q.dtype))
         if d_block_states is not None:
             d_block_states = d_block_states.to(q.dtype).contiguous()
-        dQ, dK, dV = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-        dS = torch.empty((B, H, dk, dv), device=q.device, dtype=q.dtype) if (s is not None and ctx.needs_input_grad[3]) else None
-        with torch.cuda.device(q.device):
-            d = _lib.dims(q, dv, ctx.head_decays, block_size=ctx.block_size, flags=ctx.flags)
-            _lib.check(_lib.lib().fpb_pop_retention_bwd(
-                d, _lib.seq(q), _lib.seq(k), _lib.seq(v), _lib.state(s), _lib.seq(dO),
-                None if d_block_states is None else d_block_states.data_ptr(),
-                _lib.seq(dQ), _lib.seq(dK), _lib.seq(dV), _lib.state(dS), _lib.stream_ptr(q.device)))
+        need_q = ctx.needs_input_grad[0]
+        need_s = s is not None and ctx.needs_input_grad[3]
+        need_kv = ctx.needs_input_grad[1] or ctx.needs_input_grad[2] or need_s
+        flags = ctx.flags | (0 if need_q else _lib.FLAG_SKIP_DQ) | (0 if need_kv else _lib.FLAG_SKIP_DKDV)
+        dQ = torch.empty_like(q) if need_q else None
+        dK = torch.empty_like(k) if need_kv else None
+        dV = torch.empty_like(v) if need_kv else None
+        dS = torch.empty((B, H, dk, dv), device=q.device, dtype=q.dtype) if need_s else None
+        if need_q or need_kv:
+            with torch.cuda.device(q.device):
+                d = _lib.dims(q, dv, ctx.head_decays, block_size=ctx.block_size, flags=flags)
+                _lib.check(_lib.lib().fpb_pop_retention_bwd(
+                    d, _lib.seq(q), _lib.seq(k), _lib.seq(v), _lib.state(s), _lib.seq(dO),
+                    None if d_block_states is None else d_block_states.data_ptr(),
+                    _lib.seq(dQ), _lib.seq(dK), _lib.seq(dV), _lib.state(dS), _lib.stream_ptr(q.device)))
         return dQ, dK, dV, dS, None, None
 
 

@@ -47,7 +47,10 @@ typedef enum fpb_dtype { FPB_BF16 = 0, FPB_F32 = 1 } fpb_dtype;
 typedef enum fpb_path { FPB_PATH_NONE = 0, FPB_PATH_SIMT = 1, FPB_PATH_TCGEN05 = 2 } fpb_path;
 
 enum {
-  FPB_FLAG_FORCE_SIMT = 1   /* take the CUDA-core fp32-math kernels even where the tensor-core ones apply */
+  FPB_FLAG_FORCE_SIMT = 1,  /* take the CUDA-core fp32-math kernels even where the tensor-core ones apply */
+  /* backward entry points only: leave out a part nobody needs (its output tensors may then have data == NULL) */
+  FPB_FLAG_SKIP_DQ = 2,     /* no dQ: skips the forward walk that recomputes the states */
+  FPB_FLAG_SKIP_DKDV = 4    /* no dK, dV, dS_0 (nor suffix state gradients): skips the reverse walk */
 };
 
 /* A (B, T, H, d) activation. */

@@ -148,3 +148,28 @@ def test_suffixes_on_tensor_cores():
     check("suffix O", out, ref, BF)
     for got, want, n in zip(leaves, ref_leaves, ("dQ", "dK", "dV", "dS0", "dBS")):
         check(n, got.grad, want.grad, BF)
+
+
+def test_backward_runs_only_the_walks_that_are_needed():
+    """dQ alone is one launch, dK/dV alone the other; results equal those of the full backward."""
+    import flash_pop_b200 as fp
+    from flash_pop_b200 import _lib
+    B, T, H, d = 2, 200, 2, 128
+    decays = orc.head_decays(H, (5, 12))
+    q, k, v, s, g = make_inputs(5, B, T, H, d, d, BF)
+    dO = torch.randn(B, T, H, d, generator=g).to(BF).cuda()
+    full = [t.cuda().requires_grad_(True) for t in (q, k, v)]
+    o, _ = fp.fused_chunk_retention(*full, s.cuda(), decays)
+    o.backward(dO)
+    for wanted in ((0,), (1, 2), (2,)):
+        leaves = [t.cuda().requires_grad_(i in wanted) for i, t in enumerate((q, k, v))]
+        o, _ = fp.fused_chunk_retention(*leaves, s.cuda(), decays)
+        before = _lib.launch_count()
+        o.backward(dO)
+        assert _lib.launch_count() - before == 1
+        for i in range(3):
+            if i in wanted:
+                assert torch.equal(leaves[i].grad, full[i].grad)
+            else:
+                assert leaves[i].grad is None
+    _lib.device_status()
