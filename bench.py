@@ -304,7 +304,7 @@ def main():
         # Top kernel of the launch list (profiles/): the fused reverse walk (dK, dV, dS_0), one launch per step.  It
         # reads Q, K, V, dO and writes dK, dV; DRAM traffic per launch from the ncu capture in profiles/ ("ns" only).
         rev_bytes = 2 * (2 * dk + 2 * dv) * units + 2 * (dk + dv) * units
-        rev_traffic = {"ns": 1074.3e6 + 506.4e6}.get(args.workload)
+        rev_traffic = {"ns": 1073.8e6 + 506.3e6}.get(args.workload)
         achieved = rev_bytes / (ms_rev * 1e-3) / 1e9
         step_gbs = (bf + bb) * units / (ms * 1e-3) / 1e9
         line = {
