@@ -66,7 +66,6 @@ struct ScanParams {
   int32_t T, H, dk, dv, block_size, n_blocks;
   int32_t* status;
   long long* trace;              // diagnostics: per-chunk clock64() stamps of CTA (0,0,0), or null
-  int32_t skip;                  // diagnostics (timing experiments only, results become wrong): bit mask of work to leave out
   float log2g[FPB_MAX_HEADS];
 };
 
@@ -256,7 +255,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
           const uint64_t bk = (MODE == MODE_FWD ? d_kk : d_vk) + so;
           if (leader) {
 #pragma unroll
-            for (int ks = 0; ks < ((p.skip & 32) ? 0 : G::W1 / 16); ++ks) umma_bf16(d, d_x + so + kstep(ks, 8192), bk + kstep(ks, 8192), ID_SC, ks > 0);
+            for (int ks = 0; ks < G::W1 / 16; ++ks) umma_bf16(d, d_x + so + kstep(ks, 8192), bk + kstep(ks, 8192), ID_SC, ks > 0);
             umma_commit(bar(B_SCFULL + n_sc % G::NSC));
             FPB_TRACE(0, n_sc);
           }
@@ -268,7 +267,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
           tc_fence_after();
           if (leader) {
 #pragma unroll
-            for (int ks = 0; ks < ((p.skip & 32) ? 0 : C / 16); ++ks) umma_bf16(tm + tm_ds(n_ds), d_km + so + mstep(ks), d_vm + so + mstep(ks), ID_DS, ks > 0);
+            for (int ks = 0; ks < C / 16; ++ks) umma_bf16(tm + tm_ds(n_ds), d_km + so + mstep(ks), d_vm + so + mstep(ks), ID_DS, ks > 0);
             umma_commit(bar(B_DSFULL + (n_ds & 1)));
             FPB_TRACE(4, n_ds);
           }
@@ -285,7 +284,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
           if (leader) {
             if (MODE == MODE_FWD) {
 #pragma unroll
-              for (int ks = 0; ks < ((p.skip & 32) ? 0 : R / 16); ++ks) umma_bf16(acc, d_x + so + kstep(ks, 8192), d_sb + mstep(ks), ID_STATE, ks > 0);
+              for (int ks = 0; ks < R / 16; ++ks) umma_bf16(acc, d_x + so + kstep(ks, 8192), d_sb + mstep(ks), ID_STATE, ks > 0);
             } else {
 #pragma unroll
               for (int ks = 0; ks < CC / 16; ++ks) umma_bf16(acc, d_x + so + kstep(ks, 8192), d_sb + kstep(ks, R * 128), ID_STATE, ks > 0);
@@ -305,7 +304,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
           const uint64_t bm = (MODE == MODE_FWD ? d_vm : d_km) + so;
           if (leader) {
 #pragma unroll
-            for (int ks = 0; ks < ((p.skip & 32) ? 0 : C / 16); ++ks) umma_bf16(acc, a + kstep(ks, 0), bm + mstep(ks), ID_INTRA, 1);
+            for (int ks = 0; ks < C / 16; ++ks) umma_bf16(acc, a + kstep(ks, 0), bm + mstep(ks), ID_INTRA, 1);
             umma_commit(bar(B_ACCFULL + n_pv % G::NACC));
             FPB_TRACE(3, n_pv);
           }
@@ -328,12 +327,13 @@ scan_kernel(const __grid_constant__ ScanParams p) {
     auto make_p = [&](int n, int L) {
       tc_fence_after();
       uint32_t r[32];
-      if (!(p.skip & 16)) { tmem_ld_16x256b_x8(tm + lane_base + tm_sc(n), r); tmem_wait_ld(); }
+      tmem_ld_16x256b_x8(tm + lane_base + tm_sc(n), r);
+      tmem_wait_ld();
       tc_fence_before();
       const float cs = REV ? exp2f(-(float)L * lg) : exp2f(-(float)L * lg) * rs;
       uint8_t* pt = sm + G::OFF_P + (n % G::NP) * G::P_BYTES;
 #pragma unroll
-      for (int g = 0; g < ((p.skip & 8) ? 0 : 8); ++g) {
+      for (int g = 0; g < 8; ++g) {
         const int col = g * 8 + cpair;
         auto keep = [&](int cc, int rr) { return REV ? cc >= rr : cc <= rr; };
         const float a0 = keep(col, r_lo) ? __uint_as_float(r[4 * g]) * cs : 0.f;
@@ -363,9 +363,9 @@ scan_kernel(const __grid_constant__ ScanParams p) {
 #pragma unroll
       for (int half = 0; half < G::NOUT / 64; ++half) {
         uint32_t r[32];
-        if (!(p.skip & 16)) { tmem_ld_16x256b_x8(tm + lane_base + tm_acc(n) + half * 64, r); tmem_wait_ld(); }
+        tmem_ld_16x256b_x8(tm + lane_base + tm_acc(n) + half * 64, r);
+        tmem_wait_ld();
         if (half == G::NOUT / 64 - 1) { tc_fence_before(); mbar_arrive(bar(B_ACCFREE + n % G::NACC)); }
-        if (p.skip & 2) continue;
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
           const uint32_t lo = pack_bf16(__uint_as_float(r[4 * g]) * z_lo, __uint_as_float(r[4 * g + 1]) * z_lo);
@@ -379,7 +379,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
       named_bar_sync(2, N_SCORE);
       const int ocol0 = MODE == MODE_FWD ? col0 : row0;
       if (whole_box) {
-        if (t == 0 && !(p.skip & 2)) {
+        if (t == 0) {
 #pragma unroll
           for (int cb = 0; cb < G::NOUT / 64; ++cb) tma_store_4d(&p.map_out, sbase + G::OFF_OUT + cb * 8192, ocol0 + cb * 64, ck.a, h, b);
           tma_store_commit();
@@ -510,8 +510,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
     // pieces XOR-swizzled by (row & 7) — an MN-major B operand (FWD) or a K-major B operand (DQ).
     auto publish_sb = [&]() {
       uint8_t* sb = sm + G::OFF_SB;
-      if (p.skip & 4) {
-      } else if (R == 128) {
+      if (R == 128) {
         const int row = row_of(0);
 #pragma unroll
         for (int i = 0; i < G::NS; i += 8) {
@@ -537,7 +536,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
     auto scale_v = [&](int n, int L) {
       const int s = stage_of(n);
       uint8_t* vt = sm + G::OFF_STAGE + s * G::STAGE_BYTES + G::X_BYTES + G::K_BYTES;
-      for (int idx = t; idx < ((p.skip & 1) ? 0 : C * CC / 8); idx += G::N_STATE) {
+      for (int idx = t; idx < C * CC / 8; idx += G::N_STATE) {
         const int row = (idx >> 3) & 63;
         uint4* ptr = reinterpret_cast<uint4*>(vt + idx * 16);
         uint4 val = make_uint4(0u, 0u, 0u, 0u);
@@ -596,11 +595,9 @@ scan_kernel(const __grid_constant__ ScanParams p) {
 #pragma unroll
           for (int i0 = 0; i0 < G::NS; i0 += 16) {
             uint32_t r[16];
-            if (!(p.skip & 16)) {
-              if (R == 128) tmem_ld_32x32b_x16(tm + lane_base + tm_ds(n_u) + wcol0 + i0, r);
-              else tmem_ld_16x256b_x4(tm + lane_base + tm_ds(n_u) + wcol0 + i0 * 2, r);
-              tmem_wait_ld();
-            }
+            if (R == 128) tmem_ld_32x32b_x16(tm + lane_base + tm_ds(n_u) + wcol0 + i0, r);
+            else tmem_ld_16x256b_x4(tm + lane_base + tm_ds(n_u) + wcol0 + i0 * 2, r);
+            tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 16; ++i) S[i0 + i] = fmaf(gl, S[i0 + i], ds_scale * __uint_as_float(r[i]));
           }
@@ -654,7 +651,6 @@ int launch_scan(const ScanParams& p, bool rev, dim3 grid, cudaStream_t stream) {
 int g_tile_pref = 1;            // 1: 128x128 state tiles where they apply; 0: 64-wide tiles (two CTAs per SM)
 int g_fused_bwd = 1;            // 1: dK, dV, dS_0 in one fused reverse walk where it applies; 0: two separate walks
 long long* g_trace = nullptr;   // set by fpb_debug_trace
-int g_skip = 0;                 // set by fpb_debug_skip
 
 bool aligned_state(const StateView& s) { return !s.data || ((uintptr_t)s.data % 16 == 0 && s.sb % 8 == 0 && s.sh % 8 == 0); }
 
@@ -700,7 +696,6 @@ int launch_pass(const PassArgs& a, cudaStream_t stream) {
   p.T = T; p.H = H; p.dk = dk; p.dv = dv; p.block_size = a.block_size; p.n_blocks = a.n_blocks;
   p.status = device_status_ptr();
   p.trace = g_trace;
-  p.skip = g_skip;
   if (!p.status) return FPB_ERR_LAUNCH;
   for (int h = 0; h < H; ++h) p.log2g[h] = (float)std::log2((double)a.gamma[h]);
 
@@ -728,9 +723,6 @@ long long* debug_trace_ptr() { return g_trace; }
 extern "C" void fpb_debug_trace(void* device_buffer) { g_trace = (long long*)device_buffer; }
 // Diagnostics hook: choose between the 128x128 state tiles (1, default) and the 64-wide ones (0).
 extern "C" void fpb_debug_tile_pref(int wide) { g_tile_pref = wide; }
-// Diagnostics hook for timing experiments: leave out parts of the work (1 V scaling, 2 output staging/store,
-// 4 state copy, 8 P' writes).  Results are wrong while any bit is set.
-extern "C" void fpb_debug_skip(int mask) { g_skip = mask; }
 // Diagnostics hook: 0 runs the dV and dK walks as two launches instead of the fused reverse kernel.
 extern "C" void fpb_debug_fused_bwd(int on) { g_fused_bwd = on; }
 
