@@ -373,14 +373,21 @@ def main():
     if not args.no_e2e:
         outs_host = [torch.empty_like(hv).pin_memory(), torch.empty_like(hq).pin_memory(),
                      torch.empty_like(hk).pin_memory(), torch.empty_like(hv).pin_memory()]
+        if w["block"]:
+            def e2e_step():
+                nonlocal q, k, v, dO
+                q.copy_(hq, non_blocking=True); k.copy_(hk, non_blocking=True)
+                v.copy_(hv, non_blocking=True); dO.copy_(hdO, non_blocking=True)
+                res = step()
+                for dst, src in zip(outs_host, res):
+                    dst.copy_(src, non_blocking=True)
+        else:
+            # the package's host-memory helper: batch slices, copies in / kernels / copies out on three streams
+            from flash_pop_b200.host_io import HostRetentionPipeline
+            pipe = HostRetentionPipeline(hq, hv, dev)
 
-        def e2e_step():
-            nonlocal q, k, v, dO
-            q.copy_(hq, non_blocking=True); k.copy_(hk, non_blocking=True)
-            v.copy_(hv, non_blocking=True); dO.copy_(hdO, non_blocking=True)
-            res = step()
-            for dst, src in zip(outs_host, res):
-                dst.copy_(src, non_blocking=True)
+            def e2e_step():
+                pipe.run(hq, hk, hv, hdO, dec, *outs_host)
 
         e2e_step()
         barrier()
