@@ -39,7 +39,7 @@ WORKLOADS = {
     "small": dict(B=2, H=16, T=8192, dk=128, dv=128, block=0),
 }
 # BASELINE config 5: the full RetNet stack under data parallelism (global batch fixed: strong scaling)
-STACK = dict(layers=12, heads=8, head_dim=128, ffn=4096, vocab=32000, B=64, T=4096, micro_batch=4)
+STACK = dict(layers=12, heads=8, head_dim=128, ffn=4096, vocab=32000, B=64, T=4096, micro_batch=32)
 CHUNK = 64
 
 
@@ -171,6 +171,60 @@ def run_reference(args, w, rank):
     print(json.dumps(line), flush=True)
 
 
+def run_decode(args):
+    """Recurrent decoding step over a (layers, B, H, dk, dv) state set: one kernel launch per layer per token, the
+    token's launches captured in a CUDA graph (the loop is launch-bound from Python otherwise).
+    Metric: state bytes streamed per second (read + write), against the measured HBM copy bandwidth."""
+    from flash_pop_b200 import _lib, retention_step
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "the decoding-step workload is reported for the CUDA "
+                          "kernel only; the reference arm covers the operator workloads"}))
+        return
+    dev = torch.device("cuda", 0)
+    L, B, H, d = 12, 256, 8, 128
+    dec = decays_for(H)
+    g = torch.Generator().manual_seed(6)
+    q, k, v = ((torch.randn(L, B, H, d, generator=g) * d ** -0.5).to(torch.bfloat16).to(dev) for _ in range(3))
+    out = {}
+    for name, sdt in (("bf16", torch.bfloat16), ("f32", torch.float32)):
+        states = [torch.zeros(B, H, d, d, device=dev, dtype=sdt) for _ in range(L)]
+
+        def token():
+            for l in range(L):
+                retention_step(q[l], k[l], v[l], dec, states[l], in_place=True)
+        side = torch.cuda.Stream(dev)
+        with torch.cuda.stream(side):                      # warm up off the default stream, then capture one token
+            for _ in range(args.warmup):
+                token()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        n0 = _lib.launch_count()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            token()
+        launches = (_lib.launch_count() - n0) * args.steps  # the graph replays the captured launches every step
+        for _ in range(3):
+            graph.replay()
+        ms = event_time_ms(graph.replay, args.steps)
+        nbytes = 2 * L * B * H * d * d * states[0].element_size()
+        out[name] = {"ms_per_token": ms, "gbs": nbytes / (ms * 1e-3) / 1e9, "bytes": nbytes, "launches": launches}
+    try:
+        peak = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"]; src = "measured"
+    except Exception:
+        peak = 6650.0; src = "fallback"
+    top = out["bf16"]
+    print(json.dumps({
+        "metric": "retention_decode_step_state_gbs", "value": top["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": top["ms_per_token"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"recurrent decoding step, {L} layers x B={B} H={H} dk=dv={d}, bf16 activations, "
+                               f"bf16 state updated in place (fp32 state beside it)",
+                   "l2": f"state set {top['bytes'] // 2 / 1e6:.0f} MB per token, larger than L2"},
+        "roofline": {"bound": "hbm", "achieved": top["gbs"], "peak": peak, "unit": "GB/s", "frac": top["gbs"] / peak,
+                     "peak_source": src, "traffic": None},
+        "f32_state": out["f32"], "tokens_per_s": B / (top["ms_per_token"] * 1e-3), "gpu_launches": top["launches"],
+    }), flush=True)
+
+
 def workload_name(args, w):
     kind = "POP retention" if w["block"] else "chunked retention"
     return (f"{kind} fwd+bwd bf16 B={w['B']} H={w['H']} T={w['T']} dk={w['dk']} dv={w['dv']} C={CHUNK}"
@@ -202,7 +256,7 @@ def run_stack(args):
     net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], gradient_as_bucket_view=True) if world > 1 else model
     opt = torch.optim.AdamW(model.parameters(), lr=1e-4, fused=True)
     rows = c["B"] // world
-    mb = min(c["micro_batch"], rows)
+    mb = min(args.micro_batch or c["micro_batch"], rows)
     g = torch.Generator().manual_seed(5 + rank)
     host_tokens = torch.randint(0, c["vocab"], (rows, c["T"] + 1), generator=g).pin_memory()
     tokens = torch.empty_like(host_tokens, device=dev)
@@ -285,13 +339,16 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="ns", choices=sorted(WORKLOADS) + ["c5"])
+    ap.add_argument("--workload", default="ns", choices=sorted(WORKLOADS) + ["c5", "decode"])
+    ap.add_argument("--micro-batch", type=int, default=0, help="c5 only: rows per micro-batch (0 = the workload's default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.workload == "c5":
         return run_stack(args)
+    if args.workload == "decode":
+        return run_decode(args)
     w = WORKLOADS[args.workload]
 
     rank = int(os.environ.get("RANK", "0"))

@@ -92,6 +92,7 @@ _SIGNATURES = {
     "fpb_pop_suffix_bwd": [_DIMS_P, ctypes.c_int32, ctypes.c_int32, _SEQ_P, _SEQ_P, _SEQ_P, _STATE_P,
                            ctypes.c_void_p, _SEQ_P, _SEQ_P, _SEQ_P, _SEQ_P, _STATE_P, ctypes.c_void_p,
                            ctypes.c_void_p],
+    "fpb_retention_step": [_DIMS_P, ctypes.c_int32, _SEQ_P, _SEQ_P, _SEQ_P, _STATE_P, _SEQ_P, _STATE_P, ctypes.c_void_p],
     "fpb_device_status": [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)],
 }
 

@@ -319,6 +319,23 @@ int fpb_pop_suffix_bwd(const fpb_dims* dims, int32_t M, int32_t N, const fpb_seq
                   SuffixStates{M, N, d_block_states}, (cudaStream_t)stream);
 }
 
+int fpb_retention_step(const fpb_dims* dims, int32_t state_dtype, const fpb_seq* q, const fpb_seq* k, const fpb_seq* v,
+                       const fpb_state* s_prev, const fpb_seq* o, const fpb_state* s_out, fpb_stream_t stream) {
+  Call c;
+  FPB_TRY(check_dims(dims, false, &c));
+  if (c.T != 1) return FPB_ERR_BAD_SHAPE;
+  if (state_dtype != FPB_BF16 && state_dtype != FPB_F32) return FPB_ERR_BAD_DTYPE;
+  if ((int64_t)c.B * c.H > 0x7fffffff) return FPB_ERR_TOO_LARGE;
+  FPB_TRY(check_seq(c, q, c.dk, c.B)); FPB_TRY(check_seq(c, k, c.dk, c.B));
+  FPB_TRY(check_seq(c, v, c.dv, c.B)); FPB_TRY(check_seq(c, o, c.dv, c.B));
+  FPB_TRY(check_state(s_prev, c)); FPB_TRY(check_state(s_out, c));
+  FPB_TRY(check_device());
+  if (c.B == 0 || c.H == 0) return FPB_OK;
+  launch_retention_step(c.dtype, state_dtype, c.B, c.H, c.dk, c.dv, c.gamma, view(q), view(k), view(v), view(o),
+                        view(s_prev), view(s_out), (cudaStream_t)stream);
+  return finish_launches(1, FPB_PATH_SIMT);
+}
+
 const char* fpb_strerror(int status) {
   switch (status) {
     case FPB_OK: return "ok";

@@ -49,6 +49,10 @@ struct WalkParams {
 
 int launch_walk(const WalkParams& p, int dtype, int B, cudaStream_t stream);
 
+// One recurrent decoding step (retention_step.cu); `dtype` is that of q, k, v, o, `state_dtype` that of the states.
+int launch_retention_step(int dtype, int state_dtype, int B, int H, int dk, int dv, const float* gamma, SeqView q,
+                          SeqView k, SeqView v, SeqView o, StateView s_prev, StateView s_out, cudaStream_t stream);
+
 // Device status word shared by all kernels: 0 = fine; otherwise (role << 8 | barrier id) of the
 // first bounded wait that gave up.
 int32_t* device_status_ptr();

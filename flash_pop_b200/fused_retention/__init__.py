@@ -99,3 +99,38 @@ class FusedChunkRetention(torch.autograd.Function):
 
 
 fused_chunk_retention = FusedChunkRetention.apply
+
+
+def retention_step(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, head_decays: Sequence[float],
+                   prev_state: Optional[torch.Tensor] = None, *, state_dtype: Optional[torch.dtype] = None,
+                   in_place: bool = False):
+    """One recurrent decoding step, S = gamma S_prev + k^T v / sqrt(dk), o = q S, as one streaming kernel over the
+    state (the reference's ``retention_recurrent``, flash_pop/retnet.py:79-101).
+
+    q, k: (B, H, dk); v: (B, H, dv); prev_state: (B, H, dk, dv) or None (zeros).  Returns (o (B, H, dv), state).
+    The state's element type is ``state_dtype``, else that of ``prev_state``, else that of q; with ``in_place`` the
+    new state overwrites ``prev_state``.  Inference only: no gradient is recorded."""
+    _lib.require_cuda(q, k, v, prev_state)
+    if q.dim() != 3 or k.shape != q.shape or v.dim() != 3 or v.shape[:2] != q.shape[:2]:
+        raise ValueError(f"expected q,k (B,H,dk) and v (B,H,dv); got {tuple(q.shape)}, {tuple(k.shape)}, {tuple(v.shape)}")
+    B, H, dk = q.shape
+    dv = v.shape[-1]
+    head_decays = tuple(float(g) for g in head_decays)
+    assert len(head_decays) == H, f"got {len(head_decays)} decays for {H} heads"
+    if not (q.dtype == k.dtype == v.dtype):
+        raise ValueError("q, k and v must share one dtype")
+    if prev_state is not None and tuple(prev_state.shape) != (B, H, dk, dv):
+        raise ValueError(f"state must be (B,H,dk,dv)={(B, H, dk, dv)}, got {tuple(prev_state.shape)}")
+    sdt = state_dtype or (prev_state.dtype if prev_state is not None else q.dtype)
+    if prev_state is not None and prev_state.dtype != sdt:
+        prev_state, in_place = prev_state.to(sdt), False
+    prev_state = _lib.state_tensor(prev_state)
+    q4, k4, v4 = (_lib.unit_inner(t.detach()).unsqueeze(1) for t in (q, k, v))
+    o = torch.empty((B, 1, H, dv), device=q.device, dtype=q.dtype)
+    state = prev_state if (in_place and prev_state is not None) else torch.empty((B, H, dk, dv), device=q.device, dtype=sdt)
+    with torch.cuda.device(q.device):
+        d = _lib.dims(q4, dv, head_decays)
+        _lib.check(_lib.lib().fpb_retention_step(d, _lib.dtype_code(state), _lib.seq(q4), _lib.seq(k4), _lib.seq(v4),
+                                                 _lib.state(None if prev_state is None else prev_state.detach()),
+                                                 _lib.seq(o), _lib.state(state), _lib.stream_ptr(q.device)))
+    return o.squeeze(1), state

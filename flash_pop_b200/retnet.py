@@ -25,7 +25,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 from torch import Tensor
 
-from flash_pop_b200.fused_retention import cuda_core_kernels, fused_chunk_retention
+from flash_pop_b200.fused_retention import cuda_core_kernels, fused_chunk_retention, retention_step
 from flash_pop_b200.recurrent_state import RecurrentState
 from flash_pop_b200.xpos_emb import XPos
 
@@ -49,10 +49,25 @@ def get_decays(num_heads: int, decay_range: Optional[Tuple[float, float]] = None
 
 
 def retention_recurrent(query: Tensor, key: Tensor, value: Tensor, head_decays: Tensor, prev_state: Optional[Tensor],
-                        scale: Optional[float] = None) -> Tuple[Tensor, Tensor]:
+                        scale: Optional[float] = None, decays: Optional[Tuple[float, ...]] = None) -> Tuple[Tensor, Tensor]:
     """One decoding step: S = gamma S_prev + k^T v / sqrt(dk); o = q S.  q, k: (B,H,dk), v: (B,H,dv),
-    head_decays: (1,H,1,1).  (flash_pop/retnet.py:79-101)"""
+    head_decays: (1,H,1,1).  (flash_pop/retnet.py:79-101)
+
+    On CUDA tensors outside autograd this is the library's streaming step kernel (``decays``: the same decays as
+    Python floats, which saves reading ``head_decays`` back from the device); where a gradient is being recorded it
+    is the differentiable PyTorch expression."""
     assert head_decays.dim() == 4 and head_decays.shape[0] == 1 and head_decays.shape[2:] == (1, 1)
+    needs_grad = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (query, key, value, prev_state))
+    if query.is_cuda and not needs_grad and scale is None and query.dtype in (torch.bfloat16, torch.float32):
+        common = torch.promote_types(torch.promote_types(query.dtype, key.dtype), value.dtype)
+        if common in (torch.bfloat16, torch.float32):
+            if decays is None:
+                decays = tuple(head_decays.flatten().tolist())
+            state_dtype = common if prev_state is None else torch.promote_types(prev_state.dtype, head_decays.dtype)
+            if state_dtype not in (torch.bfloat16, torch.float32):
+                state_dtype = torch.float32
+            return retention_step(query.to(common), key.to(common), value.to(common), decays, prev_state,
+                                  state_dtype=state_dtype)
     key = key / (key.size(-1) ** 0.5 if scale is None else scale)
     state = key.unsqueeze(-1) * value.unsqueeze(-2)
     if prev_state is not None:
@@ -161,7 +176,8 @@ class MultiScaleRetention(nn.Module):
         v = _split_heads(self.v_proj(x), self.num_heads)
         if self.relative_position:
             q, k = self.xpos_embedder(q, k, seq_idx)
-        retention, state = retention_recurrent(q, k, v, self.head_decays_torch.to(x.device), prev_state=prev_state)
+        retention, state = retention_recurrent(q, k, v, self.head_decays_torch.to(x.device), prev_state=prev_state,
+                                               decays=self.head_decays)
         return self._gate_and_project(retention, x), state
 
 

@@ -133,6 +133,20 @@ int fpb_pop_suffix_bwd(const fpb_dims* dims, int32_t M, int32_t N, const fpb_seq
                        const fpb_seq* d_q, const fpb_seq* d_k, const fpb_seq* d_v, const fpb_state* d_s0,
                        void* d_block_states, fpb_stream_t stream);
 
+/*
+ * One recurrent decoding step for B rows of one token each:
+ *   s_out = gamma s_prev + k^T v / sqrt(dk),   o = q s_out
+ * q, k are (B, 1, H, dk) and v, o (B, 1, H, dv): dims->T must be 1 and stride_t is not read.  The states have
+ * their own element type `state_dtype` (an fp32 state under bf16 activations is not re-rounded every token);
+ * s_prev->data == NULL means a zero state, s_out may be the same memory as s_prev (update in place) and
+ * s_out->data == NULL drops the new state.  Arithmetic is fp32.
+ * Replaces retention_recurrent (flash_pop/retnet.py:79-101) as MultiScaleRetention.forward_recurrent calls it
+ * (flash_pop/retnet.py:325-366).
+ */
+int fpb_retention_step(const fpb_dims* dims, int32_t state_dtype, const fpb_seq* q, const fpb_seq* k,
+                       const fpb_seq* v, const fpb_state* s_prev, const fpb_seq* o, const fpb_state* s_out,
+                       fpb_stream_t stream);
+
 /* Text for a status code. */
 const char* fpb_strerror(int status);
 /* Library version, major*10000 + minor*100 + patch. */
