@@ -93,6 +93,10 @@ _SIGNATURES = {
                            ctypes.c_void_p, _SEQ_P, _SEQ_P, _SEQ_P, _SEQ_P, _STATE_P, ctypes.c_void_p,
                            ctypes.c_void_p],
     "fpb_retention_step": [_DIMS_P, ctypes.c_int32, _SEQ_P, _SEQ_P, _SEQ_P, _STATE_P, _SEQ_P, _STATE_P, ctypes.c_void_p],
+    "fpb_rotary": [ctypes.c_int32] * 7 + [ctypes.c_void_p, ctypes.c_int64, _SEQ_P, _SEQ_P, _SEQ_P, _SEQ_P, ctypes.c_void_p],
+    "fpb_groupnorm_gate_fwd": [ctypes.c_int32] * 5 + [ctypes.c_float, ctypes.c_int32, _SEQ_P, _SEQ_P, _SEQ_P, ctypes.c_void_p],
+    "fpb_groupnorm_gate_bwd": [ctypes.c_int32] * 5 + [ctypes.c_float, ctypes.c_int32, _SEQ_P, _SEQ_P, _SEQ_P, _SEQ_P, _SEQ_P,
+                               ctypes.c_void_p],
     "fpb_device_status": [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)],
 }
 

@@ -104,7 +104,7 @@ int finish_launches(int n, int path) {
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { tl_last_cuda_error = (int)e; return FPB_ERR_LAUNCH; }
   g_launches.fetch_add(n);
-  tl_last_path = path;
+  if (path >= 0) tl_last_path = path;   // the elementwise entry points pass -1 and leave the operator's record alone
   return FPB_OK;
 }
 
@@ -334,6 +334,67 @@ int fpb_retention_step(const fpb_dims* dims, int32_t state_dtype, const fpb_seq*
   launch_retention_step(c.dtype, state_dtype, c.B, c.H, c.dk, c.dv, c.gamma, view(q), view(k), view(v), view(o),
                         view(s_prev), view(s_out), (cudaStream_t)stream);
   return finish_launches(1, FPB_PATH_SIMT);
+}
+
+namespace {
+// shapes and alignment of a (B,T,H,d) tensor read or written `vec` elements at a time
+int check_plain_seq(const fpb_seq* s, int dtype, int B, int T, int H, int d, int vec_bytes) {
+  if (!s) return FPB_ERR_NULL_POINTER;
+  if (B == 0 || T == 0 || H == 0) return FPB_OK;
+  if (!s->data) return FPB_ERR_NULL_POINTER;
+  const int64_t vec = vec_bytes / (dtype == FPB_F32 ? 4 : 2);
+  if ((B > 1 && s->stride_b <= 0) || (T > 1 && s->stride_t <= 0) || (H > 1 && s->stride_h < d)) return FPB_ERR_BAD_STRIDE;
+  if ((uintptr_t)s->data % vec_bytes || s->stride_b % vec || s->stride_t % vec || s->stride_h % vec) return FPB_ERR_BAD_STRIDE;
+  return FPB_OK;
+}
+bool dtype_ok(int t) { return t == FPB_BF16 || t == FPB_F32; }
+}  // namespace
+
+int fpb_rotary(int32_t B, int32_t T, int32_t H, int32_t d, int32_t in_dtype, int32_t out_dtype, int32_t conjugate,
+               const float* phasors, int64_t phasor_stride_b, const fpb_seq* q_in, const fpb_seq* k_in,
+               const fpb_seq* q_out, const fpb_seq* k_out, fpb_stream_t stream) {
+  if (B < 0 || T < 0 || H < 0 || d <= 0 || d % 8) return FPB_ERR_BAD_SHAPE;
+  if (!dtype_ok(in_dtype) || !dtype_ok(out_dtype)) return FPB_ERR_BAD_DTYPE;
+  if ((int64_t)B * T * H * d > 0 && !phasors) return FPB_ERR_NULL_POINTER;
+  if ((uintptr_t)phasors % 16 || phasor_stride_b % 2 || phasor_stride_b < 0) return FPB_ERR_BAD_STRIDE;
+  FPB_TRY(check_plain_seq(q_in, in_dtype, B, T, H, d, 16)); FPB_TRY(check_plain_seq(q_out, out_dtype, B, T, H, d, 16));
+  const bool two = k_in && k_in->data;
+  if (two) { FPB_TRY(check_plain_seq(k_in, in_dtype, B, T, H, d, 16)); FPB_TRY(check_plain_seq(k_out, out_dtype, B, T, H, d, 16)); }
+  FPB_TRY(check_device());
+  if ((int64_t)B * T * H == 0) return FPB_OK;
+  const SeqView in[2] = {view(q_in), two ? view(k_in) : view(q_in)}, out[2] = {view(q_out), two ? view(k_out) : view(q_out)};
+  launch_rotary(in_dtype, out_dtype, B, T, H, d, conjugate != 0, phasors, phasor_stride_b, in, out, two ? 2 : 1, (cudaStream_t)stream);
+  return finish_launches(1, -1);
+}
+
+int fpb_groupnorm_gate_fwd(int32_t B, int32_t T, int32_t H, int32_t dv, int32_t dtype, float eps, int32_t swish,
+                           const fpb_seq* o, const fpb_seq* z, const fpb_seq* y, fpb_stream_t stream) {
+  if (B < 0 || T < 0 || H < 0 || dv <= 0 || dv % 2 || dv > 256) return FPB_ERR_BAD_SHAPE;
+  if (!dtype_ok(dtype)) return FPB_ERR_BAD_DTYPE;
+  const int vb = dtype == FPB_F32 ? 8 : 4;
+  FPB_TRY(check_plain_seq(o, dtype, B, T, H, dv, vb)); FPB_TRY(check_plain_seq(z, dtype, B, T, H, dv, vb));
+  FPB_TRY(check_plain_seq(y, dtype, B, T, H, dv, vb));
+  FPB_TRY(check_device());
+  if ((int64_t)B * T * H == 0) return FPB_OK;
+  const SeqView none{nullptr, 0, 0, 0};
+  launch_gn_gate(dtype, false, B, T, H, dv, eps, swish != 0, view(o), view(z), view(y), none, none, none, (cudaStream_t)stream);
+  return finish_launches(1, -1);
+}
+
+int fpb_groupnorm_gate_bwd(int32_t B, int32_t T, int32_t H, int32_t dv, int32_t dtype, float eps, int32_t swish,
+                           const fpb_seq* o, const fpb_seq* z, const fpb_seq* d_y, const fpb_seq* d_o, const fpb_seq* d_z,
+                           fpb_stream_t stream) {
+  if (B < 0 || T < 0 || H < 0 || dv <= 0 || dv % 2 || dv > 256) return FPB_ERR_BAD_SHAPE;
+  if (!dtype_ok(dtype)) return FPB_ERR_BAD_DTYPE;
+  const int vb = dtype == FPB_F32 ? 8 : 4;
+  FPB_TRY(check_plain_seq(o, dtype, B, T, H, dv, vb)); FPB_TRY(check_plain_seq(z, dtype, B, T, H, dv, vb));
+  FPB_TRY(check_plain_seq(d_y, dtype, B, T, H, dv, vb)); FPB_TRY(check_plain_seq(d_o, dtype, B, T, H, dv, vb));
+  FPB_TRY(check_plain_seq(d_z, dtype, B, T, H, dv, vb));
+  FPB_TRY(check_device());
+  if ((int64_t)B * T * H == 0) return FPB_OK;
+  const SeqView none{nullptr, 0, 0, 0};
+  launch_gn_gate(dtype, true, B, T, H, dv, eps, swish != 0, view(o), view(z), none, view(d_y), view(d_o), view(d_z), (cudaStream_t)stream);
+  return finish_launches(1, -1);
 }
 
 const char* fpb_strerror(int status) {

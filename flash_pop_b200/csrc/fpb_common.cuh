@@ -53,6 +53,12 @@ int launch_walk(const WalkParams& p, int dtype, int B, cudaStream_t stream);
 int launch_retention_step(int dtype, int state_dtype, int B, int H, int dk, int dv, const float* gamma, SeqView q,
                           SeqView k, SeqView v, SeqView o, StateView s_prev, StateView s_out, cudaStream_t stream);
 
+// Fused elementwise passes around the operator (layer_fused.cu).
+int launch_rotary(int in_dtype, int out_dtype, int B, int T, int H, int d, bool conjugate, const float* phasors,
+                  int64_t phasor_stride_b, const SeqView in[2], const SeqView out[2], int n_tensors, cudaStream_t stream);
+int launch_gn_gate(int dtype, bool backward, int B, int T, int H, int dv, float eps, bool swish, SeqView o, SeqView z,
+                   SeqView y, SeqView dy, SeqView d_o, SeqView d_z, cudaStream_t stream);
+
 // Device status word shared by all kernels: 0 = fine; otherwise (role << 8 | barrier id) of the
 // first bounded wait that gave up.
 int32_t* device_status_ptr();

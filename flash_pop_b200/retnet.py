@@ -26,6 +26,7 @@ import torch.nn.functional as F
 from torch import Tensor
 
 from flash_pop_b200.fused_retention import cuda_core_kernels, fused_chunk_retention, retention_step
+from flash_pop_b200.layer_ops import groupnorm_gate, groupnorm_gate_supported
 from flash_pop_b200.recurrent_state import RecurrentState
 from flash_pop_b200.xpos_emb import XPos
 
@@ -145,11 +146,19 @@ class MultiScaleRetention(nn.Module):
     def _gate_and_project(self, retention: Tensor, x: Tensor) -> Tensor:
         """GroupNorm over each head of each token (fp32), swish gate, output projection."""
         shape = retention.shape[:-2]
+        dropping = self.dropout > 0 and self.training
+        z = self.g_proj(x)
+        o4 = retention.reshape(-1, 1, self.num_heads, self.head_dim_v) if retention.dim() == 3 else retention
+        if retention.dim() in (3, 4) and not dropping and z.dtype == retention.dtype:
+            z4 = z.reshape(o4.shape)
+            if groupnorm_gate_supported(o4, z4):
+                swish = self.activation is F.silu
+                gated = groupnorm_gate(o4, z4 if swish else self.activation(z4), self.group_norm.eps, swish)
+                return self.out_proj(gated.reshape(*shape, self.embed_dim))
         flat = retention.reshape(-1, self.embed_dim)
         flat = F.dropout(flat, p=self.dropout, training=self.training)
         flat = self.group_norm(flat.float()).to(dtype=x.dtype)
-        gate = self.activation(self.g_proj(x))
-        return self.out_proj(flat.view(*shape, self.embed_dim) * gate)
+        return self.out_proj(flat.view(*shape, self.embed_dim) * self.activation(z))
 
     def _retention_chunkwise(self, x: Tensor, start_idx: Union[int, torch.LongTensor], prev_state: Optional[Tensor] = None,
                              retention_kernel: Optional[Callable] = None, xpos_embedder: Optional[XPos] = None):

@@ -3,8 +3,9 @@
 Same call and numerics as the reference's ``XPos`` (flash_pop/xpos_emb.py:12-129): channel pairs
 (2i, 2i+1) are rotated by the angle ``position * theta_i`` with ``theta_i = 10000^(-linspace(0,1,d/2))``;
 ``start_idx`` is an int (all rows share the offset) or a LongTensor with one offset per batch row (the
-POP suffixes, whose rows start at different positions).  Computed in fp32, eagerly, as a complex
-multiplication; sin/cos tables are cached and grown on demand.
+POP suffixes, whose rows start at different positions).  Computed in fp32 from cached phasor tables that grow on
+demand: on CUDA tensors by the library's rotation kernel (q and k in one launch), elsewhere as an eager complex
+multiplication.
 """
 from __future__ import annotations
 
@@ -12,6 +13,8 @@ from typing import Optional, Union
 
 import torch
 from torch import Tensor
+
+from flash_pop_b200.layer_ops import rotary_qk, rotary_supported
 
 
 class XPos:
@@ -25,6 +28,7 @@ class XPos:
         self._rows_key: Optional[Tensor] = None
         self._rows_table: Optional[Tensor] = None
         self.seq_len = 0
+        self.fused = True            # CUDA tensors take the library's rotation kernel
         self._grow(seq_len_estimate)
 
     # -- tables -------------------------------------------------------------------------------------
@@ -73,4 +77,7 @@ class XPos:
         self._move(q.device)
         seq_len = q.size(1) if q.dim() == 4 else 1
         ph = self._rotation(seq_len, start_idx)
+        if self.fused and rotary_supported(q) and k.shape == q.shape:
+            # one kernel for both tensors (and one for their gradients) instead of the eager complex product
+            return rotary_qk(q, k, torch.view_as_real(ph).contiguous())
         return self._rotate(q, ph), self._rotate(k, ph)

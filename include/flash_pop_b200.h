@@ -147,11 +147,37 @@ int fpb_retention_step(const fpb_dims* dims, int32_t state_dtype, const fpb_seq*
                        const fpb_seq* v, const fpb_state* s_prev, const fpb_seq* o, const fpb_state* s_out,
                        fpb_stream_t stream);
 
+/*
+ * The two elementwise passes of a retention layer either side of the operator, each as one streaming kernel
+ * (fp32 arithmetic).  They replace PyTorch expressions of the reference rather than kernels of its own.
+ *
+ * fpb_rotary: rotates the channel pairs (2i, 2i+1) of q and k (B, T, H, d), d a multiple of 8, by the unit phasors
+ * phasors[b, t, i] = (cos, sin) — a device array of (rows, T, d/2, 2) floats, `phasor_stride_b` floats-pairs between
+ * batch rows or 0 when all rows share one table — and writes them as `out_dtype`.  conjugate != 0 rotates by the
+ * negative angle (the backward pass).  k_in / k_out may be NULL to rotate one tensor.  Tensors and strides must be
+ * 16-byte aligned.  Replaces XPos.__call__ / _theta_shift (flash_pop/xpos_emb.py:32-40,120-126) and the cast that
+ * follows it (flash_pop/retnet.py:268-290).
+ *
+ * fpb_groupnorm_gate_fwd: y = GroupNorm_head(o) * gate, GroupNorm over the dv channels of each (row, token, head)
+ * with biased variance, eps inside the square root and no affine parameters; gate = z * sigmoid(z) when swish != 0,
+ * else z itself (the caller applied another activation).  dv even, at most 256.  Replaces the GroupNorm, casts,
+ * activation and product of MultiScaleRetention (flash_pop/retnet.py:294-309).
+ * fpb_groupnorm_gate_bwd: from d_y writes d_o and d_z.
+ */
+int fpb_rotary(int32_t B, int32_t T, int32_t H, int32_t d, int32_t in_dtype, int32_t out_dtype, int32_t conjugate,
+               const float* phasors, int64_t phasor_stride_b, const fpb_seq* q_in, const fpb_seq* k_in,
+               const fpb_seq* q_out, const fpb_seq* k_out, fpb_stream_t stream);
+int fpb_groupnorm_gate_fwd(int32_t B, int32_t T, int32_t H, int32_t dv, int32_t dtype, float eps, int32_t swish,
+                           const fpb_seq* o, const fpb_seq* z, const fpb_seq* y, fpb_stream_t stream);
+int fpb_groupnorm_gate_bwd(int32_t B, int32_t T, int32_t H, int32_t dv, int32_t dtype, float eps, int32_t swish,
+                           const fpb_seq* o, const fpb_seq* z, const fpb_seq* d_y, const fpb_seq* d_o,
+                           const fpb_seq* d_z, fpb_stream_t stream);
+
 /* Text for a status code. */
 const char* fpb_strerror(int status);
 /* Library version, major*10000 + minor*100 + patch. */
 int fpb_version(void);
-/* Which implementation the last successful call on this host thread launched (fpb_path). */
+/* Which implementation the last successful retention / POP / decoding-step call on this host thread launched (fpb_path). */
 int fpb_last_path(void);
 /* The cudaError_t behind the last FPB_ERR_LAUNCH on this host thread. */
 int fpb_last_cuda_error(void);
