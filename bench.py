@@ -225,6 +225,52 @@ def run_decode(args):
     }), flush=True)
 
 
+def run_layer_passes(args):
+    """The fused elementwise passes of a retention layer at the full-stack shape (16 x 4096 tokens, 8 heads of 128):
+    GB/s of each kernel over its algorithmic bytes (every tensor read or written once)."""
+    from flash_pop_b200 import _lib
+    from flash_pop_b200.layer_ops import _rotate, groupnorm_gate
+    from flash_pop_b200.xpos_emb import XPos
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "the layer-pass workload is reported for the CUDA kernels "
+                          "only; the reference arm covers the operator workloads"}))
+        return
+    dev = torch.device("cuda", 0)
+    B, T, H, d = 16, 4096, 8, 128
+    g = torch.Generator().manual_seed(7)
+    q, k, o, z, dy = (torch.randn(B, T, H, d, generator=g).to(torch.bfloat16).to(dev) for _ in range(5))
+    ph = torch.view_as_real(XPos(d, seq_len_estimate=T, device=dev)._rotation(T, 0)).contiguous()
+    tensor_bytes = q.numel() * 2
+    o.requires_grad_(True); z.requires_grad_(True)
+    y = groupnorm_gate(o, z, 1e-6, True)
+    cases = {
+        "rotary (q and k)": (lambda: _rotate(q, k, ph, False, torch.bfloat16), 4 * tensor_bytes),
+        "groupnorm_gate forward": (lambda: groupnorm_gate(o.detach(), z.detach(), 1e-6, True), 3 * tensor_bytes),
+        "groupnorm_gate backward": (lambda: torch.autograd.grad(y, (o, z), dy, retain_graph=True), 5 * tensor_bytes),
+    }
+    try:
+        peak = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"]; src = "measured"
+    except Exception:
+        peak = 6650.0; src = "fallback"
+    out, n0 = {}, _lib.launch_count()
+    for name, (fn, nbytes) in cases.items():
+        for _ in range(args.warmup):
+            fn()
+        ms = event_time_ms(fn, args.steps)
+        out[name] = {"ms": ms, "gbs": nbytes / (ms * 1e-3) / 1e9, "frac": nbytes / (ms * 1e-3) / 1e9 / peak, "bytes": nbytes}
+    top = out["groupnorm_gate backward"]
+    print(json.dumps({
+        "metric": "layer_pass_gbs", "value": top["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": top["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": f"fused layer passes, bf16 (B,T,H,d)=({B},{T},{H},{d}); value = GroupNorm-gate backward",
+                   "l2": f"each tensor {tensor_bytes / 1e6:.0f} MB, every pass moves 3-5 of them: larger than L2"},
+        "roofline": {"bound": "hbm", "achieved": top["gbs"], "peak": peak, "unit": "GB/s", "frac": top["frac"],
+                     "peak_source": src, "traffic": None},
+        "passes": out, "gpu_launches": _lib.launch_count() - n0,
+    }), flush=True)
+
+
 def workload_name(args, w):
     kind = "POP retention" if w["block"] else "chunked retention"
     return (f"{kind} fwd+bwd bf16 B={w['B']} H={w['H']} T={w['T']} dk={w['dk']} dv={w['dv']} C={CHUNK}"
@@ -339,7 +385,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="ns", choices=sorted(WORKLOADS) + ["c5", "decode"])
+    ap.add_argument("--workload", default="ns", choices=sorted(WORKLOADS) + ["c5", "decode", "layer"])
     ap.add_argument("--micro-batch", type=int, default=0, help="c5 only: rows per micro-batch (0 = the workload's default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -349,6 +395,8 @@ def main():
         return run_stack(args)
     if args.workload == "decode":
         return run_decode(args)
+    if args.workload == "layer":
+        return run_layer_passes(args)
     w = WORKLOADS[args.workload]
 
     rank = int(os.environ.get("RANK", "0"))

@@ -354,6 +354,7 @@ int fpb_rotary(int32_t B, int32_t T, int32_t H, int32_t d, int32_t in_dtype, int
                const float* phasors, int64_t phasor_stride_b, const fpb_seq* q_in, const fpb_seq* k_in,
                const fpb_seq* q_out, const fpb_seq* k_out, fpb_stream_t stream) {
   if (B < 0 || T < 0 || H < 0 || d <= 0 || d % 8) return FPB_ERR_BAD_SHAPE;
+  if ((int64_t)B * T * H * (d / 8) >= (1ll << 31)) return FPB_ERR_TOO_LARGE;
   if (!dtype_ok(in_dtype) || !dtype_ok(out_dtype)) return FPB_ERR_BAD_DTYPE;
   if ((int64_t)B * T * H * d > 0 && !phasors) return FPB_ERR_NULL_POINTER;
   if ((uintptr_t)phasors % 16 || phasor_stride_b % 2 || phasor_stride_b < 0) return FPB_ERR_BAD_STRIDE;
@@ -370,6 +371,7 @@ int fpb_rotary(int32_t B, int32_t T, int32_t H, int32_t d, int32_t in_dtype, int
 int fpb_groupnorm_gate_fwd(int32_t B, int32_t T, int32_t H, int32_t dv, int32_t dtype, float eps, int32_t swish,
                            const fpb_seq* o, const fpb_seq* z, const fpb_seq* y, fpb_stream_t stream) {
   if (B < 0 || T < 0 || H < 0 || dv <= 0 || dv % 2 || dv > 256) return FPB_ERR_BAD_SHAPE;
+  if ((int64_t)B * T * H >= (1ll << 31)) return FPB_ERR_TOO_LARGE;
   if (!dtype_ok(dtype)) return FPB_ERR_BAD_DTYPE;
   const int vb = dtype == FPB_F32 ? 8 : 4;
   FPB_TRY(check_plain_seq(o, dtype, B, T, H, dv, vb)); FPB_TRY(check_plain_seq(z, dtype, B, T, H, dv, vb));
@@ -377,7 +379,11 @@ int fpb_groupnorm_gate_fwd(int32_t B, int32_t T, int32_t H, int32_t dv, int32_t 
   FPB_TRY(check_device());
   if ((int64_t)B * T * H == 0) return FPB_OK;
   const SeqView none{nullptr, 0, 0, 0};
-  launch_gn_gate(dtype, false, B, T, H, dv, eps, swish != 0, view(o), view(z), view(y), none, none, none, (cudaStream_t)stream);
+  const bool wide = dv % 4 == 0 && check_plain_seq(o, dtype, B, T, H, dv, 2 * vb) == FPB_OK &&
+                    check_plain_seq(z, dtype, B, T, H, dv, 2 * vb) == FPB_OK && check_plain_seq(y, dtype, B, T, H, dv, 2 * vb) == FPB_OK;
+  const bool packed = check_plain_seq(o, dtype, B, T, H, dv, 16) == FPB_OK && check_plain_seq(z, dtype, B, T, H, dv, 16) == FPB_OK &&
+                      check_plain_seq(y, dtype, B, T, H, dv, 16) == FPB_OK;
+  launch_gn_gate(dtype, false, wide, packed, B, T, H, dv, eps, swish != 0, view(o), view(z), view(y), none, none, none, (cudaStream_t)stream);
   return finish_launches(1, -1);
 }
 
@@ -385,6 +391,7 @@ int fpb_groupnorm_gate_bwd(int32_t B, int32_t T, int32_t H, int32_t dv, int32_t 
                            const fpb_seq* o, const fpb_seq* z, const fpb_seq* d_y, const fpb_seq* d_o, const fpb_seq* d_z,
                            fpb_stream_t stream) {
   if (B < 0 || T < 0 || H < 0 || dv <= 0 || dv % 2 || dv > 256) return FPB_ERR_BAD_SHAPE;
+  if ((int64_t)B * T * H >= (1ll << 31)) return FPB_ERR_TOO_LARGE;
   if (!dtype_ok(dtype)) return FPB_ERR_BAD_DTYPE;
   const int vb = dtype == FPB_F32 ? 8 : 4;
   FPB_TRY(check_plain_seq(o, dtype, B, T, H, dv, vb)); FPB_TRY(check_plain_seq(z, dtype, B, T, H, dv, vb));
@@ -393,7 +400,11 @@ int fpb_groupnorm_gate_bwd(int32_t B, int32_t T, int32_t H, int32_t dv, int32_t 
   FPB_TRY(check_device());
   if ((int64_t)B * T * H == 0) return FPB_OK;
   const SeqView none{nullptr, 0, 0, 0};
-  launch_gn_gate(dtype, true, B, T, H, dv, eps, swish != 0, view(o), view(z), none, view(d_y), view(d_o), view(d_z), (cudaStream_t)stream);
+  bool wide = dv % 4 == 0;
+  for (const fpb_seq* s : {o, z, d_y, d_o, d_z}) wide = wide && check_plain_seq(s, dtype, B, T, H, dv, 2 * vb) == FPB_OK;
+  bool packed = true;
+  for (const fpb_seq* s : {o, z, d_y, d_o, d_z}) packed = packed && check_plain_seq(s, dtype, B, T, H, dv, 16) == FPB_OK;
+  launch_gn_gate(dtype, true, wide, packed, B, T, H, dv, eps, swish != 0, view(o), view(z), none, view(d_y), view(d_o), view(d_z), (cudaStream_t)stream);
   return finish_launches(1, -1);
 }
 

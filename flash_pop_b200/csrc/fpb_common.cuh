@@ -56,8 +56,10 @@ int launch_retention_step(int dtype, int state_dtype, int B, int H, int dk, int 
 // Fused elementwise passes around the operator (layer_fused.cu).
 int launch_rotary(int in_dtype, int out_dtype, int B, int T, int H, int d, bool conjugate, const float* phasors,
                   int64_t phasor_stride_b, const SeqView in[2], const SeqView out[2], int n_tensors, cudaStream_t stream);
-int launch_gn_gate(int dtype, bool backward, int B, int T, int H, int dv, float eps, bool swish, SeqView o, SeqView z,
-                   SeqView y, SeqView dy, SeqView d_o, SeqView d_z, cudaStream_t stream);
+// `wide`: every tensor allows accesses of four elements (dv % 4 == 0, pointers and strides aligned for them);
+// `packed`: every tensor allows 16-byte accesses
+int launch_gn_gate(int dtype, bool backward, bool wide, bool packed, int B, int T, int H, int dv, float eps, bool swish, SeqView o,
+                   SeqView z, SeqView y, SeqView dy, SeqView d_o, SeqView d_z, cudaStream_t stream);
 
 // Device status word shared by all kernels: 0 = fine; otherwise (role << 8 | barrier id) of the
 // first bounded wait that gave up.

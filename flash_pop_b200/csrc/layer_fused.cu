@@ -5,6 +5,8 @@
 //   * gn_gate_fwd / gn_gate_bwd: GroupNorm over each head of each token, without affine parameters,
 //     times the (optionally swish-activated) gate (flash_pop/retnet.py:294-309), and its backward.
 // All three are HBM-bound: every element is read once and written once.
+#include <type_traits>
+
 #include "fpb_common.cuh"
 
 namespace fpb {
@@ -30,51 +32,61 @@ struct RotaryParams {
   float sign;                  // +1 rotates by the angle, -1 by its negative (the backward)
 };
 
-// One thread rotates four channel pairs (eight consecutive channels) of one (row, token, head).
+// One thread rotates four channel pairs (eight consecutive channels) of one (row, token, head).  A CTA takes whole
+// tokens: when a token's H*d/8 units fit its 256 threads, each thread keeps one (head, channel group) for the whole
+// launch and only the token changes from one pass to the next, so that the index arithmetic stays out of the loop.
+template <typename TIN, typename TOUT>
+__device__ __forceinline__ void rotate_unit(const RotaryParams& p, const SeqView& in, const SeqView& out, uint32_t b,
+                                            uint32_t t, uint32_t h, uint32_t c) {
+  const TIN* src = (const TIN*)in.data + b * in.sb + t * in.st + h * in.sh + c * 8;
+  TOUT* dst = (TOUT*)out.data + b * out.sb + t * out.st + h * out.sh + c * 8;
+  const float2* ph = p.phasors + b * p.ph_sb + (int64_t)t * (p.d / 2) + c * 4;
+  float2 x[4];
+  if constexpr (sizeof(TIN) == 2) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(src);
+    const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) x[i] = __bfloat1622float2(e[i]);
+  } else {
+    const float4 a = *reinterpret_cast<const float4*>(src), b4 = *reinterpret_cast<const float4*>(src + 4);
+    x[0] = make_float2(a.x, a.y); x[1] = make_float2(a.z, a.w); x[2] = make_float2(b4.x, b4.y); x[3] = make_float2(b4.z, b4.w);
+  }
+  const float4 w01 = __ldg(reinterpret_cast<const float4*>(ph)), w23 = __ldg(reinterpret_cast<const float4*>(ph + 2));
+  const float2 w[4] = {make_float2(w01.x, w01.y), make_float2(w01.z, w01.w), make_float2(w23.x, w23.y), make_float2(w23.z, w23.w)};
+  float2 y[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float s = p.sign * w[i].y;
+    y[i].x = x[i].x * w[i].x - x[i].y * s;
+    y[i].y = x[i].x * s + x[i].y * w[i].x;
+  }
+  if constexpr (sizeof(TOUT) == 2) {
+    uint4 raw;
+    __nv_bfloat162* e = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) e[i] = __float22bfloat162_rn(y[i]);
+    *reinterpret_cast<uint4*>(dst) = raw;
+  } else {
+    *reinterpret_cast<float4*>(dst) = make_float4(y[0].x, y[0].y, y[1].x, y[1].y);
+    *reinterpret_cast<float4*>(dst + 4) = make_float4(y[2].x, y[2].y, y[3].x, y[3].y);
+  }
+}
+
 template <typename TIN, typename TOUT>
 __global__ void __launch_bounds__(256) rotary_kernel(const __grid_constant__ RotaryParams p) {
-  const int which = blockIdx.y;
-  const int per_head = p.d / 8;
-  const int64_t total = (int64_t)p.B * p.T * p.H * per_head;
-  const SeqView in = p.in[which], out = p.out[which];
-  for (int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; u < total; u += (int64_t)gridDim.x * blockDim.x) {
-    const int c = (int)(u % per_head);
-    int64_t r = u / per_head;
-    const int h = (int)(r % p.H); r /= p.H;
-    const int t = (int)(r % p.T);
-    const int b = (int)(r / p.T);
-    const TIN* src = (const TIN*)in.data + b * in.sb + t * in.st + h * in.sh + c * 8;
-    TOUT* dst = (TOUT*)out.data + b * out.sb + t * out.st + h * out.sh + c * 8;
-    const float2* ph = p.phasors + b * p.ph_sb + (int64_t)t * (p.d / 2) + c * 4;
-    float2 x[4];
-    if constexpr (sizeof(TIN) == 2) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(src);
-      const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) x[i] = __bfloat1622float2(e[i]);
-    } else {
-      const float4 a = *reinterpret_cast<const float4*>(src), b4 = *reinterpret_cast<const float4*>(src + 4);
-      x[0] = make_float2(a.x, a.y); x[1] = make_float2(a.z, a.w); x[2] = make_float2(b4.x, b4.y); x[3] = make_float2(b4.z, b4.w);
-    }
-    const float4 w01 = *reinterpret_cast<const float4*>(ph), w23 = *reinterpret_cast<const float4*>(ph + 2);
-    const float2 w[4] = {make_float2(w01.x, w01.y), make_float2(w01.z, w01.w), make_float2(w23.x, w23.y), make_float2(w23.z, w23.w)};
-    float2 y[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float s = p.sign * w[i].y;
-      y[i].x = x[i].x * w[i].x - x[i].y * s;
-      y[i].y = x[i].x * s + x[i].y * w[i].x;
-    }
-    if constexpr (sizeof(TOUT) == 2) {
-      uint4 raw;
-      __nv_bfloat162* e = reinterpret_cast<__nv_bfloat162*>(&raw);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) e[i] = __float22bfloat162_rn(y[i]);
-      *reinterpret_cast<uint4*>(dst) = raw;
-    } else {
-      *reinterpret_cast<float4*>(dst) = make_float4(y[0].x, y[0].y, y[1].x, y[1].y);
-      *reinterpret_cast<float4*>(dst + 4) = make_float4(y[2].x, y[2].y, y[3].x, y[3].y);
-    }
+  const SeqView in = p.in[blockIdx.y], out = p.out[blockIdx.y];
+  const uint32_t per_head = p.d / 8, upt = p.H * per_head;          // units per token
+  const uint32_t tokens = (uint32_t)p.B * p.T;
+  if (upt <= 256) {
+    const uint32_t tpb = 256 / upt;                                  // tokens a CTA takes per pass
+    const uint32_t lt = threadIdx.x / upt, i = threadIdx.x % upt, h = i / per_head, c = i % per_head;
+    if (lt >= tpb) return;
+    for (uint32_t tok = blockIdx.x * tpb + lt; tok < tokens; tok += gridDim.x * tpb)
+      rotate_unit<TIN, TOUT>(p, in, out, tok / p.T, tok % p.T, h, c);
+  } else {
+    for (uint32_t tok = blockIdx.x; tok < tokens; tok += gridDim.x)
+      for (uint32_t i = threadIdx.x; i < upt; i += 256)
+        rotate_unit<TIN, TOUT>(p, in, out, tok / p.T, tok % p.T, i / per_head, i % per_head);
   }
 }
 
@@ -88,7 +100,32 @@ struct GateParams {
   int32_t swish;               // 1: gate = z * sigmoid(z); 0: gate = z
 };
 
-constexpr int GN_MAX_PAIRS = 4;     // channel pairs per lane: dv <= 256
+template <typename T, int V> __device__ __forceinline__ void load_vec(const T* p, float (&f)[V]) {
+  if constexpr (sizeof(T) == 2 && V == 4) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+  } else if constexpr (sizeof(T) == 4 && V == 4) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+  } else {
+    const float2 a = load2<T>(p);
+    f[0] = a.x; f[1] = a.y;
+  }
+}
+template <typename T, int V> __device__ __forceinline__ void store_vec(T* p, const float (&f)[V]) {
+  if constexpr (sizeof(T) == 2 && V == 4) {
+    uint2 raw;
+    *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __float22bfloat162_rn(make_float2(f[0], f[1]));
+    *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __float22bfloat162_rn(make_float2(f[2], f[3]));
+    *reinterpret_cast<uint2*>(p) = raw;
+  } else if constexpr (sizeof(T) == 4 && V == 4) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  } else {
+    store2<T>(p, make_float2(f[0], f[1]));
+  }
+}
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -96,83 +133,247 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-__device__ __forceinline__ int64_t group_offset(const SeqView& s, int64_t g, int T, int H) {
-  const int h = (int)(g % H);
-  const int64_t r = g / H;
-  return (r / T) * s.sb + (r % T) * s.st + h * s.sh;
+__device__ __forceinline__ int64_t seq_offset(const SeqView& s, uint32_t b, uint32_t t, uint32_t h) {
+  return b * s.sb + t * s.st + h * s.sh;
 }
 
-// One warp per (row, token, head): lane l owns channel pairs l, l+32, ... of the head.
-template <typename T, bool BWD>
+// One warp per (row, token, head), G of them in flight per warp so that their loads and reductions overlap:
+// lane l owns channels [V*l, V*l + V) of each of the NPASS 32*V-channel passes over a head.
+template <typename T, int V, int NPASS, bool BWD>
 __global__ void __launch_bounds__(256) gn_gate_kernel(const __grid_constant__ GateParams p) {
+  constexpr int G = 1;   // more heads in flight per warp cost registers and measured slower here
   const int lane = threadIdx.x & 31;
-  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const uint32_t warps = gridDim.x * (blockDim.x >> 5);
+  const uint32_t groups = (uint32_t)p.groups;
   const float inv_n = 1.0f / (float)p.dv;
-  for (int64_t g = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); g < p.groups; g += warps) {
-    const T* o = (const T*)p.o.data + group_offset(p.o, g, p.T, p.H);
-    const T* z = (const T*)p.z.data + group_offset(p.z, g, p.T, p.H);
-    float2 xo[GN_MAX_PAIRS], xz[GN_MAX_PAIRS], xd[GN_MAX_PAIRS];
-    float sum = 0.0f;
+  for (uint32_t g0 = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * G; g0 < groups; g0 += warps * G) {
+    float xo[G][NPASS][V], xz[G][NPASS][V], xd[G][NPASS][V];
+    uint32_t hb[G], ht[G], hh[G];
+    float sum[G];
 #pragma unroll
-    for (int i = 0; i < GN_MAX_PAIRS; ++i) {
-      const int c = 2 * (lane + 32 * i);
-      if (c < p.dv) {
-        xo[i] = load2<T>(o + c);
-        xz[i] = load2<T>(z + c);
-        if constexpr (BWD) xd[i] = load2<T>((const T*)p.dy.data + group_offset(p.dy, g, p.T, p.H) + c);
-        sum += xo[i].x + xo[i].y;
-      }
-    }
-    const float mean = warp_sum(sum) * inv_n;
-    float sq = 0.0f;
+    for (int j = 0; j < G; ++j) {
+      const uint32_t g = g0 + j < groups ? g0 + j : groups - 1;   // a warp past the end repeats the last group
+      hh[j] = g % p.H; const uint32_t r = g / p.H; hb[j] = r / p.T; ht[j] = r % p.T;
+      const T* o = (const T*)p.o.data + seq_offset(p.o, hb[j], ht[j], hh[j]);
+      const T* z = (const T*)p.z.data + seq_offset(p.z, hb[j], ht[j], hh[j]);
+      sum[j] = 0.0f;
 #pragma unroll
-    for (int i = 0; i < GN_MAX_PAIRS; ++i) {
-      if (2 * (lane + 32 * i) < p.dv) {
-        xo[i].x -= mean; xo[i].y -= mean;
-        sq += xo[i].x * xo[i].x + xo[i].y * xo[i].y;
-      }
-    }
-    const float rstd = rsqrtf(warp_sum(sq) * inv_n + p.eps);
-    if constexpr (!BWD) {
-      T* y = (T*)p.y.data + group_offset(p.y, g, p.T, p.H);
-#pragma unroll
-      for (int i = 0; i < GN_MAX_PAIRS; ++i) {
-        const int c = 2 * (lane + 32 * i);
+      for (int i = 0; i < NPASS; ++i) {
+        const int c = V * (lane + 32 * i);
         if (c < p.dv) {
-          float2 gate = xz[i];
-          if (p.swish) { gate.x = gate.x / (1.0f + __expf(-gate.x)); gate.y = gate.y / (1.0f + __expf(-gate.y)); }
-          store2<T>(y + c, make_float2(xo[i].x * rstd * gate.x, xo[i].y * rstd * gate.y));
+          load_vec<T, V>(o + c, xo[j][i]);
+          load_vec<T, V>(z + c, xz[j][i]);
+          if constexpr (BWD) load_vec<T, V>((const T*)p.dy.data + seq_offset(p.dy, hb[j], ht[j], hh[j]) + c, xd[j][i]);
+#pragma unroll
+          for (int e = 0; e < V; ++e) sum[j] += xo[j][i][e];
+        }
+      }
+    }
+    float rstd[G];
+#pragma unroll
+    for (int j = 0; j < G; ++j) sum[j] = warp_sum(sum[j]) * inv_n;          // mean
+#pragma unroll
+    for (int j = 0; j < G; ++j) {
+      float sq = 0.0f;
+#pragma unroll
+      for (int i = 0; i < NPASS; ++i) {
+        if (V * (lane + 32 * i) < p.dv) {
+#pragma unroll
+          for (int e = 0; e < V; ++e) { xo[j][i][e] -= sum[j]; sq += xo[j][i][e] * xo[j][i][e]; }
+        }
+      }
+      rstd[j] = sq;
+    }
+#pragma unroll
+    for (int j = 0; j < G; ++j) rstd[j] = rsqrtf(warp_sum(rstd[j]) * inv_n + p.eps);
+
+    if constexpr (!BWD) {
+#pragma unroll
+      for (int j = 0; j < G; ++j) {
+        if (g0 + j >= groups) break;
+        T* y = (T*)p.y.data + seq_offset(p.y, hb[j], ht[j], hh[j]);
+#pragma unroll
+        for (int i = 0; i < NPASS; ++i) {
+          const int c = V * (lane + 32 * i);
+          if (c < p.dv) {
+            float res[V];
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+              const float gate = p.swish ? __fdividef(xz[j][i][e], 1.0f + __expf(-xz[j][i][e])) : xz[j][i][e];
+              res[e] = xo[j][i][e] * rstd[j] * gate;
+            }
+            store_vec<T, V>(y + c, res);
+          }
         }
       }
     } else {
       // y = n * gate(z), n = (o - mean) rstd:  dz = dy n gate'(z);  dn = dy gate;  do = rstd (dn - mean(dn) - n mean(dn n))
-      float2 dn[GN_MAX_PAIRS];
-      float s1 = 0.0f, s2 = 0.0f;
-      T* d_z = (T*)p.d_z.data + group_offset(p.d_z, g, p.T, p.H);
+      // xd is overwritten with dn, xo with n.
+      float s1[G], s2[G];
 #pragma unroll
-      for (int i = 0; i < GN_MAX_PAIRS; ++i) {
-        const int c = 2 * (lane + 32 * i);
-        if (c < p.dv) {
-          xo[i].x *= rstd; xo[i].y *= rstd;                  // n
-          float2 gate = xz[i], slope = make_float2(1.0f, 1.0f);
-          if (p.swish) {
-            const float sx = 1.0f / (1.0f + __expf(-xz[i].x)), sy = 1.0f / (1.0f + __expf(-xz[i].y));
-            gate = make_float2(xz[i].x * sx, xz[i].y * sy);
-            slope = make_float2(sx * (1.0f + xz[i].x * (1.0f - sx)), sy * (1.0f + xz[i].y * (1.0f - sy)));
+      for (int j = 0; j < G; ++j) {
+        s1[j] = s2[j] = 0.0f;
+        const bool real = g0 + j < groups;
+        T* d_z = (T*)p.d_z.data + seq_offset(p.d_z, hb[j], ht[j], hh[j]);
+#pragma unroll
+        for (int i = 0; i < NPASS; ++i) {
+          const int c = V * (lane + 32 * i);
+          if (c < p.dv) {
+            float dz[V];
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+              const float n = xo[j][i][e] * rstd[j], zz = xz[j][i][e];
+              float gate = zz, slope = 1.0f;
+              if (p.swish) {
+                const float sg = __fdividef(1.0f, 1.0f + __expf(-zz));
+                gate = zz * sg;
+                slope = sg * (1.0f + zz * (1.0f - sg));
+              }
+              dz[e] = xd[j][i][e] * n * slope;
+              const float dn = xd[j][i][e] * gate;
+              xo[j][i][e] = n; xd[j][i][e] = dn;
+              s1[j] += dn;
+              s2[j] += dn * n;
+            }
+            if (real) store_vec<T, V>(d_z + c, dz);
           }
-          store2<T>(d_z + c, make_float2(xd[i].x * xo[i].x * slope.x, xd[i].y * xo[i].y * slope.y));
-          dn[i] = make_float2(xd[i].x * gate.x, xd[i].y * gate.y);
-          s1 += dn[i].x + dn[i].y;
-          s2 += dn[i].x * xo[i].x + dn[i].y * xo[i].y;
         }
       }
-      const float m1 = warp_sum(s1) * inv_n, m2 = warp_sum(s2) * inv_n;
-      T* d_o = (T*)p.d_o.data + group_offset(p.d_o, g, p.T, p.H);
 #pragma unroll
-      for (int i = 0; i < GN_MAX_PAIRS; ++i) {
-        const int c = 2 * (lane + 32 * i);
-        if (c < p.dv)
-          store2<T>(d_o + c, make_float2(rstd * (dn[i].x - m1 - xo[i].x * m2), rstd * (dn[i].y - m1 - xo[i].y * m2)));
+      for (int j = 0; j < G; ++j) { s1[j] = warp_sum(s1[j]) * inv_n; s2[j] = warp_sum(s2[j]) * inv_n; }
+#pragma unroll
+      for (int j = 0; j < G; ++j) {
+        if (g0 + j >= groups) break;
+        T* d_o = (T*)p.d_o.data + seq_offset(p.d_o, hb[j], ht[j], hh[j]);
+#pragma unroll
+        for (int i = 0; i < NPASS; ++i) {
+          const int c = V * (lane + 32 * i);
+          if (c < p.dv) {
+            float res[V];
+#pragma unroll
+            for (int e = 0; e < V; ++e) res[e] = rstd[j] * (xd[j][i][e] - s1[j] - xo[j][i][e] * s2[j]);
+            store_vec<T, V>(d_o + c, res);
+          }
+        }
+      }
+    }
+  }
+}
+
+// The same computation for heads of 128, 256 or 512 bytes: LPG lanes share a head, 16 bytes each, so a warp holds
+// 32/LPG heads per pass and G passes in flight — every access is 16 bytes wide and a warp has 1-2 KB per tensor
+// outstanding, which is what it takes to keep HBM busy from a kernel this short.
+template <typename T, int LPG, bool BWD>
+__global__ void __launch_bounds__(256) gn_gate_packed_kernel(const __grid_constant__ GateParams p) {
+  constexpr int V = 16 / sizeof(T), GPW = 32 / LPG, G = 2;
+  const int lane = threadIdx.x & 31, sub = lane / LPG, c = (lane % LPG) * V;
+  const uint32_t warps = gridDim.x * (blockDim.x >> 5);
+  const uint32_t groups = (uint32_t)p.groups;
+  const float inv_n = 1.0f / (float)p.dv;
+  auto sub_sum = [](float v) {
+#pragma unroll
+    for (int o = LPG / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+  };
+  auto load16 = [](const T* ptr, float (&f)[V]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(ptr);
+    if constexpr (sizeof(T) == 2) {
+      const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { const float2 a = __bfloat1622float2(e[i]); f[2 * i] = a.x; f[2 * i + 1] = a.y; }
+    } else {
+      f[0] = __uint_as_float(raw.x); f[1] = __uint_as_float(raw.y); f[2] = __uint_as_float(raw.z); f[3] = __uint_as_float(raw.w);
+    }
+  };
+  auto store16 = [](T* ptr, const float (&f)[V]) {
+    uint4 raw;
+    if constexpr (sizeof(T) == 2) {
+      __nv_bfloat162* e = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) e[i] = __float22bfloat162_rn(make_float2(f[2 * i], f[2 * i + 1]));
+    } else {
+      raw = make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+    }
+    *reinterpret_cast<uint4*>(ptr) = raw;
+  };
+  for (uint32_t g0 = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * (GPW * G); g0 < groups; g0 += warps * (GPW * G)) {
+    float xo[G][V], xz[G][V], xd[G][V], mean[G], rstd[G];
+    int64_t off_o[G], off_z[G];
+    uint32_t hb[G], ht[G], hh[G];
+    bool real[G];
+#pragma unroll
+    for (int j = 0; j < G; ++j) {
+      const uint32_t want = g0 + j * GPW + sub;
+      real[j] = want < groups;
+      const uint32_t g = real[j] ? want : groups - 1;             // lanes past the end repeat the last head
+      hh[j] = g % p.H; const uint32_t r = g / p.H; hb[j] = r / p.T; ht[j] = r % p.T;
+      off_o[j] = seq_offset(p.o, hb[j], ht[j], hh[j]) + c;
+      off_z[j] = seq_offset(p.z, hb[j], ht[j], hh[j]) + c;
+      load16((const T*)p.o.data + off_o[j], xo[j]);
+      load16((const T*)p.z.data + off_z[j], xz[j]);
+      if constexpr (BWD) load16((const T*)p.dy.data + seq_offset(p.dy, hb[j], ht[j], hh[j]) + c, xd[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < G; ++j) {
+      float s = 0.0f;
+#pragma unroll
+      for (int e = 0; e < V; ++e) s += xo[j][e];
+      mean[j] = s;
+    }
+#pragma unroll
+    for (int j = 0; j < G; ++j) mean[j] = sub_sum(mean[j]) * inv_n;
+#pragma unroll
+    for (int j = 0; j < G; ++j) {
+      float sq = 0.0f;
+#pragma unroll
+      for (int e = 0; e < V; ++e) { xo[j][e] -= mean[j]; sq += xo[j][e] * xo[j][e]; }
+      rstd[j] = sq;
+    }
+#pragma unroll
+    for (int j = 0; j < G; ++j) rstd[j] = rsqrtf(sub_sum(rstd[j]) * inv_n + p.eps);
+
+    if constexpr (!BWD) {
+#pragma unroll
+      for (int j = 0; j < G; ++j) {
+        float res[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          const float gate = p.swish ? __fdividef(xz[j][e], 1.0f + __expf(-xz[j][e])) : xz[j][e];
+          res[e] = xo[j][e] * rstd[j] * gate;
+        }
+        if (real[j]) store16((T*)p.y.data + seq_offset(p.y, hb[j], ht[j], hh[j]) + c, res);
+      }
+    } else {
+      float s1[G], s2[G];
+#pragma unroll
+      for (int j = 0; j < G; ++j) {
+        s1[j] = s2[j] = 0.0f;
+        float dz[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          const float n = xo[j][e] * rstd[j], zz = xz[j][e];
+          float gate = zz, slope = 1.0f;
+          if (p.swish) {
+            const float sg = __fdividef(1.0f, 1.0f + __expf(-zz));
+            gate = zz * sg;
+            slope = sg * (1.0f + zz * (1.0f - sg));
+          }
+          dz[e] = xd[j][e] * n * slope;
+          const float dn = xd[j][e] * gate;
+          xo[j][e] = n; xd[j][e] = dn;
+          s1[j] += dn;
+          s2[j] += dn * n;
+        }
+        if (real[j]) store16((T*)p.d_z.data + seq_offset(p.d_z, hb[j], ht[j], hh[j]) + c, dz);
+      }
+#pragma unroll
+      for (int j = 0; j < G; ++j) { s1[j] = sub_sum(s1[j]) * inv_n; s2[j] = sub_sum(s2[j]) * inv_n; }
+#pragma unroll
+      for (int j = 0; j < G; ++j) {
+        float res[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) res[e] = rstd[j] * (xd[j][e] - s1[j] - xo[j][e] * s2[j]);
+        if (real[j]) store16((T*)p.d_o.data + seq_offset(p.d_o, hb[j], ht[j], hh[j]) + c, res);
       }
     }
   }
@@ -192,7 +393,8 @@ int launch_rotary(int in_dtype, int out_dtype, int B, int T, int H, int d, bool 
   for (int i = 0; i < 2; ++i) { p.in[i] = in[i < n_tensors ? i : 0]; p.out[i] = out[i < n_tensors ? i : 0]; }
   p.phasors = reinterpret_cast<const float2*>(phasors);
   p.ph_sb = phasor_stride_b; p.B = B; p.T = T; p.H = H; p.d = d; p.sign = conjugate ? -1.0f : 1.0f;
-  const dim3 grid(grid_for((int64_t)B * T * H * (d / 8), 256), n_tensors);
+  const int64_t upt = (int64_t)H * (d / 8);
+  const dim3 grid(grid_for((int64_t)B * T, upt <= 256 ? (int)(256 / upt) : 1), n_tensors);
   if (in_dtype == FPB_BF16 && out_dtype == FPB_BF16) rotary_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, stream>>>(p);
   else if (in_dtype == FPB_BF16) rotary_kernel<__nv_bfloat16, float><<<grid, 256, 0, stream>>>(p);
   else if (out_dtype == FPB_BF16) rotary_kernel<float, __nv_bfloat16><<<grid, 256, 0, stream>>>(p);
@@ -200,18 +402,52 @@ int launch_rotary(int in_dtype, int out_dtype, int B, int T, int H, int d, bool 
   return FPB_OK;
 }
 
-int launch_gn_gate(int dtype, bool backward, int B, int T, int H, int dv, float eps, bool swish, SeqView o, SeqView z,
-                   SeqView y, SeqView dy, SeqView d_o, SeqView d_z, cudaStream_t stream) {
+int launch_gn_gate(int dtype, bool backward, bool wide, bool packed, int B, int T, int H, int dv, float eps, bool swish, SeqView o,
+                   SeqView z, SeqView y, SeqView dy, SeqView d_o, SeqView d_z, cudaStream_t stream) {
   GateParams p;
   p.o = o; p.z = z; p.y = y; p.dy = dy; p.d_o = d_o; p.d_z = d_z;
   p.groups = (int64_t)B * T * H; p.T = T; p.H = H; p.dv = dv; p.eps = eps; p.swish = swish ? 1 : 0;
-  const int grid = grid_for(p.groups, 8);
+  const int head_bytes = dv * (dtype == FPB_F32 ? 4 : 2);
+  if (packed && (head_bytes == 128 || head_bytes == 256 || head_bytes == 512)) {
+    const int lpg = head_bytes / 16;
+    const int grid = grid_for((p.groups + (32 / lpg) * 2 - 1) / ((32 / lpg) * 2), 8);
+    auto run = [&](auto tag, auto lanes) {
+      using T = decltype(tag);
+      constexpr int L = decltype(lanes)::value;
+      if (backward) gn_gate_packed_kernel<T, L, true><<<grid, 256, 0, stream>>>(p);
+      else gn_gate_packed_kernel<T, L, false><<<grid, 256, 0, stream>>>(p);
+    };
+    auto by_lanes = [&](auto tag) {
+      if (lpg == 8) run(tag, std::integral_constant<int, 8>{});
+      else if (lpg == 16) run(tag, std::integral_constant<int, 16>{});
+      else run(tag, std::integral_constant<int, 32>{});
+    };
+    if (dtype == FPB_BF16) by_lanes(__nv_bfloat16{}); else by_lanes(float{});
+    return FPB_OK;
+  }
+  // passes of 32 lanes x V channels that cover a head; G groups per warp as in the kernel
+  const int V = wide ? 4 : 2;
+  const int npass = (dv + 32 * V - 1) / (32 * V);
+  const int per_warp = 1;
+  const int grid = grid_for((p.groups + per_warp - 1) / per_warp, 8);
+  auto go = [&](auto tag, auto vec, auto passes) {
+    using T = decltype(tag);
+    constexpr int VV = decltype(vec)::value, NP = decltype(passes)::value;
+    if (backward) gn_gate_kernel<T, VV, NP, true><<<grid, 256, 0, stream>>>(p);
+    else gn_gate_kernel<T, VV, NP, false><<<grid, 256, 0, stream>>>(p);
+  };
+  auto by_passes = [&](auto tag, auto vec) {
+    constexpr int VV = decltype(vec)::value;
+    if (npass == 1) go(tag, vec, std::integral_constant<int, 1>{});
+    else if (npass == 2) go(tag, vec, std::integral_constant<int, 2>{});
+    else if constexpr (VV == 2) {
+      if (npass == 3) go(tag, vec, std::integral_constant<int, 3>{}); else go(tag, vec, std::integral_constant<int, 4>{});
+    }
+  };
   if (dtype == FPB_BF16) {
-    if (backward) gn_gate_kernel<__nv_bfloat16, true><<<grid, 256, 0, stream>>>(p);
-    else gn_gate_kernel<__nv_bfloat16, false><<<grid, 256, 0, stream>>>(p);
+    if (wide) by_passes(__nv_bfloat16{}, std::integral_constant<int, 4>{}); else by_passes(__nv_bfloat16{}, std::integral_constant<int, 2>{});
   } else {
-    if (backward) gn_gate_kernel<float, true><<<grid, 256, 0, stream>>>(p);
-    else gn_gate_kernel<float, false><<<grid, 256, 0, stream>>>(p);
+    if (wide) by_passes(float{}, std::integral_constant<int, 4>{}); else by_passes(float{}, std::integral_constant<int, 2>{});
   }
   return FPB_OK;
 }
