@@ -408,6 +408,45 @@ int fpb_groupnorm_gate_bwd(int32_t B, int32_t T, int32_t H, int32_t dv, int32_t 
   return finish_launches(1, -1);
 }
 
+namespace {
+int check_norm(int64_t rows, int32_t d, int32_t dtype, const void* a, int64_t a_stride, const void* b, int64_t b_stride) {
+  if (rows < 0 || d <= 0) return FPB_ERR_BAD_SHAPE;
+  if (!dtype_ok(dtype)) return FPB_ERR_BAD_DTYPE;
+  const int vec = dtype == FPB_F32 ? 4 : 8;
+  if (d % vec || d > 4 * 32 * vec) return FPB_ERR_BAD_SHAPE;
+  if (rows == 0) return FPB_OK;
+  if (!a || !b) return FPB_ERR_NULL_POINTER;
+  if ((rows > 1 && (a_stride < d || b_stride < d)) || a_stride % vec || b_stride % vec || (uintptr_t)a % 16 || (uintptr_t)b % 16)
+    return FPB_ERR_BAD_STRIDE;
+  return FPB_OK;
+}
+}  // namespace
+
+int fpb_layernorm_fwd(int64_t rows, int32_t d, int32_t dtype, float eps, const void* x, int64_t x_stride,
+                      const float* weight, const float* bias, void* y, int64_t y_stride, fpb_stream_t stream) {
+  FPB_TRY(check_norm(rows, d, dtype, x, x_stride, y, y_stride));
+  FPB_TRY(check_device());
+  if (rows == 0) return FPB_OK;
+  launch_layernorm(dtype, false, rows, d, eps, x, x_stride, weight, bias, y, y_stride, nullptr, nullptr, nullptr, nullptr,
+                   (cudaStream_t)stream);
+  return finish_launches(1, -1);
+}
+
+int fpb_layernorm_bwd(int64_t rows, int32_t d, int32_t dtype, float eps, const void* x, int64_t x_stride,
+                      const float* weight, const void* d_y, int64_t dy_stride, void* d_x, float* d_weight, float* d_bias,
+                      fpb_stream_t stream) {
+  FPB_TRY(check_norm(rows, d, dtype, x, x_stride, d_y, dy_stride));
+  if (rows > 0 && (!d_x || (uintptr_t)d_x % 16)) return d_x ? FPB_ERR_BAD_STRIDE : FPB_ERR_NULL_POINTER;
+  FPB_TRY(check_device());
+  // the kernel adds its partial sums into the two gradient vectors
+  if (d_weight && cudaMemsetAsync(d_weight, 0, sizeof(float) * d, (cudaStream_t)stream) != cudaSuccess) return finish_launches(0, -1);
+  if (d_bias && cudaMemsetAsync(d_bias, 0, sizeof(float) * d, (cudaStream_t)stream) != cudaSuccess) return finish_launches(0, -1);
+  if (rows == 0) return FPB_OK;
+  launch_layernorm(dtype, true, rows, d, eps, x, x_stride, weight, nullptr, nullptr, dy_stride, d_y, d_x, d_weight, d_bias,
+                   (cudaStream_t)stream);
+  return finish_launches(1, -1);
+}
+
 const char* fpb_strerror(int status) {
   switch (status) {
     case FPB_OK: return "ok";

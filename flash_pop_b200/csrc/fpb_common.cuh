@@ -61,6 +61,10 @@ int launch_rotary(int in_dtype, int out_dtype, int B, int T, int H, int d, bool 
 int launch_gn_gate(int dtype, bool backward, bool wide, bool packed, int B, int T, int H, int dv, float eps, bool swish, SeqView o,
                    SeqView z, SeqView y, SeqView dy, SeqView d_o, SeqView d_z, cudaStream_t stream);
 
+int launch_layernorm(int dtype, bool backward, int64_t rows, int d, float eps, const void* x, int64_t x_stride,
+                     const float* w, const float* b, void* y, int64_t y_stride, const void* dy, void* dx, float* dw,
+                     float* db, cudaStream_t stream);
+
 // Device status word shared by all kernels: 0 = fine; otherwise (role << 8 | barrier id) of the
 // first bounded wait that gave up.
 int32_t* device_status_ptr();

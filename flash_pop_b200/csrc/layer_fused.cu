@@ -379,6 +379,153 @@ __global__ void __launch_bounds__(256) gn_gate_packed_kernel(const __grid_consta
   }
 }
 
+// ---- LayerNorm with fp32 arithmetic on bf16 (or fp32) rows -----------------------------------------
+// The reference's layers run their LayerNorms in fp32 on bf16 activations by casting around them
+// (flash_pop/retnet.py:474-486): three passes forward, and a backward whose weight/bias gradient is a
+// separate column reduction.  Here a warp owns a row at a time, 16 bytes per lane and pass, statistics
+// in registers; the backward keeps its lanes' weight and bias gradient sums in registers over all the
+// rows the warp walks and adds them to the output once at the end.
+struct NormParams {
+  const void* x; const void* dy; void* y; void* dx;
+  const float* w; const float* b;
+  float* dw; float* db;
+  int64_t rows, x_stride, y_stride;      // row strides in elements (dy and dx share y_stride / x_stride)
+  int32_t d;
+  float eps;
+};
+
+template <typename T, int V> __device__ __forceinline__ void load16v(const T* ptr, float (&f)[V]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(ptr);
+  if constexpr (sizeof(T) == 2) {
+    const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 a = __bfloat1622float2(e[i]); f[2 * i] = a.x; f[2 * i + 1] = a.y; }
+  } else {
+    f[0] = __uint_as_float(raw.x); f[1] = __uint_as_float(raw.y); f[2] = __uint_as_float(raw.z); f[3] = __uint_as_float(raw.w);
+  }
+}
+template <typename T, int V> __device__ __forceinline__ void store16v(T* ptr, const float (&f)[V]) {
+  uint4 raw;
+  if constexpr (sizeof(T) == 2) {
+    __nv_bfloat162* e = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) e[i] = __float22bfloat162_rn(make_float2(f[2 * i], f[2 * i + 1]));
+  } else {
+    raw = make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+  }
+  *reinterpret_cast<uint4*>(ptr) = raw;
+}
+
+template <typename T, int NPASS, bool BWD>
+__global__ void __launch_bounds__(BWD ? 128 : 256) layernorm_kernel(const __grid_constant__ NormParams p) {
+  constexpr int V = 16 / sizeof(T);
+  extern __shared__ float sh_grad[];             // backward: d floats of weight gradient, d of bias gradient
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const float inv_n = 1.0f / (float)p.d;
+  float gw[BWD ? NPASS : 1][V], gb[BWD ? NPASS : 1][V];
+  if constexpr (BWD) {
+#pragma unroll
+    for (int i = 0; i < NPASS; ++i)
+#pragma unroll
+      for (int e = 0; e < V; ++e) gw[i][e] = gb[i][e] = 0.0f;
+    for (int i = threadIdx.x; i < 2 * p.d; i += blockDim.x) sh_grad[i] = 0.0f;
+    __syncthreads();
+  }
+  for (int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < p.rows; row += warps) {
+    const T* x = (const T*)p.x + row * p.x_stride;
+    float xv[NPASS][V], dv[BWD ? NPASS : 1][V];
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NPASS; ++i) {
+      const int c = V * (lane + 32 * i);
+      if (c < p.d) {
+        load16v<T, V>(x + c, xv[i]);
+        if constexpr (BWD) load16v<T, V>((const T*)p.dy + row * p.y_stride + c, dv[i]);
+#pragma unroll
+        for (int e = 0; e < V; ++e) sum += xv[i][e];
+      }
+    }
+    const float mean = warp_sum(sum) * inv_n;
+    float sq = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NPASS; ++i) {
+      if (V * (lane + 32 * i) < p.d) {
+#pragma unroll
+        for (int e = 0; e < V; ++e) { xv[i][e] -= mean; sq += xv[i][e] * xv[i][e]; }
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(sq) * inv_n + p.eps);
+    if constexpr (!BWD) {
+      T* y = (T*)p.y + row * p.y_stride;
+#pragma unroll
+      for (int i = 0; i < NPASS; ++i) {
+        const int c = V * (lane + 32 * i);
+        if (c < p.d) {
+          float res[V];
+#pragma unroll
+          for (int e = 0; e < V; ++e) {
+            const float w = p.w ? __ldg(p.w + c + e) : 1.0f, b = p.b ? __ldg(p.b + c + e) : 0.0f;
+            res[e] = xv[i][e] * rstd * w + b;
+          }
+          store16v<T, V>(y + c, res);
+        }
+      }
+    } else {
+      // n = (x - mean) rstd, y = n w + b:  dn = dy w;  dx = rstd (dn - mean(dn) - n mean(dn n));  dw += dy n;  db += dy
+      float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+      for (int i = 0; i < NPASS; ++i) {
+        const int c = V * (lane + 32 * i);
+        if (c < p.d) {
+#pragma unroll
+          for (int e = 0; e < V; ++e) {
+            const float n = xv[i][e] * rstd, g = dv[i][e];
+            gw[i][e] += g * n;
+            gb[i][e] += g;
+            const float dn = p.w ? g * __ldg(p.w + c + e) : g;
+            xv[i][e] = n; dv[i][e] = dn;
+            s1 += dn;
+            s2 += dn * n;
+          }
+        }
+      }
+      const float m1 = warp_sum(s1) * inv_n, m2 = warp_sum(s2) * inv_n;
+      T* dx = (T*)p.dx + row * p.x_stride;
+#pragma unroll
+      for (int i = 0; i < NPASS; ++i) {
+        const int c = V * (lane + 32 * i);
+        if (c < p.d) {
+          float res[V];
+#pragma unroll
+          for (int e = 0; e < V; ++e) res[e] = rstd * (dv[i][e] - m1 - xv[i][e] * m2);
+          store16v<T, V>(dx + c, res);
+        }
+      }
+    }
+  }
+  if constexpr (BWD) {
+    if (p.dw || p.db) {
+#pragma unroll
+      for (int i = 0; i < NPASS; ++i) {
+        const int c = V * (lane + 32 * i);
+        if (c < p.d) {
+#pragma unroll
+          for (int e = 0; e < V; ++e) {
+            atomicAdd(&sh_grad[c + e], gw[i][e]);
+            atomicAdd(&sh_grad[p.d + c + e], gb[i][e]);
+          }
+        }
+      }
+      __syncthreads();
+      for (int i = threadIdx.x; i < p.d; i += blockDim.x) {
+        if (p.dw) atomicAdd(p.dw + i, sh_grad[i]);
+        if (p.db) atomicAdd(p.db + i, sh_grad[p.d + i]);
+      }
+    }
+  }
+}
+
 int grid_for(int64_t work_items, int per_block) {
   const int64_t blocks = (work_items + per_block - 1) / per_block;
   const int64_t cap = 148 * 16;              // a few waves of the 148 SMs; the kernels loop over the rest
@@ -399,6 +546,36 @@ int launch_rotary(int in_dtype, int out_dtype, int B, int T, int H, int d, bool 
   else if (in_dtype == FPB_BF16) rotary_kernel<__nv_bfloat16, float><<<grid, 256, 0, stream>>>(p);
   else if (out_dtype == FPB_BF16) rotary_kernel<float, __nv_bfloat16><<<grid, 256, 0, stream>>>(p);
   else rotary_kernel<float, float><<<grid, 256, 0, stream>>>(p);
+  return FPB_OK;
+}
+
+// d <= 4 passes of 32 lanes x 16 bytes (1024 bf16 / 512 fp32 channels); the caller has checked it
+int launch_layernorm(int dtype, bool backward, int64_t rows, int d, float eps, const void* x, int64_t x_stride,
+                     const float* w, const float* b, void* y, int64_t y_stride, const void* dy, void* dx, float* dw,
+                     float* db, cudaStream_t stream) {
+  NormParams p;
+  p.x = x; p.dy = dy; p.y = y; p.dx = dx; p.w = w; p.b = b; p.dw = dw; p.db = db;
+  p.rows = rows; p.x_stride = x_stride; p.y_stride = y_stride; p.d = d; p.eps = eps;
+  const int V = dtype == FPB_F32 ? 4 : 8;
+  const int npass = (d + 32 * V - 1) / (32 * V);
+  const int wpb = backward ? 4 : 8;
+  // backward: every CTA ends with 2d atomic adds, so no more CTAs than keep the SMs full
+  const int64_t blocks = (rows + wpb - 1) / wpb;
+  const int cap = backward ? 148 * 4 : 148 * 16;
+  const int grid = (int)(blocks < 1 ? 1 : (blocks < cap ? blocks : cap));
+  const size_t smem = backward ? 2 * (size_t)d * sizeof(float) : 0;
+  auto go = [&](auto tag, auto passes) {
+    using T = decltype(tag);
+    constexpr int NP = decltype(passes)::value;
+    if (backward) layernorm_kernel<T, NP, true><<<grid, 128, smem, stream>>>(p);
+    else layernorm_kernel<T, NP, false><<<grid, 256, 0, stream>>>(p);
+  };
+  auto by_passes = [&](auto tag) {
+    if (npass == 1) go(tag, std::integral_constant<int, 1>{});
+    else if (npass == 2) go(tag, std::integral_constant<int, 2>{});
+    else go(tag, std::integral_constant<int, 4>{});
+  };
+  if (dtype == FPB_BF16) by_passes(__nv_bfloat16{}); else by_passes(float{});
   return FPB_OK;
 }
 

@@ -102,3 +102,70 @@ def groupnorm_gate(o: Tensor, z: Tensor, eps: float, swish: bool = True) -> Tens
     """GroupNorm over the last dimension of o (B,T,H,dv) (no affine parameters) times the gate: z * sigmoid(z) when
     `swish`, else z as given."""
     return GroupNormGate.apply(o, z, eps, swish)
+
+
+# ---- LayerNorm with fp32 arithmetic on bf16 rows ------------------------------------------------------------------
+def layer_norm_supported(x: Tensor, d: int) -> bool:
+    if not (x.is_cuda and x.dtype in _OK_DTYPES and x.dim() >= 1 and x.size(-1) == d):
+        return False
+    vec = 8 if x.dtype == torch.bfloat16 else 4
+    return d % vec == 0 and d <= 128 * vec
+
+
+def _rows(t: Tensor) -> Tensor:
+    """(rows, d) view with unit inner stride and a 16-byte aligned row pitch, copied if that is not what `t` is."""
+    t2 = t.reshape(-1, t.size(-1))
+    vec = 16 // t2.element_size()
+    ok = t2.stride(1) == 1 and t2.data_ptr() % 16 == 0 and (t2.size(0) <= 1 or t2.stride(0) % vec == 0)
+    return t2 if ok else t2.contiguous()
+
+
+def _ptr(t: Optional[Tensor]):
+    return ctypes.c_void_p(None if t is None else t.data_ptr())
+
+
+class FusedLayerNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps: float):
+        x2 = _rows(x)
+        rows, d = x2.shape
+        w = None if weight is None else weight.detach().float().contiguous()
+        b = None if bias is None else bias.detach().float().contiguous()
+        y = torch.empty((rows, d), device=x.device, dtype=x.dtype)
+        with torch.cuda.device(x.device):
+            _lib.check(_lib.lib().fpb_layernorm_fwd(rows, d, _lib.dtype_code(x2), float(eps), _ptr(x2), x2.stride(0) if rows > 1 else d,
+                                                    _ptr(w), _ptr(b), _ptr(y), d, _lib.stream_ptr(x.device)))
+        ctx.save_for_backward(x2, w)
+        ctx.eps, ctx.shape = float(eps), x.shape
+        ctx.w_dtype = None if weight is None else weight.dtype
+        ctx.b_dtype = None if bias is None else bias.dtype
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        rows, d = x2.shape
+        dy2 = _rows(dy.to(x2.dtype))
+        dx = torch.empty((rows, d), device=x2.device, dtype=x2.dtype)
+        need_w = ctx.w_dtype is not None and ctx.needs_input_grad[1]
+        need_b = ctx.b_dtype is not None and ctx.needs_input_grad[2]
+        dw = torch.empty(d, device=x2.device, dtype=torch.float32) if need_w else None
+        db = torch.empty(d, device=x2.device, dtype=torch.float32) if need_b else None
+        x_in = x2 if (rows <= 1 or x2.stride(0) == d) else x2.contiguous()      # d_x is written with x's row pitch
+        with torch.cuda.device(x2.device):
+            _lib.check(_lib.lib().fpb_layernorm_bwd(rows, d, _lib.dtype_code(x2), ctx.eps, _ptr(x_in), d, _ptr(w), _ptr(dy2),
+                                                    dy2.stride(0) if rows > 1 else d, _ptr(dx), _ptr(dw), _ptr(db),
+                                                    _lib.stream_ptr(x2.device)))
+        return (dx.view(ctx.shape), None if dw is None else dw.to(ctx.w_dtype), None if db is None else db.to(ctx.b_dtype), None)
+
+
+def layer_norm(x: Tensor, weight: Optional[Tensor], bias: Optional[Tensor], eps: float) -> Tensor:
+    """LayerNorm over the last dimension, fp32 arithmetic, result in x's dtype; weight / bias may be None."""
+    return FusedLayerNorm.apply(x, weight, bias, eps)
+
+
+def norm_in_fp32(module: torch.nn.LayerNorm, x: Tensor) -> Tensor:
+    """``module(x.float()).to(x.dtype)`` — as one kernel when the rows qualify, else literally that."""
+    if len(module.normalized_shape) == 1 and layer_norm_supported(x, module.normalized_shape[0]):
+        return layer_norm(x, module.weight, module.bias, module.eps)
+    return module(x.float()).to(dtype=x.dtype)

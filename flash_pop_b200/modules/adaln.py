@@ -8,6 +8,8 @@ from typing import Optional, Tuple
 import torch
 import torch.nn as nn
 
+from flash_pop_b200.layer_ops import norm_in_fp32
+
 
 def modulate(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     assert x.shape == shift.shape == scale.shape, f"Got x: {x.shape}, shift: {shift.shape}, scale: {scale.shape}"
@@ -53,7 +55,7 @@ class _AdaNormBase(nn.Module):
             nn.init.zeros_(self.modulation[-2].weight)
 
     def _parts(self, x, c):
-        return apply_modulation(c, self.modulation, x.shape).chunk(self.n_chunks, dim=-1), self.norm(x.float()).to(dtype=x.dtype)
+        return apply_modulation(c, self.modulation, x.shape).chunk(self.n_chunks, dim=-1), norm_in_fp32(self.norm, x)
 
 
 class AdaLayerNorm(_AdaNormBase):

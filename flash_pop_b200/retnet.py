@@ -26,7 +26,7 @@ import torch.nn.functional as F
 from torch import Tensor
 
 from flash_pop_b200.fused_retention import cuda_core_kernels, fused_chunk_retention, retention_step
-from flash_pop_b200.layer_ops import groupnorm_gate, groupnorm_gate_supported
+from flash_pop_b200.layer_ops import groupnorm_gate, groupnorm_gate_supported, norm_in_fp32
 from flash_pop_b200.recurrent_state import RecurrentState
 from flash_pop_b200.xpos_emb import XPos
 
@@ -247,7 +247,7 @@ class RetNetDecoderLayer(nn.Module):
     def _residual_blocks(self, x: Tensor, retention_fn: Callable[[Tensor], Tuple[Tensor, Tensor]], fp32_norm: bool):
         """x + retention, x + feed-forward, with the norm before (pre-norm) or after each branch."""
         dtype = self.config.dtype
-        norm = (lambda m, t: m(t.float()).to(dtype=dtype)) if fp32_norm else (lambda m, t: m(t))
+        norm = (lambda m, t: norm_in_fp32(m, t).to(dtype=dtype)) if fp32_norm else (lambda m, t: m(t))
         if self.norm_first:
             y, state = retention_fn(norm(self.norm1, x))
             x = x + y

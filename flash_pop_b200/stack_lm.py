@@ -10,6 +10,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from flash_pop_b200.layer_ops import norm_in_fp32
 from flash_pop_b200.recurrent_state import RecurrentState
 from flash_pop_b200.retnet import RetNetDecoder, RetNetDecoderLayer
 
@@ -31,7 +32,7 @@ class RetNetLM(nn.Module):
     def forward(self, tokens: torch.Tensor, recurrent_state: Optional[RecurrentState] = None):
         """tokens: (B, T) int64 -> logits (B, T, vocab), new RecurrentState."""
         x, state = self.decoder(self.embed(tokens), recurrent_state)
-        return self.head(self.norm(x.float()).to(x.dtype)), state
+        return self.head(norm_in_fp32(self.norm, x)), state
 
     def loss(self, tokens: torch.Tensor) -> torch.Tensor:
         """Next-token cross entropy of `tokens` (B, T)."""

@@ -173,6 +173,21 @@ int fpb_groupnorm_gate_bwd(int32_t B, int32_t T, int32_t H, int32_t dv, int32_t 
                            const fpb_seq* o, const fpb_seq* z, const fpb_seq* d_y, const fpb_seq* d_o,
                            const fpb_seq* d_z, fpb_stream_t stream);
 
+/*
+ * LayerNorm over the last dimension with fp32 arithmetic on bf16 (or fp32) rows, in one pass each way.
+ *   y = (x - mean) / sqrt(var + eps) * weight + bias      (biased variance; weight / bias fp32, either may be NULL)
+ * x, y: `rows` rows of d elements, `*_stride` elements apart, 16-byte aligned; d a multiple of 8 (bf16) / 4 (fp32)
+ * and at most 1024 (bf16) / 512 (fp32).  The backward recomputes the statistics from x, writes d_x (x's strides)
+ * and overwrites d_weight / d_bias (fp32, d entries each, either may be NULL) with the sums over all rows; the
+ * sums are accumulated with atomic adds, so their last bits depend on the order.
+ * Replaces the cast - nn.LayerNorm(fp32) - cast sequence around the layers' norms (flash_pop/retnet.py:474-486).
+ */
+int fpb_layernorm_fwd(int64_t rows, int32_t d, int32_t dtype, float eps, const void* x, int64_t x_stride,
+                      const float* weight, const float* bias, void* y, int64_t y_stride, fpb_stream_t stream);
+int fpb_layernorm_bwd(int64_t rows, int32_t d, int32_t dtype, float eps, const void* x, int64_t x_stride,
+                      const float* weight, const void* d_y, int64_t dy_stride, void* d_x, float* d_weight,
+                      float* d_bias, fpb_stream_t stream);
+
 /* Text for a status code. */
 const char* fpb_strerror(int status);
 /* Library version, major*10000 + minor*100 + patch. */

@@ -100,3 +100,49 @@ def test_layer_with_fused_passes_matches_layer_without():
     for a, b in zip(*outs):
         rr = ((a.float() - b.float()).square().mean().sqrt() / b.float().square().mean().sqrt()).item()
         assert rr < 2e-2, rr
+
+
+@pytest.mark.parametrize("dtype,d,affine", [(BF, 1024, True), (BF, 256, True), (F32, 512, True), (BF, 264, False),
+                                            (F32, 36, True), (BF, 8, True)])
+def test_layer_norm_forward_and_backward(dtype, d, affine):
+    from flash_pop_b200.layer_ops import layer_norm, layer_norm_supported
+    rows_shape, eps = (3, 41), 1e-6
+    g = torch.Generator().manual_seed(d)
+    x0 = (torch.randn(*rows_shape, d, generator=g) * 1.5 + 0.3).to(dtype).cuda()
+    dy = torch.randn(*rows_shape, d, generator=g).to(dtype).cuda()
+    w0 = (1 + 0.1 * torch.randn(d, generator=g)).cuda() if affine else None
+    b0 = (0.1 * torch.randn(d, generator=g)).cuda() if affine else None
+    assert layer_norm_supported(x0, d)
+    x = x0.clone().requires_grad_(True)
+    w = None if w0 is None else w0.clone().requires_grad_(True)
+    b = None if b0 is None else b0.clone().requires_grad_(True)
+    y = layer_norm(x, w, b, eps)
+    y.backward(dy)
+    xd = x0.double().requires_grad_(True)
+    wd = None if w0 is None else w0.double().requires_grad_(True)
+    bd = None if b0 is None else b0.double().requires_grad_(True)
+    ref = F.layer_norm(xd, (d,), wd, bd, eps)
+    ref.backward(dy.double())
+    pairs = [("y", y, ref), ("d_x", x.grad, xd.grad)]
+    if affine:
+        pairs += [("d_weight", w.grad, wd.grad), ("d_bias", b.grad, bd.grad)]
+    for name, got, want in pairs:
+        rr = ((got.double() - want).square().mean().sqrt() / want.square().mean().sqrt()).item()
+        assert rr < (5e-3 if dtype == BF else 2e-5), f"{name}: rel-RMS {rr:.3e}"
+
+
+def test_layer_norm_module_helper_matches_cast_norm_cast():
+    from flash_pop_b200.layer_ops import norm_in_fp32
+    torch.manual_seed(1)
+    m = torch.nn.LayerNorm(512, device="cuda", dtype=F32)
+    with torch.no_grad():
+        m.weight.normal_(1.0, 0.1); m.bias.normal_(0.0, 0.1)
+    x = torch.randn(4, 50, 512, device="cuda", dtype=BF)
+    strided = torch.randn(4, 50, 1024, device="cuda", dtype=BF)[..., :512]       # rows 2048 bytes apart
+    for t in (x, strided):
+        want = m(t.float()).to(BF)
+        got = norm_in_fp32(m, t)
+        assert got.dtype == BF and torch.allclose(got.float(), want.float(), rtol=1e-2, atol=1e-2)
+    big = torch.randn(2, 2048, device="cuda", dtype=BF)                          # wider than the kernel takes: eager path
+    m2 = torch.nn.LayerNorm(2048, device="cuda", dtype=F32)
+    assert torch.equal(norm_in_fp32(m2, big), m2(big.float()).to(BF))
