@@ -229,7 +229,7 @@ def run_layer_passes(args):
     """The fused elementwise passes of a retention layer at the full-stack shape (16 x 4096 tokens, 8 heads of 128):
     GB/s of each kernel over its algorithmic bytes (every tensor read or written once)."""
     from flash_pop_b200 import _lib
-    from flash_pop_b200.layer_ops import _rotate, groupnorm_gate
+    from flash_pop_b200.layer_ops import _rotate, groupnorm_gate, layer_norm
     from flash_pop_b200.xpos_emb import XPos
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the layer-pass workload is reported for the CUDA kernels "
@@ -243,7 +243,13 @@ def run_layer_passes(args):
     tensor_bytes = q.numel() * 2
     o.requires_grad_(True); z.requires_grad_(True)
     y = groupnorm_gate(o, z, 1e-6, True)
+    x = q.view(B * T, H * d).detach().requires_grad_(True)
+    lw = torch.ones(H * d, device=dev, requires_grad=True); lb = torch.zeros(H * d, device=dev, requires_grad=True)
+    ln_y = layer_norm(x, lw, lb, 1e-6)
+    ln_dy = dy.view(B * T, H * d)
     cases = {
+        "layer_norm forward": (lambda: layer_norm(x.detach(), lw.detach(), lb.detach(), 1e-6), 2 * tensor_bytes),
+        "layer_norm backward": (lambda: torch.autograd.grad(ln_y, (x, lw, lb), ln_dy, retain_graph=True), 3 * tensor_bytes),
         "rotary (q and k)": (lambda: _rotate(q, k, ph, False, torch.bfloat16), 4 * tensor_bytes),
         "groupnorm_gate forward": (lambda: groupnorm_gate(o.detach(), z.detach(), 1e-6, True), 3 * tensor_bytes),
         "groupnorm_gate backward": (lambda: torch.autograd.grad(y, (o, z), dy, retain_graph=True), 5 * tensor_bytes),

@@ -425,6 +425,7 @@ int check_norm(int64_t rows, int32_t d, int32_t dtype, const void* a, int64_t a_
 int fpb_layernorm_fwd(int64_t rows, int32_t d, int32_t dtype, float eps, const void* x, int64_t x_stride,
                       const float* weight, const float* bias, void* y, int64_t y_stride, fpb_stream_t stream) {
   FPB_TRY(check_norm(rows, d, dtype, x, x_stride, y, y_stride));
+  if ((uintptr_t)weight % 16 || (uintptr_t)bias % 16) return FPB_ERR_BAD_STRIDE;
   FPB_TRY(check_device());
   if (rows == 0) return FPB_OK;
   launch_layernorm(dtype, false, rows, d, eps, x, x_stride, weight, bias, y, y_stride, nullptr, nullptr, nullptr, nullptr,
@@ -437,6 +438,7 @@ int fpb_layernorm_bwd(int64_t rows, int32_t d, int32_t dtype, float eps, const v
                       fpb_stream_t stream) {
   FPB_TRY(check_norm(rows, d, dtype, x, x_stride, d_y, dy_stride));
   if (rows > 0 && (!d_x || (uintptr_t)d_x % 16)) return d_x ? FPB_ERR_BAD_STRIDE : FPB_ERR_NULL_POINTER;
+  if ((uintptr_t)weight % 16) return FPB_ERR_BAD_STRIDE;
   FPB_TRY(check_device());
   // the kernel adds its partial sums into the two gradient vectors
   if (d_weight && cudaMemsetAsync(d_weight, 0, sizeof(float) * d, (cudaStream_t)stream) != cudaSuccess) return finish_launches(0, -1);

@@ -416,6 +416,20 @@ template <typename T, int V> __device__ __forceinline__ void store16v(T* ptr, co
   *reinterpret_cast<uint4*>(ptr) = raw;
 }
 
+// V consecutive fp32 parameters starting at channel c (16-byte loads), or `fill` when there is no such parameter
+template <int V> __device__ __forceinline__ void load_params(const float* base, int c, float fill, float (&f)[V]) {
+  if (base) {
+#pragma unroll
+    for (int i = 0; i < V / 4; ++i) {
+      const float4 a = __ldg(reinterpret_cast<const float4*>(base + c) + i);
+      f[4 * i] = a.x; f[4 * i + 1] = a.y; f[4 * i + 2] = a.z; f[4 * i + 3] = a.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < V; ++i) f[i] = fill;
+  }
+}
+
 template <typename T, int NPASS, bool BWD>
 __global__ void __launch_bounds__(BWD ? 128 : 256) layernorm_kernel(const __grid_constant__ NormParams p) {
   constexpr int V = 16 / sizeof(T);
@@ -462,12 +476,11 @@ __global__ void __launch_bounds__(BWD ? 128 : 256) layernorm_kernel(const __grid
       for (int i = 0; i < NPASS; ++i) {
         const int c = V * (lane + 32 * i);
         if (c < p.d) {
-          float res[V];
+          float res[V], w[V], b[V];
+          load_params<V>(p.w, c, 1.0f, w);
+          load_params<V>(p.b, c, 0.0f, b);
 #pragma unroll
-          for (int e = 0; e < V; ++e) {
-            const float w = p.w ? __ldg(p.w + c + e) : 1.0f, b = p.b ? __ldg(p.b + c + e) : 0.0f;
-            res[e] = xv[i][e] * rstd * w + b;
-          }
+          for (int e = 0; e < V; ++e) res[e] = xv[i][e] * rstd * w[e] + b[e];
           store16v<T, V>(y + c, res);
         }
       }
@@ -478,12 +491,14 @@ __global__ void __launch_bounds__(BWD ? 128 : 256) layernorm_kernel(const __grid
       for (int i = 0; i < NPASS; ++i) {
         const int c = V * (lane + 32 * i);
         if (c < p.d) {
+          float w[V];
+          load_params<V>(p.w, c, 1.0f, w);
 #pragma unroll
           for (int e = 0; e < V; ++e) {
             const float n = xv[i][e] * rstd, g = dv[i][e];
             gw[i][e] += g * n;
             gb[i][e] += g;
-            const float dn = p.w ? g * __ldg(p.w + c + e) : g;
+            const float dn = g * w[e];
             xv[i][e] = n; dv[i][e] = dn;
             s1 += dn;
             s2 += dn * n;
@@ -561,14 +576,24 @@ int launch_layernorm(int dtype, bool backward, int64_t rows, int d, float eps, c
   const int wpb = backward ? 4 : 8;
   // backward: every CTA ends with 2d atomic adds, so no more CTAs than keep the SMs full
   const int64_t blocks = (rows + wpb - 1) / wpb;
-  const int cap = backward ? 148 * 4 : 148 * 16;
-  const int grid = (int)(blocks < 1 ? 1 : (blocks < cap ? blocks : cap));
   const size_t smem = backward ? 2 * (size_t)d * sizeof(float) : 0;
   auto go = [&](auto tag, auto passes) {
     using T = decltype(tag);
     constexpr int NP = decltype(passes)::value;
-    if (backward) layernorm_kernel<T, NP, true><<<grid, 128, smem, stream>>>(p);
-    else layernorm_kernel<T, NP, false><<<grid, 256, 0, stream>>>(p);
+    if (backward) {
+      // one wave of resident CTAs, each walking its share of the rows: a second, partial wave would cost as much
+      // as a full one, and every CTA ends with 2d atomic adds
+      int per_sm = 0, sms = 148, dev = 0;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, layernorm_kernel<T, NP, true>, 128, smem) != cudaSuccess || per_sm < 1)
+        per_sm = 1;
+      const int64_t cap = (int64_t)per_sm * sms;
+      layernorm_kernel<T, NP, true><<<(int)(blocks < 1 ? 1 : (blocks < cap ? blocks : cap)), 128, smem, stream>>>(p);
+    } else {
+      const int64_t cap = 148 * 16;
+      layernorm_kernel<T, NP, false><<<(int)(blocks < 1 ? 1 : (blocks < cap ? blocks : cap)), 256, 0, stream>>>(p);
+    }
   };
   auto by_passes = [&](auto tag) {
     if (npass == 1) go(tag, std::integral_constant<int, 1>{});
