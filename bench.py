@@ -422,7 +422,9 @@ def main():
 
     B, H, T, dk, dv = w["B"], w["H"], w["T"], w["dk"], w["dv"]
     dec = decays_for(H)
-    hq, hk, hv, hdO = make_host_inputs(w, seed=2 + rank, pin=True)
+    from flash_pop_b200.host_io import allocate_near
+    with allocate_near(dev):                 # pinned host buffers in the memory of the GPU's own NUMA node
+        hq, hk, hv, hdO = make_host_inputs(w, seed=2 + rank, pin=True)
     q, k, v, dO = (t.to(dev, non_blocking=True) for t in (hq, hk, hv, hdO))
     torch.cuda.synchronize()
 
@@ -482,8 +484,9 @@ def main():
     h2d = sum(t.numel() * 2 for t in (hq, hk, hv, hdO))
     d2h = (2 * hq.numel() + 2 * hv.numel()) * 2
     if not args.no_e2e:
-        outs_host = [torch.empty_like(hv).pin_memory(), torch.empty_like(hq).pin_memory(),
-                     torch.empty_like(hk).pin_memory(), torch.empty_like(hv).pin_memory()]
+        with allocate_near(dev):
+            outs_host = [torch.empty_like(hv).pin_memory(), torch.empty_like(hq).pin_memory(),
+                         torch.empty_like(hk).pin_memory(), torch.empty_like(hv).pin_memory()]
         if w["block"]:
             def e2e_step():
                 nonlocal q, k, v, dO

@@ -51,3 +51,44 @@ class HostRetentionPipeline:
                 for dst, src in ((ho, self.o), (hdq, self.dq), (hdk, self.dk), (hdv, self.dv)):
                     dst[a:b].copy_(src[a:b], non_blocking=True)
         cur.wait_stream(self.s_out)
+
+
+def _parse_cpulist(text: str) -> set:
+    cpus = set()
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus.update(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+class allocate_near:
+    """Context manager: while it is open, the calling thread runs on the CPUs that sit next to `device` (the PCI
+    device's ``local_cpulist`` in sysfs), so host buffers allocated and pinned inside land in that NUMA node's memory
+    and copies to the GPU do not cross the socket interconnect.  Does nothing where the topology cannot be read."""
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self.saved = None
+
+    def __enter__(self):
+        try:
+            import os
+            p = torch.cuda.get_device_properties(self.device)
+            bus = f"{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+            with open(f"/sys/bus/pci/devices/{bus}/local_cpulist") as f:
+                near = _parse_cpulist(f.read())
+            allowed = os.sched_getaffinity(0)
+            if near & allowed and (near & allowed) != allowed:
+                self.saved = allowed
+                os.sched_setaffinity(0, near & allowed)
+        except Exception:
+            self.saved = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.saved is not None:
+            import os
+            os.sched_setaffinity(0, self.saved)
+        return False
