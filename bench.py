@@ -508,6 +508,34 @@ def main():
         e2e_ms = event_time_ms(e2e_step, max(3, min(args.steps, 5)))
         barrier()
 
+    # POP only: the prediction-token suffixes (one per block, 80 tokens each) run from the block states in place
+    suffix = None
+    if w["block"]:
+        N, P = T // w["block"], w["block"]
+        gs = torch.Generator().manual_seed(40 + rank)
+        sq, sk, sv = ((torch.randn(B, N, P, H, d_, generator=gs) * dk ** -0.5).to(torch.bfloat16).to(dev) for d_ in (dk, dk, dv))
+        sdo = torch.randn(B, N, P, H, dv, generator=gs).to(torch.bfloat16).to(dev)
+        with torch.no_grad():
+            blocks = fp.flash_pop_retention(q, k, v, None, dec, w["block"])[1]
+
+        def suffix_step():
+            leaves = [t.detach().requires_grad_(True) for t in (sq, sk, sv)]
+            bs = blocks.detach().requires_grad_(True)
+            so = fp.pop_suffix_retention(*leaves, None, bs, dec)
+            so.backward(sdo)
+
+        def suffix_fwd():
+            with torch.no_grad():
+                fp.pop_suffix_retention(sq, sk, sv, None, blocks, dec)
+        for _ in range(3):
+            suffix_step()
+        s_ms, s_fwd = event_time_ms(suffix_step, args.steps), event_time_ms(suffix_fwd, args.steps)
+        s_units = B * N * P * H
+        s_bytes = (bf_ := bytes_per_token_head(dk, dv))[0] * s_units + bf_[1] * s_units
+        suffix = {"ms_fwd_bwd": s_ms, "ms_fwd": s_fwd, "suffixes": B * N, "tokens_each": P,
+                  "hbm_gbs_algorithmic": s_bytes / (s_ms * 1e-3) / 1e9,
+                  "note": "start states read in place from block_states; state gradients written back to d_block_states"}
+
     t_ms = torch.tensor([ms, ms_fwd, ms_bwd, e2e_ms or 0.0, ms_dq, ms_rev], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
@@ -560,6 +588,8 @@ def main():
             "clocks": clocks,
             "gpu_launches": launches,
         }
+        if suffix is not None:
+            line["pop_suffixes"] = suffix
         if e2e_ms is not None:
             line["e2e"] = {"value": total_flop / (e2e_max * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_max,
                            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}

@@ -401,17 +401,23 @@ scan_kernel(const __grid_constant__ ScanParams p) {
     if (NC > 0) {
       // P' may run ahead of the epilogues by the number of P' buffers: buffer n % NP is free again once the
       // intra-chunk product of chunk n - NP has run, which epilogue n - NP has waited for
-      int n_p = 0, n_e = 0;
+      int n_p = 0, n_e = 0, n_acc = 0;      // n_acc: chunks whose accumulator this thread has seen complete
       Chunk ck_p = first, ck_e = first;
       Patience patience{0, 0};
       while (n_e < NC) {
-        if (n_p < NC && n_p < n_e + G::NP && mbar_test_wait(bar(B_SCFULL + n_p % G::NSC), (n_p / G::NSC) & 1)) {
+        // an accumulator's barrier phase stays put until its epilogue has released the buffer, so it can be
+        // tested once, ahead of the epilogue, and P' of the next chunk made first: that is what the tensor pipe
+        // is waiting for, the epilogue only drains
+        if (n_acc < n_p && n_acc < n_e + G::NACC && mbar_test_wait(bar(B_ACCFULL + n_acc % G::NACC), (n_acc / G::NACC) & 1)) {
+          if (t == 0) FPB_TRACE(8, n_acc);
+          ++n_acc;
+        }
+        if (n_p < NC && n_p < n_acc + G::NP && mbar_test_wait(bar(B_SCFULL + n_p % G::NSC), (n_p / G::NSC) & 1)) {
           if (t == 0) FPB_TRACE(6, n_p);
           make_p(n_p, ck_p.L);
           ++n_p; advance<REV>(ck_p, p.T, p.block_size);
           patience.progress();
-        } else if (n_e < n_p && mbar_test_wait(bar(B_ACCFULL + n_e % G::NACC), (n_e / G::NACC) & 1)) {
-          if (t == 0) FPB_TRACE(8, n_e);
+        } else if (n_e < n_acc) {
           if (!epilogue(n_e, ck_e, false)) break;
           ++n_e; advance<REV>(ck_e, p.T, p.block_size);
           patience.progress();
@@ -422,9 +428,9 @@ scan_kernel(const __grid_constant__ ScanParams p) {
         } else {
           // idle: sleep in hardware on the barrier most likely to complete next (leaves the issue slots to the
           // warps that have work, wakes at once when that barrier completes)
-          const bool want_p = n_p < NC && n_p < n_e + G::NP;
+          const bool want_p = n_p < NC && n_p < n_acc + G::NP;
           if (want_p) mbar_try_wait_hint(bar(B_SCFULL + n_p % G::NSC), (n_p / G::NSC) & 1, 200);
-          else mbar_try_wait_hint(bar(B_ACCFULL + n_e % G::NACC), (n_e / G::NACC) & 1, 200);
+          else mbar_try_wait_hint(bar(B_ACCFULL + n_acc % G::NACC), (n_acc / G::NACC) & 1, 200);
         }
       }
       if (t == 0) tma_store_wait_all0();
