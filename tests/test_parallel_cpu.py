@@ -63,3 +63,36 @@ def test_two_ranks_reproduce_the_unsharded_result(case):
         assert p.exitcode == 0
     o_ok, s_ok, slowest = out.get()
     assert o_ok and s_ok and slowest == 11.0
+
+
+def _failing_worker(rank, world, port, out):
+    """Rank 1 fails on the host before the gradient all-reduce; rank 0 must get an error out of its collective
+    within the process-group timeout instead of waiting for ever."""
+    import datetime
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    dist.barrier()                                     # both ranks are up
+    if rank == 1:
+        os._exit(0)                                    # dies between steps, nothing of its own in flight
+    t0 = time.time()
+    try:
+        dist.all_reduce(torch.ones(4))
+        out.put(("no error", time.time() - t0))
+    except Exception as e:                             # gloo reports the lost peer or the timeout
+        out.put((type(e).__name__, time.time() - t0))
+    os._exit(0)                                        # the group is broken: leave without the collective teardown
+
+
+def test_a_lost_rank_ends_the_survivors_collective_with_an_error():
+    ctx = mp.get_context("spawn")
+    out = ctx.SimpleQueue()
+    port = 31500 + os.getpid() % 2000
+    procs = [ctx.Process(target=_failing_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    kind, waited = out.get()
+    assert kind != "no error" and waited < 30, (kind, waited)
