@@ -55,6 +55,7 @@ constexpr int MODE_FWD = 0, MODE_DQ = 1;
 constexpr int SCORE_WARP0 = 2, STATE_WARP0 = 6;
 constexpr int N_SCORE = 128;
 
+
 struct ScanParams {
   CUtensorMap map_x, map_k, map_v, map_out;
   bf16* out; int64_t out_sb, out_st, out_sh;
@@ -78,6 +79,9 @@ template <int MODE, int R, int CC>
 struct Cfg {
   static constexpr int W1 = MODE == MODE_FWD ? R : CC;       // width of X (and of the Sc contraction)
   static constexpr int NOUT = MODE == MODE_FWD ? CC : R;     // width of the output tile
+  // Output rows go from tensor memory through registers straight to global memory (measured faster for 64-wide
+  // output tiles) or through a staging tile and a TMA store (faster for the wider ones).
+  static constexpr bool DIRECT_OUT = NOUT == 64;
   // one CTA per SM for the large state tiles (128x128, 64x256), two for the small ones
   static constexpr bool ONE = R * CC >= 128 * 128;
   static constexpr int STATE_WARPS = ONE ? 8 : 4;
@@ -398,6 +402,38 @@ scan_kernel(const __grid_constant__ ScanParams p) {
       return true;
     };
 
+    // E(n) without the staging tile: with the 32-lane load shape thread t of a warp reads tensor-memory lane
+    // 32*q4 + t, i.e. row 16*q4 + (t & 15) of accumulator buffer t >> 4 (the two buffers interleave in lanes), 32
+    // consecutive columns at a time; the threads of buffer n & 1 scale, pack and store 64 bytes each per load.  No
+    // thread waits for another, rows >= L are simply not stored, and the shared-memory port is left to the MMAs.
+    auto epilogue_direct = [&](int n, Chunk ck) {
+      tc_fence_after();
+      const int row = q4 * 16 + (lane & 15);
+      const bool mine = (lane >> 4) == (n & 1) && row < ck.L;
+      const float z = REV ? exp2f((float)(ck.L - 1 - row) * lg) * rs : exp2f((float)(row + 1) * lg);
+      const int ocol0 = MODE == MODE_FWD ? col0 : row0;
+      bf16* go = p.out + (int64_t)b * p.out_sb + (int64_t)h * p.out_sh + (int64_t)(ck.a + row) * p.out_st + ocol0;
+#pragma unroll 1
+      for (int c0 = 0; c0 < G::NOUT; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tm + lane_base + G::TM_ACC + c0, r);
+        tmem_wait_ld();
+        if (c0 + 32 == G::NOUT) { tc_fence_before(); mbar_arrive(bar(B_ACCFREE + n % G::NACC)); }
+        if (mine) {
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            uint4 val;
+            val.x = pack_bf16(__uint_as_float(r[8 * v4]) * z, __uint_as_float(r[8 * v4 + 1]) * z);
+            val.y = pack_bf16(__uint_as_float(r[8 * v4 + 2]) * z, __uint_as_float(r[8 * v4 + 3]) * z);
+            val.z = pack_bf16(__uint_as_float(r[8 * v4 + 4]) * z, __uint_as_float(r[8 * v4 + 5]) * z);
+            val.w = pack_bf16(__uint_as_float(r[8 * v4 + 6]) * z, __uint_as_float(r[8 * v4 + 7]) * z);
+            *reinterpret_cast<uint4*>(go + c0 + 8 * v4) = val;
+          }
+        }
+      }
+      if (t == 0) FPB_TRACE(10, n);
+    };
+
     if (NC > 0) {
       // P' may run ahead of the epilogues by the number of P' buffers: buffer n % NP is free again once the
       // intra-chunk product of chunk n - NP has run, which epilogue n - NP has waited for
@@ -418,12 +454,13 @@ scan_kernel(const __grid_constant__ ScanParams p) {
           ++n_p; advance<REV>(ck_p, p.T, p.block_size);
           patience.progress();
         } else if (n_e < n_acc) {
-          if (!epilogue(n_e, ck_e, false)) break;
+          if (G::DIRECT_OUT) epilogue_direct(n_e, ck_e);
+          else if (!epilogue(n_e, ck_e, false)) break;
           ++n_e; advance<REV>(ck_e, p.T, p.block_size);
           patience.progress();
         } else if (patience.exhausted(abort_flag)) {
           FPB_GIVE_UP(0x300 | (n_e & 0xff));
-          epilogue(n_e, ck_e, true);     // meet the others at the epilogue's first barrier and leave with them
+          if (!G::DIRECT_OUT) epilogue(n_e, ck_e, true);     // meet the others at the epilogue's first barrier and leave with them
           break;
         } else {
           // idle: sleep in hardware on the barrier most likely to complete next (leaves the issue slots to the
@@ -433,7 +470,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
           else mbar_try_wait_hint(bar(B_ACCFULL + n_acc % G::NACC), (n_acc / G::NACC) & 1, 200);
         }
       }
-      if (t == 0) tma_store_wait_all0();
+      if (!G::DIRECT_OUT && t == 0) tma_store_wait_all0();
     }
   } else {                                           // ---------------- state warps
     const int t = tid - STATE_WARP0 * 32;            // 0..N_STATE-1
