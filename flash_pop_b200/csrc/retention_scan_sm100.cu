@@ -57,7 +57,7 @@ constexpr int N_SCORE = 128;
 
 
 struct ScanParams {
-  CUtensorMap map_x, map_k, map_v, map_out;
+  CUtensorMap map_x, map_k, map_v, map_out;   // map_out: 16-row boxes
   bf16* out; int64_t out_sb, out_st, out_sh;
   const bf16* s0; int64_t s0_sb, s0_sh;
   bf16* s_out; int64_t so_sb, so_sh;
@@ -352,12 +352,14 @@ scan_kernel(const __grid_constant__ ScanParams p) {
       if (t == 0) FPB_TRACE(7, n);
     };
 
-    // E(n): out_i = rowscale_i * ACC_i -> staging tile -> TMA store.  `fail` makes all 128 threads leave
-    // together at the first barrier when some thread's polling gave up.  Returns false when leaving.
-    auto epilogue = [&](int n, Chunk ck, bool fail) -> bool {
-      // the previous TMA store must have finished reading the staging tile
-      if (t == 0) tma_store_wait_read0();
-      if (named_bar_or(1, N_SCORE, fail)) return false;
+    // E(n): out_i = rowscale_i * ACC_i -> staging tile -> TMA store.  Each warp owns 16 rows of the accumulator (its
+    // tensor-memory sub-partition) and stores them itself - its 2 KB slice of every 64-column block of the staging
+    // tile is a whole number of 1024-byte swizzle patterns, so it is a valid TMA source on its own - which leaves
+    // the four score warps free of one another: no warp waits at a barrier for the slowest.
+    auto epilogue = [&](int n, Chunk ck) {
+      // this warp's previous TMA stores must have finished reading its slice of the staging tile
+      if (lane == 0) tma_store_wait_read0();
+      __syncwarp();
       if (t == 0) FPB_TRACE(9, n);
       tc_fence_after();
       // row scale: zeta_i (forward walks) or eta_j * rs (reverse walks)
@@ -379,27 +381,29 @@ scan_kernel(const __grid_constant__ ScanParams p) {
         }
       }
       const bool whole_box = ck.L == C || ck.a + ck.L >= p.T;   // rows beyond L are past the sequence end: TMA clips them
-      if (whole_box) fence_async_smem();
-      named_bar_sync(2, N_SCORE);
+      const int wrow0 = q4 * 16;                                // this warp's rows [wrow0, wrow0 + 16)
       const int ocol0 = MODE == MODE_FWD ? col0 : row0;
       if (whole_box) {
-        if (t == 0) {
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0 && ck.a + wrow0 < p.T) {
 #pragma unroll
-          for (int cb = 0; cb < G::NOUT / 64; ++cb) tma_store_4d(&p.map_out, sbase + G::OFF_OUT + cb * 8192, ocol0 + cb * 64, ck.a, h, b);
+          for (int cb = 0; cb < G::NOUT / 64; ++cb)
+            tma_store_4d(&p.map_out, sbase + G::OFF_OUT + cb * 8192 + wrow0 * 128, ocol0 + cb * 64, ck.a + wrow0, h, b);
           tma_store_commit();
         }
       } else {   // chunk cut short by a block end: rows >= L belong to another chunk, store rows < L only
+        __syncwarp();
         bf16* go = p.out + (int64_t)b * p.out_sb + (int64_t)h * p.out_sh + ocol0;
-        for (int idx = t; idx < ck.L * (G::NOUT / 8); idx += N_SCORE) {
-          const int row = idx / (G::NOUT / 8), ch = idx % (G::NOUT / 8);
+        const int rows = min(16, ck.L - wrow0);
+        for (int idx = lane; idx < rows * (G::NOUT / 8); idx += 32) {
+          const int row = wrow0 + idx / (G::NOUT / 8), ch = idx % (G::NOUT / 8);
           const uint4 val = *reinterpret_cast<const uint4*>(stg + (ch >> 3) * 8192 + row * 128 + (((ch & 7) ^ (row & 7)) << 4));
           *reinterpret_cast<uint4*>(go + (int64_t)(ck.a + row) * p.out_st + ch * 8) = val;
         }
-        // these generic reads of the staging tile are ordered before its next rewrite by the barrier at
-        // the top of the next epilogue
+        __syncwarp();   // these generic reads of the slice come before its next rewrite
       }
       if (t == 0) FPB_TRACE(10, n);
-      return true;
     };
 
     // E(n) without the staging tile: with the 32-lane load shape thread t of a warp reads tensor-memory lane
@@ -455,12 +459,11 @@ scan_kernel(const __grid_constant__ ScanParams p) {
           patience.progress();
         } else if (n_e < n_acc) {
           if (G::DIRECT_OUT) epilogue_direct(n_e, ck_e);
-          else if (!epilogue(n_e, ck_e, false)) break;
+          else epilogue(n_e, ck_e);
           ++n_e; advance<REV>(ck_e, p.T, p.block_size);
           patience.progress();
         } else if (patience.exhausted(abort_flag)) {
           FPB_GIVE_UP(0x300 | (n_e & 0xff));
-          if (!G::DIRECT_OUT) epilogue(n_e, ck_e, true);     // meet the others at the epilogue's first barrier and leave with them
           break;
         } else {
           // idle: sleep in hardware on the barrier most likely to complete next (leaves the issue slots to the
@@ -470,7 +473,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
           else mbar_try_wait_hint(bar(B_ACCFULL + n_acc % G::NACC), (n_acc / G::NACC) & 1, 200);
         }
       }
-      if (!G::DIRECT_OUT && t == 0) tma_store_wait_all0();
+      if (!G::DIRECT_OUT && lane == 0) tma_store_wait_all0();
     }
   } else {                                           // ---------------- state warps
     const int t = tid - STATE_WARP0 * 32;            // 0..N_STATE-1
@@ -729,7 +732,7 @@ int launch_pass(const PassArgs& a, cudaStream_t stream) {
   if ((r = make_seq_map(&p.map_x, a.x, B, T, H, xw, C)) != FPB_OK) return r;
   if ((r = make_seq_map(&p.map_k, a.k, B, T, H, dk, C)) != FPB_OK) return r;
   if ((r = make_seq_map(&p.map_v, a.v, B, T, H, dv, C)) != FPB_OK) return r;
-  if ((r = make_seq_map(&p.map_out, a.out, B, T, H, ow, C)) != FPB_OK) return r;
+  if ((r = make_seq_map(&p.map_out, a.out, B, T, H, ow, 16)) != FPB_OK) return r;   // one score warp's 16 rows
   p.out = (bf16*)a.out.data; p.out_sb = a.out.sb; p.out_st = a.out.st; p.out_sh = a.out.sh;
   p.s0 = (const bf16*)a.start.data; p.s0_sb = a.start.sb; p.s0_sh = a.start.sh;
   p.s_out = (bf16*)a.end.data; p.so_sb = a.end.sb; p.so_sh = a.end.sh;
