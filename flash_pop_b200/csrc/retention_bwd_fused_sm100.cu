@@ -45,6 +45,7 @@ struct BwdParams {
   bf16* g_end; int64_t ge_sb, ge_sh;             // dS_0 (end of the reverse walk), or null
   const bf16* block_grads;                       // POP: gradients of the block states (B, NB, H, dk, dv), or null
   bf16* sfx_blocks; int32_t sfx_M, sfx_N;        // suffix calls: gradients of the start states taken from block states
+  int32_t sfx_G;                                 // suffixes one CTA walks back to back as one sequence (>= 1)
   int32_t T, H, dk, dv, block_size, n_blocks;
   int32_t* status;
   long long* trace;
@@ -392,10 +393,17 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
     // end: dS_0, or for suffix m > 0 of a row the gradient of block state m-1
     const bf16* x_start = nullptr;
     bf16* x_end = nullptr;
+    // suffix calls: the batch index is (row, group of sfx_G consecutive suffixes); the walk goes through the group's
+    // suffixes from the last to the first, and what it carries when it leaves suffix m is the gradient of the state
+    // that suffix started from
+    const int groups = p.sfx_M > 0 ? p.sfx_M / p.sfx_G : 1;
+    const int sfx_row = b / groups, sfx_m0 = (b % groups) * p.sfx_G;
+    auto sfx_grad = [&](int m) -> bf16* {
+      if (m == 0) return p.g_end ? p.g_end + sfx_row * p.ge_sb + h * p.ge_sh : nullptr;
+      return p.sfx_blocks ? p.sfx_blocks + (((int64_t)sfx_row * p.sfx_N + (m - 1)) * p.H + h) * state_elems : nullptr;
+    };
     if (p.sfx_M > 0) {
-      const int row = b / p.sfx_M, m = b % p.sfx_M;
-      if (m == 0) x_end = p.g_end ? p.g_end + row * p.ge_sb + h * p.ge_sh : nullptr;
-      else x_end = p.sfx_blocks ? p.sfx_blocks + (((int64_t)row * p.sfx_N + (m - 1)) * p.H + h) * state_elems : nullptr;
+      if (p.sfx_G == 1) x_end = sfx_grad(sfx_m0);      // grouped walks store at every suffix start, inside the loop
     } else {
       if (p.g_start) x_start = p.g_start + b * p.gs_sb + h * p.gs_sh;
       if (p.g_end) x_end = p.g_end + b * p.ge_sb + h * p.ge_sh;
@@ -533,6 +541,12 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
           tc_fence_before();
           mbar_arrive(bar(B_DSFREE + (n_u & 1)));
           ++n_u;
+          if (p.sfx_G > 1 && ck_u.a % p.block_size == 0) {   // that was the first chunk of a suffix
+            bf16* dst = sfx_grad(sfx_m0 + ck_u.a / p.block_size);
+            if (dst) store_global(dst);
+#pragma unroll
+            for (int i = 0; i < G::NS; ++i) S[i] = 0.f;      // the suffix before it ends in a state nobody reads
+          }
           if (n_u < NC) {
             prev_chunk(ck_u, p.block_size);
             inject(ck_u.a + ck_u.L);
@@ -585,20 +599,33 @@ int launch_bwd_fused(const UmmaBwdArgs& a, cudaStream_t stream) {
     return FPB_UMMA_NOT_APPLICABLE;
   BwdParams p;
   int r;
-  const int B = a.B, T = a.T, H = a.H;
-  if ((r = make_seq_map(&p.map_q, a.q, B, T, H, a.dk, C)) != FPB_OK) return r;
-  if ((r = make_seq_map(&p.map_k, a.k, B, T, H, a.dk, C)) != FPB_OK) return r;
-  if ((r = make_seq_map(&p.map_v, a.v, B, T, H, a.dv, C)) != FPB_OK) return r;
-  if ((r = make_seq_map(&p.map_do, a.dO, B, T, H, a.dv, C)) != FPB_OK) return r;
-  if ((r = make_seq_map(&p.map_dk, a.dK, B, T, H, a.dk, C)) != FPB_OK) return r;
-  if ((r = make_seq_map(&p.map_dv, a.dV, B, T, H, a.dv, C)) != FPB_OK) return r;
-  p.dk_out = (bf16*)a.dK.data; p.dk_sb = a.dK.sb; p.dk_st = a.dK.st; p.dk_sh = a.dK.sh;
-  p.dv_out = (bf16*)a.dV.data; p.dv_sb = a.dV.sb; p.dv_st = a.dV.st; p.dv_sh = a.dV.sh;
+  int B = a.B, T = a.T, block_size = a.block_size;
+  const int H = a.H;
+  // suffix calls: G consecutive suffixes of a row as one sequence per CTA (see launch_pass in retention_scan_sm100.cu)
+  SeqView q = a.q, k = a.k, v = a.v, dO = a.dO, dK = a.dK, dV = a.dV;
+  int G = 1;
+  if (a.sfx_grad.M > 1 && a.block_size == 0) {
+    bool contiguous = true;
+    for (const SeqView* s : {&q, &k, &v, &dO, &dK, &dV}) contiguous = contiguous && s->sb == (int64_t)T * s->st;
+    if (contiguous) G = choose_suffix_group(a.sfx_grad.M, (long long)(B / a.sfx_grad.M) * H);
+    if (G > 1) {
+      B /= G; block_size = T; T *= G;
+      for (SeqView* s : {&q, &k, &v, &dO, &dK, &dV}) s->sb *= G;
+    }
+  }
+  if ((r = make_seq_map(&p.map_q, q, B, T, H, a.dk, C)) != FPB_OK) return r;
+  if ((r = make_seq_map(&p.map_k, k, B, T, H, a.dk, C)) != FPB_OK) return r;
+  if ((r = make_seq_map(&p.map_v, v, B, T, H, a.dv, C)) != FPB_OK) return r;
+  if ((r = make_seq_map(&p.map_do, dO, B, T, H, a.dv, C)) != FPB_OK) return r;
+  if ((r = make_seq_map(&p.map_dk, dK, B, T, H, a.dk, C)) != FPB_OK) return r;
+  if ((r = make_seq_map(&p.map_dv, dV, B, T, H, a.dv, C)) != FPB_OK) return r;
+  p.dk_out = (bf16*)dK.data; p.dk_sb = dK.sb; p.dk_st = dK.st; p.dk_sh = dK.sh;
+  p.dv_out = (bf16*)dV.data; p.dv_sb = dV.sb; p.dv_st = dV.st; p.dv_sh = dV.sh;
   p.g_start = (const bf16*)a.d_s_out.data; p.gs_sb = a.d_s_out.sb; p.gs_sh = a.d_s_out.sh;
   p.g_end = (bf16*)a.d_s0.data; p.ge_sb = a.d_s0.sb; p.ge_sh = a.d_s0.sh;
   p.block_grads = (const bf16*)a.d_block_states;
-  p.sfx_blocks = (bf16*)a.sfx_grad.blocks; p.sfx_M = a.sfx_grad.M; p.sfx_N = a.sfx_grad.N;
-  p.T = T; p.H = H; p.dk = a.dk; p.dv = a.dv; p.block_size = a.block_size; p.n_blocks = a.n_blocks;
+  p.sfx_blocks = (bf16*)a.sfx_grad.blocks; p.sfx_M = a.sfx_grad.M; p.sfx_N = a.sfx_grad.N; p.sfx_G = G;
+  p.T = T; p.H = H; p.dk = a.dk; p.dv = a.dv; p.block_size = block_size; p.n_blocks = a.n_blocks;
   p.status = device_status_ptr();
   p.trace = debug_trace_ptr();
   if (!p.status) return FPB_ERR_LAUNCH;

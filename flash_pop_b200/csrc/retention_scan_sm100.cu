@@ -64,6 +64,7 @@ struct ScanParams {
   bf16* block_states;            // forward walk: states after full blocks (written)
   const bf16* block_grads;       // reverse walk: gradients of those states (read)
   bf16* sfx_blocks; int32_t sfx_M, sfx_N;   // suffix calls: start states (forward) / their gradients (reverse)
+  int32_t sfx_G;                 // suffixes walked back to back by one CTA as one sequence of sfx_G * block_size tokens (>= 1)
   int32_t T, H, dk, dv, block_size, n_blocks;
   int32_t* status;
   long long* trace;              // diagnostics: per-chunk clock64() stamps of CTA (0,0,0), or null
@@ -497,10 +498,17 @@ scan_kernel(const __grid_constant__ ScanParams p) {
     // gradient of that start state.
     const bf16* x_start = nullptr;
     bf16* x_end = nullptr;
+    // suffix calls: the batch index is (row, group of sfx_G consecutive suffixes)
+    const int groups = p.sfx_M > 0 ? p.sfx_M / p.sfx_G : 1;
+    const int sfx_row = b / groups, sfx_m0 = (b % groups) * p.sfx_G;
+    auto sfx_start = [&](int m) -> const bf16* {       // where suffix m of this row starts from (forward walks)
+      if (m == 0) return p.s0 ? p.s0 + sfx_row * p.s0_sb + h * p.s0_sh : nullptr;
+      return p.sfx_blocks ? p.sfx_blocks + (((int64_t)sfx_row * p.sfx_N + (m - 1)) * p.H + h) * state_elems : nullptr;
+    };
     if (p.sfx_M > 0) {
-      const int row = b / p.sfx_M, m = b % p.sfx_M;
+      const int row = sfx_row, m = sfx_m0;
       bf16* blk = (m > 0 && p.sfx_blocks) ? p.sfx_blocks + (((int64_t)row * p.sfx_N + (m - 1)) * p.H + h) * state_elems : nullptr;
-      if (!REV) x_start = m == 0 ? (p.s0 ? p.s0 + row * p.s0_sb + h * p.s0_sh : nullptr) : blk;
+      if (!REV) x_start = sfx_start(m);
       else x_end = m == 0 ? (p.s_out ? p.s_out + row * p.so_sb + h * p.so_sh : nullptr) : blk;
     } else {
       if (p.s0) x_start = p.s0 + b * p.s0_sb + h * p.s0_sh;
@@ -655,6 +663,15 @@ scan_kernel(const __grid_constant__ ScanParams p) {
           ++n_u;
           if (n_u < NC) {
             advance<REV>(ck_u, p.T, p.block_size);
+            if (!REV && p.sfx_G > 1 && ck_u.a % p.block_size == 0) {
+              // grouped suffixes: the next chunk opens the next suffix, which starts from its own state
+              const bf16* src = sfx_start(sfx_m0 + ck_u.a / p.block_size);
+              if (src) load_global(src, false);
+              else {
+#pragma unroll
+                for (int i = 0; i < G::NS; ++i) S[i] = 0.f;
+              }
+            }
             inject(ck_u.a + ck_u.L);
             publish_due = true;
           }
@@ -695,6 +712,8 @@ int launch_scan(const ScanParams& p, bool rev, dim3 grid, cudaStream_t stream) {
 }
 
 int g_tile_pref = 1;            // 1: 128x128 state tiles where they apply; 0: 64-wide tiles (two CTAs per SM)
+int g_sfx_group = 16;           // most suffixes one CTA walks back to back (1: one CTA per suffix)
+int g_sfx_min_ctas = 3 * 296;   // ... as long as that many CTAs remain (three waves of two CTAs per SM)
 int g_fused_bwd = 1;            // 1: dK, dV, dS_0 in one fused reverse walk where it applies; 0: two separate walks
 long long* g_trace = nullptr;   // set by fpb_debug_trace
 
@@ -729,23 +748,38 @@ int launch_pass(const PassArgs& a, cudaStream_t stream) {
   const int B = a.B, T = a.T, H = a.H, dk = a.dk, dv = a.dv;
   ScanParams p;
   int r;
-  if ((r = make_seq_map(&p.map_x, a.x, B, T, H, xw, C)) != FPB_OK) return r;
-  if ((r = make_seq_map(&p.map_k, a.k, B, T, H, dk, C)) != FPB_OK) return r;
-  if ((r = make_seq_map(&p.map_v, a.v, B, T, H, dv, C)) != FPB_OK) return r;
-  if ((r = make_seq_map(&p.map_out, a.out, B, T, H, ow, 16)) != FPB_OK) return r;   // one score warp's 16 rows
-  p.out = (bf16*)a.out.data; p.out_sb = a.out.sb; p.out_st = a.out.st; p.out_sh = a.out.sh;
+  // Suffix calls are thousands of sequences of a few chunks.  Where the suffixes of a row follow one another in
+  // memory, G of them are walked by one CTA as one sequence of G * T tokens whose state is replaced at every suffix
+  // start (block size = suffix length, so no chunk straddles two suffixes): the CTA's set-up and pipeline fill are
+  // paid once per G suffixes.  G is the largest divisor of M that still leaves a few waves of CTAs.
+  int G = 1;
+  SeqView x = a.x, k = a.k, v = a.v, out = a.out;
+  int Bk = B, Tk = T, block_size = a.block_size;
+  if (a.sfx.M > 1 && !a.rev && g_sfx_group && a.block_size == 0 && x.sb == (int64_t)T * x.st && k.sb == (int64_t)T * k.st &&
+      v.sb == (int64_t)T * v.st && out.sb == (int64_t)T * out.st) {
+    G = choose_suffix_group(a.sfx.M, (long long)(B / a.sfx.M) * H * (a.mode == MODE_FWD ? (dv + 127) / 128 : (dk + 127) / 128));
+    if (G > 1) {
+      Bk = B / G; Tk = T * G; block_size = T;
+      x.sb *= G; k.sb *= G; v.sb *= G; out.sb *= G;
+    }
+  }
+  if ((r = make_seq_map(&p.map_x, x, Bk, Tk, H, xw, C)) != FPB_OK) return r;
+  if ((r = make_seq_map(&p.map_k, k, Bk, Tk, H, dk, C)) != FPB_OK) return r;
+  if ((r = make_seq_map(&p.map_v, v, Bk, Tk, H, dv, C)) != FPB_OK) return r;
+  if ((r = make_seq_map(&p.map_out, out, Bk, Tk, H, ow, 16)) != FPB_OK) return r;   // one score warp's 16 rows
+  p.out = (bf16*)out.data; p.out_sb = out.sb; p.out_st = out.st; p.out_sh = out.sh;
   p.s0 = (const bf16*)a.start.data; p.s0_sb = a.start.sb; p.s0_sh = a.start.sh;
   p.s_out = (bf16*)a.end.data; p.so_sb = a.end.sb; p.so_sh = a.end.sh;
   p.block_states = (bf16*)a.block_states;
   p.block_grads = (const bf16*)a.block_grads;
-  p.sfx_blocks = (bf16*)a.sfx.blocks; p.sfx_M = a.sfx.M; p.sfx_N = a.sfx.N;
-  p.T = T; p.H = H; p.dk = dk; p.dv = dv; p.block_size = a.block_size; p.n_blocks = a.n_blocks;
+  p.sfx_blocks = (bf16*)a.sfx.blocks; p.sfx_M = a.sfx.M; p.sfx_N = a.sfx.N; p.sfx_G = G;
+  p.T = Tk; p.H = H; p.dk = dk; p.dv = dv; p.block_size = block_size; p.n_blocks = a.n_blocks;
   p.status = device_status_ptr();
   p.trace = g_trace;
   if (!p.status) return FPB_ERR_LAUNCH;
   for (int h = 0; h < H; ++h) p.log2g[h] = (float)std::log2((double)a.gamma[h]);
 
-#define FPB_SCAN_CASE(MODE_, R_, CC_, TILES_) return launch_scan<MODE_, R_, CC_>(p, a.rev, dim3((TILES_), H, B), stream)
+#define FPB_SCAN_CASE(MODE_, R_, CC_, TILES_) return launch_scan<MODE_, R_, CC_>(p, a.rev, dim3((TILES_), H, Bk), stream)
   if (a.mode == MODE_FWD) {       // state tile: all dk rows x CC columns of dv
     if (dk == 128 && dv % 128 == 0 && g_tile_pref) FPB_SCAN_CASE(MODE_FWD, 128, 128, dv / 128);
     if (dk == 128) FPB_SCAN_CASE(MODE_FWD, 128, 64, dv / 64);
@@ -764,11 +798,20 @@ int launch_pass(const PassArgs& a, cudaStream_t stream) {
 
 long long* debug_trace_ptr() { return g_trace; }
 
+int choose_suffix_group(int M, long long units) {
+  for (int cand = g_sfx_group; cand > 1; --cand)
+    if (M % cand == 0 && units * (M / cand) >= g_sfx_min_ctas) return cand;
+  return 1;
+}
+
 // Diagnostics hook (not part of the public header): install a device buffer of 64*16 int64 that the next
 // launches fill with clock64() stamps of their first CTA; null removes it.
 extern "C" void fpb_debug_trace(void* device_buffer) { g_trace = (long long*)device_buffer; }
 // Diagnostics hook: choose between the 128x128 state tiles (1, default) and the 64-wide ones (0).
 extern "C" void fpb_debug_tile_pref(int wide) { g_tile_pref = wide; }
+// Diagnostics hook: upper limit of the suffixes one CTA walks back to back (1 = one CTA per suffix) and the number of
+// CTAs that must remain.
+extern "C" void fpb_debug_suffix_group(int g, int min_ctas) { g_sfx_group = g < 1 ? 1 : g; if (min_ctas > 0) g_sfx_min_ctas = min_ctas; }
 // Diagnostics hook: 0 runs the dV and dK walks as two launches instead of the fused reverse kernel.
 extern "C" void fpb_debug_fused_bwd(int on) { g_fused_bwd = on; }
 

@@ -32,6 +32,9 @@ int launch_umma_fwd(const UmmaFwdArgs& a, cudaStream_t stream);
 int launch_umma_bwd(const UmmaBwdArgs& a, cudaStream_t stream, int* n_launched);
 // dK, dV, dS_0 in one reverse walk (retention_bwd_fused_sm100.cu)
 int launch_bwd_fused(const UmmaBwdArgs& a, cudaStream_t stream);
+// How many consecutive suffixes of a row one CTA walks as one sequence: the largest divisor of M (up to a limit)
+// that leaves enough CTAs to fill the GPU a few times over; `units` = CTAs per suffix index (rows x heads x tiles).
+int choose_suffix_group(int M, long long units);
 // diagnostics: device buffer for per-chunk time stamps, or null
 long long* debug_trace_ptr();
 

@@ -193,3 +193,37 @@ def test_host_memory_pipeline_equals_direct_call():
     o.backward(dO.cuda())
     for got, want in zip(outs, (o, leaves[0].grad, leaves[1].grad, leaves[2].grad)):
         assert torch.equal(got, want.detach().cpu())
+
+
+@pytest.mark.parametrize("M,N,P,d", [(8, 8, 80, 64), (12, 12, 40, 64), (9, 8, 80, 64), (6, 6, 100, 128)])
+def test_grouped_suffix_walks_equal_one_cta_per_suffix(M, N, P, d):
+    """Consecutive suffixes of a row walked by one CTA as one sequence (state replaced at every suffix start) give
+    bit for bit what one CTA per suffix gives, forward and backward; odd counts and strided tensors fall back."""
+    import ctypes
+    import flash_pop_b200 as fp
+    from flash_pop_b200 import _lib
+    hook = _lib.lib().fpb_debug_suffix_group
+    hook.argtypes = [ctypes.c_int, ctypes.c_int]
+    B, H = 2, 3
+    decays = orc.head_decays(H, (5, 12))
+    g = torch.Generator().manual_seed(M * 100 + P)
+    sq, sk, sv, sdo = ((torch.randn(B, M, P, H, d, generator=g) * d ** -0.5).to(BF).cuda() for _ in range(4))
+    s0 = (torch.randn(B, H, d, d, generator=g) * d ** -0.5).to(BF).cuda()
+    blocks = (torch.randn(B, N, H, d, d, generator=g) * d ** -0.5).to(BF).cuda()
+    results = []
+    try:
+        for limit, floor in ((1, 1), (16, 1)):
+            hook(limit, floor)
+            leaves = [t.detach().clone().requires_grad_(True) for t in (sq, sk, sv, s0, blocks)]
+            o = fp.pop_suffix_retention(leaves[0], leaves[1], leaves[2], leaves[3], leaves[4], decays)
+            assert _lib.last_path() == _lib.PATH_TCGEN05
+            o.backward(sdo)
+            results.append([o.detach()] + [t.grad for t in leaves])
+    finally:
+        hook(16, 3 * 296)
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
+    qd, kd, vd = (t.double().cpu() for t in (sq, sk, sv))
+    o_ref = orc.pop_suffix_retention(qd, kd, vd, s0.double().cpu(), blocks.double().cpu(), decays)
+    assert orc.rel_rms(results[1][0].float().cpu(), o_ref) < 5e-3
+    _lib.device_status()
