@@ -38,6 +38,14 @@
 // their tasks is ready (scores of chunk n+1 before the products of chunk n if that is what has arrived),
 // with the score tile, P' and the accumulator double-buffered where tensor/shared memory allows, so that
 // several chunks are in flight per SM and the chain latency is hidden.
+//
+// Output.  Each score warp owns 16 rows of an accumulator and stores them itself: through its slice of a staging
+// tile and a 16-row TMA store (tiles wider than 64 columns), or straight from tensor memory to global memory
+// (64-column tiles).  No barrier joins the score warps.
+//
+// Suffix calls (thousands of sequences of a few chunks, each starting from its own state and dropping its end
+// state) may be regrouped by the launcher: G consecutive suffixes of a row as one sequence of G*T tokens with block
+// size T, the state replaced at every suffix start - same results, one CTA set-up per G suffixes.
 #include "fpb_common.cuh"
 #include "ptx_sm100.cuh"
 #include "scan_common.cuh"
