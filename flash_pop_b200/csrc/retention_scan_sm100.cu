@@ -837,8 +837,10 @@ int launch_umma_bwd(const UmmaBwdArgs& a, cudaStream_t stream, int* n_launched) 
   *n_launched = 0;
   if (a.dtype != FPB_BF16) return FPB_UMMA_NOT_APPLICABLE;
   const StateView none{nullptr, 0, 0};
+  // dQ needs the states at chunk starts only, never a block state: its walk ignores the POP block structure and
+  // takes full 64-token chunks (fewer chunks than the block-aligned schedule whenever the block is not a multiple of 64)
   PassArgs dq{MODE_DQ, false, a.dO, a.k, a.v, a.dQ, a.s0, none, nullptr, nullptr, a.sfx_in, a.gamma,
-              a.B, a.T, a.H, a.dk, a.dv, a.block_size, a.n_blocks};
+              a.B, a.T, a.H, a.dk, a.dv, 0, 0};
   PassArgs dv{MODE_FWD, true, a.k, a.q, a.dO, a.dV, a.d_s_out, a.d_s0, nullptr, a.d_block_states, a.sfx_grad, a.gamma,
               a.B, a.T, a.H, a.dk, a.dv, a.block_size, a.n_blocks};
   SuffixStates no_write = a.sfx_grad;
