@@ -74,6 +74,8 @@ struct ScanParams {
   bf16* sfx_blocks; int32_t sfx_M, sfx_N;   // suffix calls: start states (forward) / their gradients (reverse)
   int32_t sfx_G;                 // suffixes walked back to back by one CTA as one sequence of sfx_G * block_size tokens (>= 1)
   int32_t T, H, dk, dv, block_size, n_blocks;
+  int32_t sched_bs;              // block size the chunk schedule is cut at: block_size, or 0 when block states are
+                                 // emitted from inside full chunks (forward walk, 64 x 64 tiles, see EMIT below)
   int32_t* status;
   long long* trace;              // diagnostics: per-chunk clock64() stamps of CTA (0,0,0), or null
   float log2g[FPB_MAX_HEADS];
@@ -81,7 +83,7 @@ struct ScanParams {
 
 // barrier slots (8 bytes each) at the start of the barrier page, then two 4-byte words
 enum { B_FULL = 0, B_EMPTY = 3, B_VRDY = 6, B_SCFULL = 9, B_PRDY = 11, B_ACCFULL = 13, B_ACCFREE = 15, B_DSFULL = 17,
-       B_DSFREE = 19, B_SBRDY = 21, B_SBFREE = 22, B_COUNT = 23 };
+       B_DSFREE = 19, B_SBRDY = 21, B_SBFREE = 22, B_DSPFULL = 23, B_DSPFREE = 24, B_COUNT = 25 };
 constexpr int OFF_TMEM_SLOT = B_COUNT * 8, OFF_ABORT = OFF_TMEM_SLOT + 4, BAR_PAGE = 256;
 
 template <int MODE, int R, int CC>
@@ -120,7 +122,13 @@ struct Cfg {
   static constexpr int NACC = 2;
   static constexpr int TM_SC = 0, TM_ACC = 64, TM_DS = 64 + NOUT;
   static constexpr int DS_COLS = R == 128 ? 2 * CC : CC;
-  static constexpr int TM_USED = TM_DS + DS_COLS;
+  // EMIT: a POP forward walk over full 64-token chunks that still delivers the state after every block: a block end
+  // that falls inside a chunk (block sizes that are multiples of 16) gets its state from a PARTIAL increment, the
+  // first p/16 k-steps of K^T Veta in a tile of its own:  S_block = gamma^p S + gamma^-(L-p) rs (K[:p]^T Veta[:p]).
+  // Built where tensor memory has the room: the 64 x 64 tiles.
+  static constexpr bool EMIT = MODE == MODE_FWD && R == 64 && CC == 64;
+  static constexpr int TM_DSP = TM_DS + DS_COLS;
+  static constexpr int TM_USED = TM_DSP + (EMIT ? CC : 0);
   static constexpr int TM_COLS = TM_USED <= 256 ? 256 : 512;
   static_assert(TM_USED <= 512, "tensor memory budget");
   static_assert(ONE || TM_COLS == 256, "two CTAs per SM need at most 256 columns each");
@@ -149,7 +157,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
   const int col0 = MODE == MODE_FWD ? tile * CC : 0;    // state cols [col0, col0+CC) of dv
   const float lg = p.log2g[h];
   const float rs = rsqrtf((float)p.dk);
-  const int NC = chunk_count(p.T, p.block_size);
+  const int NC = chunk_count(p.T, p.sched_bs);
   auto bar = [&](int slot) { return sbase + G::OFF_BAR + slot * 8; };
   auto stage_of = [&](int n) { return n % G::STAGES; };
   auto stage_ph = [&](int n) { return (uint32_t)((n / G::STAGES) & 1); };
@@ -166,6 +174,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
     }
     for (int j = 0; j < 2; ++j) { mbar_init(bar(B_DSFULL + j), 1); mbar_init(bar(B_DSFREE + j), G::N_STATE); }
     mbar_init(bar(B_SBRDY), G::N_STATE); mbar_init(bar(B_SBFREE), 1);
+    mbar_init(bar(B_DSPFULL), 1); mbar_init(bar(B_DSPFREE), G::N_STATE);
     fence_mbar_init();
     *abort_flag = 0;
     prefetch_tmap(&p.map_x); prefetch_tmap(&p.map_k); prefetch_tmap(&p.map_v); prefetch_tmap(&p.map_out);
@@ -176,8 +185,16 @@ scan_kernel(const __grid_constant__ ScanParams p) {
   tc_fence_after();
   const uint32_t tm = *tmem_slot;
 
+  // EMIT walks (forward, full chunks): tokens from the start of chunk n to the block end that falls strictly inside
+  // it, or 0 when there is none (block sizes above 64 are the only ones walked this way: at most one per chunk)
+  const bool emit = G::EMIT && !REV && p.sched_bs == 0 && p.block_size > 0 && p.block_states != nullptr;
+  auto mid_end = [&](int n) {
+    const int a = n * C, L = min(C, p.T - a);
+    const int e = (a / p.block_size + 1) * p.block_size;
+    return (e < a + L && e / p.block_size - 1 < p.n_blocks) ? e - a : 0;
+  };
   Chunk first{REV ? p.T : 0, 0};
-  advance<REV>(first, p.T, p.block_size);
+  advance<REV>(first, p.T, p.sched_bs);
 
   // =============================================================================================
   if (warp == 0) {                                   // ---------------- TMA producer
@@ -198,7 +215,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
 #pragma unroll
         for (int cb = 0; cb < CC / 64; ++cb) tma_load_4d(st + G::X_BYTES + G::K_BYTES + cb * 8192, &p.map_v, bar(B_FULL + s), col0 + cb * 64, ck.a, h, b);
         ++issued;
-        advance<REV>(ck, p.T, p.block_size);
+        advance<REV>(ck, p.T, p.sched_bs);
       }
       if (*abort_flag) {   // let the copies in flight land before the CTA's shared memory is released
         for (int i = max(0, issued - G::STAGES); i < issued; ++i) {
@@ -235,10 +252,11 @@ scan_kernel(const __grid_constant__ ScanParams p) {
       // Next chunk to issue for each of the four products, and the next stage to hand back to the producer.
       // Each product of chunk n is issued when its inputs are there; the tensor pipe runs them in issue order.
       int n_sc = 0, n_ds = 0, n_qs = 0, n_pv = 0, n_rel = 0;
+      int n_dsp = emit ? 0 : 0x7fffffff, m_dsp = 0;   // chunks whose partial increment is settled; partials issued
       // a stage goes back to the producer as soon as all four products of its chunk have been issued (issuing
       // blocks while the tensor pipe is busy, so this is checked after every group, not once per round)
       auto release = [&]() {
-        while (n_rel < n_pv && n_rel < n_ds && n_rel < n_sc) {
+        while (n_rel < n_pv && n_rel < n_ds && n_rel < n_sc && n_rel < n_dsp) {
           if (leader) { umma_commit(bar(B_EMPTY + stage_of(n_rel))); FPB_TRACE(5, n_rel); }
           ++n_rel;
         }
@@ -286,6 +304,21 @@ scan_kernel(const __grid_constant__ ScanParams p) {
           }
           ++n_ds; progress = true;
           release();
+        }
+        // EMIT: partial increment of the chunk whose full increment has just been issued (same operands, first k-steps)
+        if (G::EMIT && n_dsp < n_ds) {
+          const int pmid = mid_end(n_dsp);
+          if (pmid == 0) { ++n_dsp; progress = true; release(); }
+          else if (m_dsp == 0 || ready(B_DSPFREE, (m_dsp - 1) & 1)) {
+            const uint64_t so = (uint64_t)(stage_of(n_dsp) * STAGE16);
+            tc_fence_after();
+            if (leader) {
+              for (int ks = 0; ks < pmid / 16; ++ks) umma_bf16(tm + G::TM_DSP, d_km + so + mstep(ks), d_vm + so + mstep(ks), ID_DS, ks > 0);
+              umma_commit(bar(B_DSPFULL));
+            }
+            ++m_dsp; ++n_dsp; progress = true;
+            release();
+          }
         }
         // state term: ACC = X Sb (FWD) | X Sb^T (DQ)
         if (n_qs < NC && data_ready(n_qs) && (n_qs < G::NACC || ready(B_ACCFREE + n_qs % G::NACC, ((n_qs / G::NACC) & 1) ^ 1)) &&
@@ -464,12 +497,12 @@ scan_kernel(const __grid_constant__ ScanParams p) {
         if (n_p < NC && n_p < n_acc + G::NP && mbar_test_wait(bar(B_SCFULL + n_p % G::NSC), (n_p / G::NSC) & 1)) {
           if (t == 0) FPB_TRACE(6, n_p);
           make_p(n_p, ck_p.L);
-          ++n_p; advance<REV>(ck_p, p.T, p.block_size);
+          ++n_p; advance<REV>(ck_p, p.T, p.sched_bs);
           patience.progress();
         } else if (n_e < n_acc) {
           if (G::DIRECT_OUT) epilogue_direct(n_e, ck_e);
           else epilogue(n_e, ck_e);
-          ++n_e; advance<REV>(ck_e, p.T, p.block_size);
+          ++n_e; advance<REV>(ck_e, p.T, p.sched_bs);
           patience.progress();
         } else if (patience.exhausted(abort_flag)) {
           FPB_GIVE_UP(0x300 | (n_e & 0xff));
@@ -630,8 +663,8 @@ scan_kernel(const __grid_constant__ ScanParams p) {
       //   U(n)  S <- gamma^L S + dS(n)                              (needs the increment of chunk n)
       //   Sb(n) publish the bf16 copy of the state at the start of chunk n; it must happen between U(n-1) and U(n),
       //         and after the state-term product of chunk n-1 has finished reading the previous copy
-      int n_v = 0, n_u = 0;
-      bool publish_due = true;
+      int n_v = 0, n_u = 0, m_part = 0;
+      bool publish_due = true, partial_due = emit && mid_end(0) > 0;   // partial_due: chunk n_u has a block end inside
       Chunk ck_v = first, ck_u = first;
       inject(first.a + first.L);
       Patience patience{0, 0};
@@ -640,7 +673,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
         if (n_v < NC && mbar_test_wait(bar(B_FULL + stage_of(n_v)), stage_ph(n_v))) {
           scale_v(n_v, ck_v.L);
           if (t == 0) FPB_TRACE(11, n_v);
-          ++n_v; advance<REV>(ck_v, p.T, p.block_size);
+          ++n_v; advance<REV>(ck_v, p.T, p.sched_bs);
           progress = true;
         }
         if (publish_due) {
@@ -648,6 +681,26 @@ scan_kernel(const __grid_constant__ ScanParams p) {
             publish_sb();
             if (t == 0) FPB_TRACE(13, n_u);
             publish_due = false; progress = true;
+          }
+        } else if (G::EMIT && partial_due) {
+          if (mbar_test_wait(bar(B_DSPFULL), m_part & 1)) {
+            tc_fence_after();
+            const int pmid = mid_end(n_u);
+            const float gp = exp2f((float)pmid * lg), up = exp2f(-(float)(ck_u.L - pmid) * lg) * rs;
+            bf16* dst = p.block_states + (((int64_t)b * p.n_blocks + ((ck_u.a + pmid) / p.block_size - 1)) * p.H + h) * state_elems;
+#pragma unroll
+            for (int i0 = 0; i0 < G::NS; i0 += 16) {
+              uint32_t r[16];
+              tmem_ld_16x256b_x4(tm + lane_base + G::TM_DSP + wcol0 + i0 * 2, r);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 16; i += 2)
+                *reinterpret_cast<uint32_t*>(dst + (int64_t)(row0 + row_of(i0 + i)) * p.dv + col0 + col_of(i0 + i)) =
+                    pack_bf16(fmaf(gp, S[i0 + i], up * __uint_as_float(r[i])), fmaf(gp, S[i0 + i + 1], up * __uint_as_float(r[i + 1])));
+            }
+            tc_fence_before();
+            mbar_arrive(bar(B_DSPFREE));
+            ++m_part; partial_due = false; progress = true;
           }
         } else if (mbar_test_wait(bar(B_DSFULL + (n_u & 1)), (n_u >> 1) & 1)) {
           if (t == 0) FPB_TRACE(12, n_u);
@@ -670,7 +723,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
             store_global(p.block_states + (((int64_t)b * p.n_blocks + (end / p.block_size - 1)) * p.H + h) * state_elems);
           ++n_u;
           if (n_u < NC) {
-            advance<REV>(ck_u, p.T, p.block_size);
+            advance<REV>(ck_u, p.T, p.sched_bs);
             if (!REV && p.sfx_G > 1 && ck_u.a % p.block_size == 0) {
               // grouped suffixes: the next chunk opens the next suffix, which starts from its own state
               const bf16* src = sfx_start(sfx_m0 + ck_u.a / p.block_size);
@@ -682,12 +735,14 @@ scan_kernel(const __grid_constant__ ScanParams p) {
             }
             inject(ck_u.a + ck_u.L);
             publish_due = true;
+            partial_due = emit && mid_end(n_u) > 0;
           }
           progress = true;
         }
         if (progress) patience.progress();
         else if (patience.exhausted(abort_flag)) { FPB_GIVE_UP(0x400 | (n_u & 0xff)); break; }
         else if (publish_due) mbar_try_wait_hint(bar(B_SBFREE), (n_u - 1) & 1, 200);   // idle: sleep on the likely next
+        else if (G::EMIT && partial_due) mbar_try_wait_hint(bar(B_DSPFULL), m_part & 1, 200);
         else mbar_try_wait_hint(bar(B_DSFULL + (n_u & 1)), (n_u >> 1) & 1, 200);
       }
     }
@@ -722,6 +777,7 @@ int launch_scan(const ScanParams& p, bool rev, dim3 grid, cudaStream_t stream) {
 int g_tile_pref = 1;            // 1: 128x128 state tiles where they apply; 0: 64-wide tiles (two CTAs per SM)
 int g_sfx_group = 16;           // most suffixes one CTA walks back to back (1: one CTA per suffix)
 int g_sfx_min_ctas = 3 * 296;   // ... as long as that many CTAs remain (three waves of two CTAs per SM)
+int g_pop_emit = 1;             // 1: POP forward walks over full chunks where block states can come from partial increments
 int g_fused_bwd = 1;            // 1: dK, dV, dS_0 in one fused reverse walk where it applies; 0: two separate walks
 long long* g_trace = nullptr;   // set by fpb_debug_trace
 
@@ -782,6 +838,11 @@ int launch_pass(const PassArgs& a, cudaStream_t stream) {
   p.block_grads = (const bf16*)a.block_grads;
   p.sfx_blocks = (bf16*)a.sfx.blocks; p.sfx_M = a.sfx.M; p.sfx_N = a.sfx.N; p.sfx_G = G;
   p.T = Tk; p.H = H; p.dk = dk; p.dv = dv; p.block_size = block_size; p.n_blocks = a.n_blocks;
+  // POP forward at 64 x 64: full chunks, block states from partial increments (block sizes above 64 that are multiples
+  // of 16 but not of 64 - for those the block-aligned schedule already is the full-chunk one)
+  const bool emit = g_pop_emit && a.mode == MODE_FWD && !a.rev && a.block_states && dk == 64 && dv == 64 &&
+                    block_size > 64 && block_size % 16 == 0 && block_size % 64 != 0 && G == 1;
+  p.sched_bs = emit ? 0 : block_size;
   p.status = device_status_ptr();
   p.trace = g_trace;
   if (!p.status) return FPB_ERR_LAUNCH;
@@ -820,6 +881,8 @@ extern "C" void fpb_debug_tile_pref(int wide) { g_tile_pref = wide; }
 // Diagnostics hook: upper limit of the suffixes one CTA walks back to back (1 = one CTA per suffix) and the number of
 // CTAs that must remain.
 extern "C" void fpb_debug_suffix_group(int g, int min_ctas) { g_sfx_group = g < 1 ? 1 : g; if (min_ctas > 0) g_sfx_min_ctas = min_ctas; }
+// Diagnostics hook: 0 makes every POP forward walk cut its chunks at block ends.
+extern "C" void fpb_debug_pop_emit(int on) { g_pop_emit = on; }
 // Diagnostics hook: 0 runs the dV and dK walks as two launches instead of the fused reverse kernel.
 extern "C" void fpb_debug_fused_bwd(int on) { g_fused_bwd = on; }
 

@@ -31,6 +31,7 @@ def _state_embedded(B, H, dk, dv):
 
 
 @pytest.mark.parametrize("T,d,block,simt", [(70, 64, 0, False), (150, 128, 0, False), (150, 64, 40, False), (28, 64, 15, False),
+                                            (300, 64, 80, False), (287, 64, 144, False),
                                             (70, 64, 0, True), (150, 64, 40, True)])
 def test_outputs_stay_inside_their_views(T, d, block, simt):
     from flash_pop_b200 import _lib

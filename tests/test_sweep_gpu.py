@@ -50,8 +50,10 @@ def test_block_sizes_around_every_alignment_case():
     import flash_pop_b200 as fp
     from flash_pop_b200 import _lib
     d, T = 64, 150
+    # 80, 96, 112, 144: multiples of 16 above 64 - the forward walk keeps full chunks and emits those block states from
+    # partial state increments
     decays = orc.head_decays(2, (5, 12))
-    for block in (1, 2, 3, 7, 15, 16, 17, 31, 32, 33, 50, 63, 64, 65, 75, 100, 127, 128, 129, 149, 150, 151):
+    for block in (1, 2, 3, 7, 15, 16, 17, 31, 32, 33, 50, 63, 64, 65, 75, 80, 96, 100, 112, 127, 128, 129, 144, 149, 150, 151):
         q, k, v, s, dO = _inputs(T, d, block)
         g = torch.Generator().manual_seed(1000 + block)
         dBS = torch.randn(1, T // block, 2, d, d, generator=g).to(BF)

@@ -227,3 +227,34 @@ def test_grouped_suffix_walks_equal_one_cta_per_suffix(M, N, P, d):
     o_ref = orc.pop_suffix_retention(qd, kd, vd, s0.double().cpu(), blocks.double().cpu(), decays)
     assert orc.rel_rms(results[1][0].float().cpu(), o_ref) < 5e-3
     _lib.device_status()
+
+
+@pytest.mark.parametrize("T,block", [(5120, 80), (287, 144), (400, 96), (1000, 112)])
+def test_block_states_from_partial_increments_match_the_block_aligned_walk(T, block):
+    """POP forward at d = 64: the walk over full chunks with block states taken from partial state increments against
+    the walk that cuts its chunks at block ends (same kernel, hook), and against the oracle."""
+    import ctypes
+    import flash_pop_b200 as fp
+    from flash_pop_b200 import _lib
+    hook = _lib.lib().fpb_debug_pop_emit
+    hook.argtypes = [ctypes.c_int]
+    B, H, d = 2, 4, 64
+    decays = orc.head_decays(H, (5, 12))
+    q, k, v, s0, _ = make_inputs(T + block, B, T, H, d, d, BF)
+    outs = []
+    try:
+        for on in (0, 1):
+            hook(on)
+            with torch.no_grad():
+                o, bs = fp.flash_pop_retention(q.cuda(), k.cuda(), v.cuda(), s0.cuda(), decays, block)
+            assert _lib.last_path() == _lib.PATH_TCGEN05
+            outs.append((o.cpu(), bs.cpu()))
+    finally:
+        hook(1)
+    o_ref, bs_ref = orc.pop_retention(q.double(), k.double(), v.double(), s0.double(), decays, block)
+    for o, bs in outs:
+        check("o", o, o_ref, BF)
+        check("block states", bs, bs_ref, BF)
+    # the two schedules differ in rounding only
+    assert orc.rel_rms(outs[1][1].float(), outs[0][1].double()) < 5e-3
+    _lib.device_status()
