@@ -67,3 +67,32 @@ def test_operators_refuse_cpu_tensors():
         fp.fused_chunk_retention(q, q, q, None, (0.9, 0.9))
     with pytest.raises(RuntimeError, match="no CPU path"):
         fp.flash_pop_retention(q, q, q, None, (0.9, 0.9), 4)
+
+
+def test_layer_pass_and_step_entry_points_check_arguments_without_a_device(handle):
+    seq = _lib._Seq(None, 0, 0, 0)
+    st = _lib._State(None, 0, 0)
+    # rotation: d must be a multiple of 8, dtypes known, phasors given
+    assert handle.fpb_rotary(1, 4, 2, 12, 0, 0, 0, None, 0, seq, seq, seq, seq, None) == 2
+    assert handle.fpb_rotary(1, 4, 2, 16, 5, 0, 0, None, 0, seq, seq, seq, seq, None) == 3
+    assert handle.fpb_rotary(1, 4, 2, 16, 0, 0, 0, None, 0, seq, seq, seq, seq, None) == 1
+    # GroupNorm-gate: even width up to 256
+    assert handle.fpb_groupnorm_gate_fwd(1, 4, 2, 7, 0, 1e-6, 1, seq, seq, seq, None) == 2
+    assert handle.fpb_groupnorm_gate_fwd(1, 4, 2, 512, 0, 1e-6, 1, seq, seq, seq, None) == 2
+    assert handle.fpb_groupnorm_gate_bwd(1, 4, 2, 64, 9, 1e-6, 1, seq, seq, seq, seq, seq, None) == 3
+    assert handle.fpb_groupnorm_gate_fwd(1, 4, 2, 64, 0, 1e-6, 1, seq, seq, seq, None) == 1
+    # LayerNorm: width a multiple of 8 (bf16) and at most 1024
+    assert handle.fpb_layernorm_fwd(8, 12, 0, 1e-6, None, 12, None, None, None, 12, None) == 2
+    assert handle.fpb_layernorm_fwd(8, 2048, 0, 1e-6, None, 2048, None, None, None, 2048, None) == 2
+    assert handle.fpb_layernorm_fwd(8, 64, 0, 1e-6, None, 64, None, None, None, 64, None) == 1
+    assert handle.fpb_layernorm_bwd(8, 64, 3, 1e-6, None, 64, None, None, 64, None, None, None, None) == 3
+    # decoding step: one token per row
+    assert handle.fpb_retention_step(_dims(T=2), 0, seq, seq, seq, st, seq, st, None) == 2
+    assert handle.fpb_retention_step(_dims(T=1), 4, seq, seq, seq, st, seq, st, None) == 3
+    assert handle.fpb_retention_step(_dims(T=1), 0, seq, seq, seq, st, seq, st, None) == 1
+
+
+def test_cpu_list_parser_of_the_numa_helper():
+    from flash_pop_b200.host_io import _parse_cpulist
+    assert _parse_cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    assert _parse_cpulist("") == set()
