@@ -291,6 +291,7 @@ def run_stack(args):
     import contextlib
     import torch.distributed as dist
     from flash_pop_b200 import _lib
+    from flash_pop_b200.layer_ops import cross_entropy
     from flash_pop_b200.stack_lm import RetNetLM
     rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
@@ -315,7 +316,7 @@ def run_stack(args):
 
     def loss_of(tok):                                          # through `net` so that DDP's gradient hooks are armed
         logits, _ = net(tok[:, :-1])
-        return torch.nn.functional.cross_entropy(logits.float().flatten(0, 1), tok[:, 1:].flatten())
+        return cross_entropy(logits.flatten(0, 1), tok[:, 1:].flatten())   # fp32 arithmetic on the bf16 logits, one kernel each way
 
     def step():
         tokens.copy_(host_tokens, non_blocking=True)           # the step's input comes from the host

@@ -449,6 +449,41 @@ int fpb_layernorm_bwd(int64_t rows, int32_t d, int32_t dtype, float eps, const v
   return finish_launches(1, -1);
 }
 
+namespace {
+int check_xent(int64_t rows, int32_t V, int32_t dtype, const void* logits, int64_t row_stride) {
+  if (rows < 0 || V <= 0) return FPB_ERR_BAD_SHAPE;
+  if (rows >= (1ll << 31)) return FPB_ERR_TOO_LARGE;
+  if (!dtype_ok(dtype)) return FPB_ERR_BAD_DTYPE;
+  if (rows == 0) return FPB_OK;
+  if (!logits) return FPB_ERR_NULL_POINTER;
+  const int vec = dtype == FPB_F32 ? 4 : 8;
+  if ((rows > 1 && row_stride < V) || row_stride % vec || (uintptr_t)logits % 16) return FPB_ERR_BAD_STRIDE;
+  return FPB_OK;
+}
+}  // namespace
+
+int fpb_cross_entropy_fwd(int64_t rows, int32_t V, int32_t dtype, const void* logits, int64_t row_stride, const int64_t* targets,
+                          float* loss, float* lse, fpb_stream_t stream) {
+  FPB_TRY(check_xent(rows, V, dtype, logits, row_stride));
+  if (rows > 0 && (!targets || !loss || !lse)) return FPB_ERR_NULL_POINTER;
+  FPB_TRY(check_device());
+  if (rows == 0) return FPB_OK;
+  launch_xent_fwd(dtype, rows, V, logits, row_stride, targets, loss, lse, (cudaStream_t)stream);
+  return finish_launches(1, -1);
+}
+
+int fpb_cross_entropy_bwd(int64_t rows, int32_t V, int32_t dtype, const void* logits, int64_t row_stride, const int64_t* targets,
+                          const float* lse, const float* scale, float row_weight, void* d_logits, int64_t d_stride,
+                          fpb_stream_t stream) {
+  FPB_TRY(check_xent(rows, V, dtype, logits, row_stride));
+  FPB_TRY(check_xent(rows, V, dtype, d_logits, d_stride));
+  if (rows > 0 && (!targets || !lse || !scale)) return FPB_ERR_NULL_POINTER;
+  FPB_TRY(check_device());
+  if (rows == 0) return FPB_OK;
+  launch_xent_bwd(dtype, rows, V, logits, row_stride, targets, lse, scale, row_weight, d_logits, d_stride, (cudaStream_t)stream);
+  return finish_launches(1, -1);
+}
+
 const char* fpb_strerror(int status) {
   switch (status) {
     case FPB_OK: return "ok";

@@ -65,6 +65,12 @@ int launch_layernorm(int dtype, bool backward, int64_t rows, int d, float eps, c
                      const float* w, const float* b, void* y, int64_t y_stride, const void* dy, void* dx, float* dw,
                      float* db, cudaStream_t stream);
 
+// Softmax cross entropy of (rows x V) logits against int64 targets (loss_fused.cu).
+int launch_xent_fwd(int dtype, int64_t rows, int V, const void* logits, int64_t row_stride, const int64_t* targets, float* loss,
+                    float* lse, cudaStream_t stream);
+int launch_xent_bwd(int dtype, int64_t rows, int V, const void* logits, int64_t row_stride, const int64_t* targets, const float* lse,
+                    const float* scale, float row_weight, void* d_logits, int64_t d_stride, cudaStream_t stream);
+
 // Device status word shared by all kernels: 0 = fine; otherwise (role << 8 | barrier id) of the
 // first bounded wait that gave up.
 int32_t* device_status_ptr();

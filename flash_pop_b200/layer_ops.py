@@ -169,3 +169,49 @@ def norm_in_fp32(module: torch.nn.LayerNorm, x: Tensor) -> Tensor:
     if len(module.normalized_shape) == 1 and layer_norm_supported(x, module.normalized_shape[0]):
         return layer_norm(x, module.weight, module.bias, module.eps)
     return module(x.float()).to(dtype=x.dtype)
+
+
+# ---- softmax cross entropy for the language-model head --------------------------------------------------------------
+def cross_entropy_supported(logits: Tensor, targets: Tensor) -> bool:
+    vec = 16 // max(logits.element_size(), 1)
+    return (logits.is_cuda and logits.dim() == 2 and logits.dtype in _OK_DTYPES and targets.dtype == torch.int64 and
+            targets.shape == logits.shape[:1] and logits.stride(1) == 1 and logits.data_ptr() % 16 == 0 and
+            (logits.size(0) <= 1 or logits.stride(0) % vec == 0))
+
+
+class FusedCrossEntropy(torch.autograd.Function):
+    """Mean softmax cross entropy of (rows, V) logits; fp32 arithmetic, one read of the logits forward, one read and
+    one write backward, gradient in the logits' own dtype."""
+
+    @staticmethod
+    def forward(ctx, logits, targets):
+        rows, V = logits.shape
+        targets = targets.contiguous()
+        loss = torch.empty(rows, device=logits.device, dtype=torch.float32)
+        lse = torch.empty(rows, device=logits.device, dtype=torch.float32)
+        with torch.cuda.device(logits.device):
+            _lib.check(_lib.lib().fpb_cross_entropy_fwd(rows, V, _lib.dtype_code(logits), _ptr(logits), logits.stride(0) if rows > 1 else V,
+                                                        _ptr(targets), _ptr(loss), _ptr(lse), _lib.stream_ptr(logits.device)))
+        ctx.save_for_backward(logits, targets, lse)
+        return loss.mean()
+
+    @staticmethod
+    def backward(ctx, g):
+        logits, targets, lse = ctx.saved_tensors
+        rows, V = logits.shape
+        vec = 16 // logits.element_size()
+        pitch = (V + vec - 1) // vec * vec                       # rows of the gradient start on 16-byte boundaries too
+        d_logits = torch.empty((rows, pitch), device=logits.device, dtype=logits.dtype)[:, :V]
+        scale = g.detach().to(torch.float32).reshape(1).contiguous()
+        with torch.cuda.device(logits.device):
+            _lib.check(_lib.lib().fpb_cross_entropy_bwd(rows, V, _lib.dtype_code(logits), _ptr(logits), logits.stride(0) if rows > 1 else V,
+                                                        _ptr(targets), _ptr(lse), _ptr(scale), 1.0 / max(rows, 1), _ptr(d_logits), pitch,
+                                                        _lib.stream_ptr(logits.device)))
+        return d_logits, None
+
+
+def cross_entropy(logits: Tensor, targets: Tensor) -> Tensor:
+    """Mean cross entropy of (rows, V) logits against int64 targets, as ``F.cross_entropy(logits.float(), targets)``."""
+    if cross_entropy_supported(logits, targets):
+        return FusedCrossEntropy.apply(logits, targets)
+    return torch.nn.functional.cross_entropy(logits.float(), targets)

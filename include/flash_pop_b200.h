@@ -188,6 +188,22 @@ int fpb_layernorm_bwd(int64_t rows, int32_t d, int32_t dtype, float eps, const v
                       const float* weight, const void* d_y, int64_t dy_stride, void* d_x, float* d_weight,
                       float* d_bias, fpb_stream_t stream);
 
+/*
+ * Softmax cross entropy of `rows` rows of V logits (bf16 or fp32, `row_stride` elements apart, 16-byte aligned rows)
+ * against int64 targets, fp32 arithmetic, for the language-model head of the full-stack training workload (the
+ * reference has no loss of its own; this replaces the cast-to-fp32 + log_softmax + nll_loss passes of PyTorch).
+ * The forward writes per row loss[r] = logsumexp(x_r) - x_r[target] and lse[r] (kept for the backward); a target
+ * outside [0, V) gives loss 0 and a zero gradient row.  The backward writes
+ *   d_logits[r, j] = (exp(x[r, j] - lse[r]) - [j == target_r]) * scale[0] * row_weight
+ * in the logits' type (`scale`: device pointer to the upstream gradient of the reduced loss; row_weight = 1 / rows
+ * for a mean).  d_logits may be the logits buffer itself.
+ */
+int fpb_cross_entropy_fwd(int64_t rows, int32_t V, int32_t dtype, const void* logits, int64_t row_stride,
+                          const int64_t* targets, float* loss, float* lse, fpb_stream_t stream);
+int fpb_cross_entropy_bwd(int64_t rows, int32_t V, int32_t dtype, const void* logits, int64_t row_stride,
+                          const int64_t* targets, const float* lse, const float* scale, float row_weight,
+                          void* d_logits, int64_t d_stride, fpb_stream_t stream);
+
 /* Text for a status code. */
 const char* fpb_strerror(int status);
 /* Library version, major*10000 + minor*100 + patch. */

@@ -146,3 +146,25 @@ def test_layer_norm_module_helper_matches_cast_norm_cast():
     big = torch.randn(2, 2048, device="cuda", dtype=BF)                          # wider than the kernel takes: eager path
     m2 = torch.nn.LayerNorm(2048, device="cuda", dtype=F32)
     assert torch.equal(norm_in_fp32(m2, big), m2(big.float()).to(BF))
+
+
+@pytest.mark.parametrize("dtype,rows,V", [(BF, 300, 32000), (BF, 17, 1000), (F32, 64, 517), (BF, 5, 8)])
+def test_cross_entropy_forward_and_backward(dtype, rows, V):
+    from flash_pop_b200.layer_ops import FusedCrossEntropy, cross_entropy_supported
+    g = torch.Generator().manual_seed(V)
+    pad = (-V) % 8                                     # rows 16-byte aligned even when V is not a multiple of 8
+    buf = (torch.randn(rows, V + pad, generator=g) * 3).to(dtype).cuda()
+    logits0 = buf[:, :V]
+    targets = torch.randint(0, V, (rows,), generator=g).cuda()
+    targets[0] = -100                                   # ignored row
+    assert cross_entropy_supported(logits0, targets)
+    x = logits0.detach().requires_grad_(True)
+    loss = FusedCrossEntropy.apply(x, targets)
+    (loss * 1.7).backward()
+    xd = logits0.double().detach().requires_grad_(True)
+    ref = F.cross_entropy(xd, targets, ignore_index=-100, reduction="sum") / rows      # mean over ALL rows, ignored ones count as 0
+    (ref * 1.7).backward()
+    assert abs(loss.item() - ref.item()) < (2e-5 if dtype == F32 else 2e-4) * max(1.0, abs(ref.item()))
+    rr = ((x.grad.double() - xd.grad).square().mean().sqrt() / xd.grad.square().mean().sqrt()).item()
+    assert rr < (5e-3 if dtype == BF else 2e-5), rr
+    assert x.grad.dtype == dtype and float(x.grad[0].abs().max()) == 0.0
