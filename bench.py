@@ -537,6 +537,15 @@ def main():
                   "hbm_gbs_algorithmic": s_bytes / (s_ms * 1e-3) / 1e9,
                   "note": "start states read in place from block_states; state gradients written back to d_block_states"}
 
+    # the copy bandwidth of THIS GPU right now (read + write of a 1 GiB device-to-device copy): boxes of the pool differ,
+    # and the kernel closest to the HBM roof follows it
+    src_buf = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
+    dst_buf = torch.empty_like(src_buf)
+    for _ in range(3):
+        dst_buf.copy_(src_buf)
+    copy_gbs = 2 * src_buf.numel() / (event_time_ms(lambda: dst_buf.copy_(src_buf), 10) * 1e-3) / 1e9
+    del src_buf, dst_buf
+
     t_ms = torch.tensor([ms, ms_fwd, ms_bwd, e2e_ms or 0.0, ms_dq, ms_rev], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
@@ -576,7 +585,8 @@ def main():
                        "flop_count": "algorithmic, causal half of intra-chunk tiles (C=64)"},
             "roofline": {"bound": "hbm", "kernel": "bwd_fused_kernel (reverse walk: dK, dV, dS0; one launch per step, largest share)",
                          "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                         "peak_source": peak_src, "traffic": rev_traffic, "algorithmic_bytes": rev_bytes, "ms_per_launch": ms_rev},
+                         "peak_source": peak_src, "traffic": rev_traffic, "algorithmic_bytes": rev_bytes, "ms_per_launch": ms_rev,
+                         "copy_gbs_this_gpu": copy_gbs, "frac_of_copy_here": achieved / copy_gbs},
             "roofline_fwd": {"bound": "hbm", "kernel": "scan_kernel<MODE_FWD, forward>", "achieved": bf * units / (ms_fwd * 1e-3) / 1e9,
                              "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": bf * units / (ms_fwd * 1e-3) / 1e9 / peaks["hbm_gbs"],
                              "algorithmic_bytes": bf * units, "ms_per_launch": ms_fwd},

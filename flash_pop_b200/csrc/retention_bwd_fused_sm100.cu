@@ -396,14 +396,18 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
     // suffix calls: the batch index is (row, group of sfx_G consecutive suffixes); the walk goes through the group's
     // suffixes from the last to the first, and what it carries when it leaves suffix m is the gradient of the state
     // that suffix started from
-    const int groups = p.sfx_M > 0 ? p.sfx_M / p.sfx_G : 1;
-    const int sfx_row = b / groups, sfx_m0 = (b % groups) * p.sfx_G;
+    // (Grouping is compiled into the 64 x 64 kernel only - the shape suffixes come in; in the larger tiles its few
+    // extra live registers spill the state, which costs the long-sequence workloads far more than grouping gains.)
+    constexpr bool GROUPED = DK == 64 && DV == 64;
+    const int sfx_g = GROUPED ? p.sfx_G : 1;
+    const int groups = p.sfx_M > 0 ? p.sfx_M / sfx_g : 1;
     auto sfx_grad = [&](int m) -> bf16* {
+      const int sfx_row = b / groups;
       if (m == 0) return p.g_end ? p.g_end + sfx_row * p.ge_sb + h * p.ge_sh : nullptr;
       return p.sfx_blocks ? p.sfx_blocks + (((int64_t)sfx_row * p.sfx_N + (m - 1)) * p.H + h) * state_elems : nullptr;
     };
     if (p.sfx_M > 0) {
-      if (p.sfx_G == 1) x_end = sfx_grad(sfx_m0);      // grouped walks store at every suffix start, inside the loop
+      if (sfx_g == 1) x_end = sfx_grad(b % groups);    // grouped walks store at every suffix start, inside the loop
     } else {
       if (p.g_start) x_start = p.g_start + b * p.gs_sb + h * p.gs_sh;
       if (p.g_end) x_end = p.g_end + b * p.ge_sb + h * p.ge_sh;
@@ -541,8 +545,8 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
           tc_fence_before();
           mbar_arrive(bar(B_DSFREE + (n_u & 1)));
           ++n_u;
-          if (p.sfx_G > 1 && ck_u.a % p.block_size == 0) {   // that was the first chunk of a suffix
-            bf16* dst = sfx_grad(sfx_m0 + ck_u.a / p.block_size);
+          if (GROUPED && sfx_g > 1 && ck_u.a % p.block_size == 0) {   // that was the first chunk of a suffix
+            bf16* dst = sfx_grad((b % groups) * sfx_g + ck_u.a / p.block_size);
             if (dst) store_global(dst);
 #pragma unroll
             for (int i = 0; i < G::NS; ++i) S[i] = 0.f;      // the suffix before it ends in a state nobody reads
@@ -607,7 +611,7 @@ int launch_bwd_fused(const UmmaBwdArgs& a, cudaStream_t stream) {
   if (a.sfx_grad.M > 1 && a.block_size == 0) {
     bool contiguous = true;
     for (const SeqView* s : {&q, &k, &v, &dO, &dK, &dV}) contiguous = contiguous && s->sb == (int64_t)T * s->st;
-    if (contiguous) G = choose_suffix_group(a.sfx_grad.M, (long long)(B / a.sfx_grad.M) * H);
+    if (contiguous && a.dk == 64 && a.dv == 64) G = choose_suffix_group(a.sfx_grad.M, (long long)(B / a.sfx_grad.M) * H);
     if (G > 1) {
       B /= G; block_size = T; T *= G;
       for (SeqView* s : {&q, &k, &v, &dO, &dK, &dV}) s->sb *= G;
