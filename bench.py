@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the chunked-retention hot path (forward + backward) on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload ns|c3|c4]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload ns|c3|c4|c5|decode|layer]
 
 Workload "ns" (default) is the configuration the headline metric is quoted on: chunked retention
 forward+backward, bf16, B=8, H=16, T=8192, dk=dv=128 per GPU, decays 1-2^-linspace(5,12,H), seeded
@@ -11,8 +11,11 @@ rows (weak scaling, no collective on the data path); the time is the max over ra
 
 Prints ONE JSON line (rank 0).  `value` is algorithmic TFLOP/s with inputs resident in HBM; `e2e` is
 the same metric with host buffers (pinned) copied in and every result copied back inside the timed
-region.  `--impl reference` times the reference's PyTorch CPU algorithm (the CPU port in oracle/) on
-the host cores over a bounded sample of the same workload.
+region (`e2e.copy_only_ms`: the same copies without the kernels).  The default line carries two sub-records:
+`strong` - the SAME B=8 problem split over the ranks with flash_pop_b200.parallel.partition - and `c5` - a few steps
+of the full 12-layer RetNet training step under DistributedDataParallel (tokens/s).  `--impl reference` times the
+reference's PyTorch CPU algorithm (the CPU port in oracle/) on the host cores over a bounded sample of the same
+workload.
 """
 from __future__ import annotations
 
@@ -38,7 +41,7 @@ WORKLOADS = {
     # a quarter of "ns" (still 4 x 67 MB of inputs, larger than L2): the case profiler captures run on
     "small": dict(B=2, H=16, T=8192, dk=128, dv=128, block=0),
 }
-# BASELINE config 5: the full RetNet stack under data parallelism (global batch fixed: strong scaling)
+# the full RetNet stack under data parallelism: 12 layers, d_model 1024, global batch 64 x 4096 fixed (strong scaling)
 STACK = dict(layers=12, heads=8, head_dim=128, ffn=4096, vocab=32000, B=64, T=4096, micro_batch=32)
 CHUNK = 64
 
@@ -59,14 +62,17 @@ def decays_for(H):
     return tuple((1 - np.exp2(-np.linspace(5, 12, H))).tolist())
 
 
-def make_host_inputs(w, seed, pin):
-    g = torch.Generator().manual_seed(seed)
+def make_host_inputs(w, seed, pin, rows=None):
+    """q, k, v, dO of the workload (bf16, host).  Every (tensor, batch row) has its own seed, so a rank that owns only
+    some rows of the problem builds exactly those (`rows` = a range of batch rows; default all)."""
     B, H, T, dk, dv = w["B"], w["H"], w["T"], w["dk"], w["dv"]
+    rows = range(B) if rows is None else rows
     out = []
-    for d, sc in ((dk, dk ** -0.5), (dk, dk ** -0.5), (dv, dk ** -0.5), (dv, 1.0)):
-        t = torch.empty(B, T, H, d, dtype=torch.bfloat16)
-        for b in range(B):   # row by row keeps the fp32 temporary small
-            t[b] = (torch.randn(T, H, d, generator=g) * sc).to(torch.bfloat16)
+    for i, (d, sc) in enumerate(((dk, dk ** -0.5), (dk, dk ** -0.5), (dv, dk ** -0.5), (dv, 1.0))):
+        t = torch.empty(len(rows), T, H, d, dtype=torch.bfloat16)
+        for j, b in enumerate(rows):   # row by row keeps the fp32 temporary small
+            g = torch.Generator().manual_seed((seed * 8 + i) * 4096 + b)
+            t[j] = (torch.randn(T, H, d, generator=g) * sc).to(torch.bfloat16)
         out.append(t.pin_memory() if pin else t)
     return out   # q, k, v, dO
 
@@ -120,8 +126,9 @@ def event_time_ms(fn, steps):
 
 
 # --------------------------------------------------------------------------------------------------
-def cpu_port_tflops(w, rows, reps, threads):
-    """The reference's PyTorch algorithm (CPU port in oracle/) forward+backward on `rows` batch rows."""
+def cpu_reference_pass(w, rows, threads):
+    """One forward+backward of the reference's PyTorch CPU algorithm (its restatement in oracle/, pinned bit for bit to
+    the reference's own functions by the committed fixtures) on `rows` batch rows of the workload; returns seconds."""
     from oracle import retention_oracle as orc
     torch.set_num_threads(threads)
     H, T, dk, dv = w["H"], w["T"], w["dk"], w["dv"]
@@ -129,19 +136,34 @@ def cpu_port_tflops(w, rows, reps, threads):
     g = torch.Generator().manual_seed(2)
     q, k, v = (torch.randn(rows, T, H, d, generator=g) * dk ** -0.5 for d in (dk, dk, dv))
     dO = torch.randn(rows, T, H, dv, generator=g)
-    best = float("inf")
-    for it in range(reps + 1):
-        leaves = [t.clone().requires_grad_(True) for t in (q, k, v)]
-        t0 = time.perf_counter()
-        if w["block"]:
-            o, bs = orc.pop_retention(*leaves, None, dec, w["block"])
-        else:
-            o, _ = orc.retention_chunkwise(*leaves, None, dec, chunk_size=CHUNK)
-        (o * dO).sum().backward()
-        dt = time.perf_counter() - t0
-        best = min(best, dt) if it else best   # first pass is the warm-up
-    ff, fb = flops_per_token_head(dk, dv)
-    return (ff + fb) * rows * T * H / best / 1e12, best
+    leaves = [t.requires_grad_(True) for t in (q, k, v)]
+    t0 = time.perf_counter()
+    if w["block"]:
+        o, _ = orc.pop_retention(*leaves, None, dec, w["block"])
+    else:
+        o, _ = orc.retention_chunkwise(*leaves, None, dec, chunk_size=CHUNK)
+    (o * dO).sum().backward()
+    return time.perf_counter() - t0
+
+
+def cpu_reference_tflops(w, rows, passes, warmup, threads):
+    """Mean over `passes` timed passes after `warmup` untimed ones - the one method both CPU figures use."""
+    for _ in range(warmup):
+        cpu_reference_pass(w, rows, threads)
+    dt = sum(cpu_reference_pass(w, rows, threads) for _ in range(passes)) / passes
+    ff, fb = flops_per_token_head(w["dk"], w["dv"])
+    return (ff + fb) * rows * w["T"] * w["H"] / dt / 1e12, dt
+
+
+def cpu_sample_text(w, rows, passes):
+    return (f"{rows} of {w['B']} batch rows (H={w['H']}, T={w['T']}), fp32 torch CPU, chunk {CHUNK}, mean of {passes} "
+            f"pass(es) after a warm-up")
+
+
+def op_config(args, w):
+    """The `config` object of an operator workload: identical for both arms."""
+    return {"workload": workload_name(args, w), "l2": "inputs (1 GB+) larger than the 126 MB L2; no flush",
+            "flop_count": "algorithmic, causal half of intra-chunk tiles (C=64)"}
 
 
 def run_reference(args, w, rank):
@@ -149,22 +171,15 @@ def run_reference(args, w, rank):
         return
     threads = os.cpu_count() or 1
     rows = 1
-    times = []
-    for i in range(args.warmup + args.steps):
-        tf, dt = cpu_port_tflops(w, rows, 1, threads)
-        if i >= args.warmup:
-            times.append(dt)
-    ff, fb = flops_per_token_head(w["dk"], w["dv"])
-    dt = sum(times) / len(times)
-    tf = (ff + fb) * rows * w["T"] * w["H"] / dt / 1e12
-    sample = f"{rows} of {w['B']} batch rows per step (H={w['H']}, T={w['T']}), fp32, chunk {CHUNK}, torch CPU"
+    tf, dt = cpu_reference_tflops(w, rows, args.steps, max(args.warmup, 1), threads)
     line = {
         "impl": "reference", "metric": "chunked_retention_fwd_bwd_tflops", "value": tf, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "tokens_per_s": rows * w["T"] / dt,
-        "config": {"workload": workload_name(args, w), "l2": "inputs larger than L2"},
-        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "config": op_config(args, w),
+        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                         "sample": cpu_sample_text(w, rows, args.steps)},
         "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -284,25 +299,17 @@ def workload_name(args, w):
 
 
 # --------------------------------------------------------------------------------------------------
-def run_stack(args):
+def stack_record(args, dev, rank, world, steps, warmup, sample_clocks=True):
     """Full 12-layer RetNet training step (embedding, stack, head, cross entropy, AdamW), bf16, global batch 64 x 4096
     tokens split over the ranks (strong scaling), micro-batches with gradient accumulation, NCCL gradient all-reduce
-    through DistributedDataParallel on the last micro-batch.  Metric: tokens/s."""
+    through DistributedDataParallel on the last micro-batch.  Metric: tokens/s.  Uses the default process group when
+    world > 1; returns the record on rank 0 (None elsewhere)."""
     import contextlib
     import torch.distributed as dist
     from flash_pop_b200 import _lib
     from flash_pop_b200.layer_ops import cross_entropy
     from flash_pop_b200.stack_lm import RetNetLM
-    rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
-        if rank == 0:
-            print(json.dumps({"impl": "reference", "unavailable": "the full-stack configuration has no CPU-sized reference run; "
-                              "the reference arm covers the operator workloads"}))
-        return
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    local = dev.index
     c = STACK
     torch.manual_seed(0)
     model = RetNetLM(c["vocab"], c["layers"], c["heads"], c["head_dim"], c["ffn"], device=dev)
@@ -332,10 +339,10 @@ def run_stack(args):
         opt.step()
         return total
 
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         step()
     _lib.device_status(dev)
-    sampler = ClockSampler(local) if rank == 0 else None
+    sampler = ClockSampler(local) if (rank == 0 and sample_clocks) else None
     if sampler:
         sampler.start(); time.sleep(0.3)
     launches0 = _lib.launch_count()
@@ -345,44 +352,73 @@ def run_stack(args):
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     last = None
-    for _ in range(args.steps):
+    for _ in range(steps):
         last = step().item()                                   # device -> host read of the step's loss
     b.record()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    ms = a.elapsed_time(b) / args.steps
+    ms = a.elapsed_time(b) / steps
     t = torch.tensor([ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = t.item()
     launches = _lib.launch_count() - launches0
     clocks = sampler.stop() if sampler else None
+    flops_per_token = model.flops_per_token(c["T"])
+    del net, opt, model, tokens
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return None
+    toks = c["B"] * c["T"]
+    flops = flops_per_token * toks
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))); src = "measured"
+    except Exception:
+        peaks = {"bf16_tflops_sustained": 1400.0}; src = "fallback"
+    tf = flops / (ms * 1e-3) / 1e12
+    peak = peaks.get("bf16_tflops_sustained", 1400.0) * world
+    return {
+        "metric": "retnet_stack_train_tokens_per_s", "value": toks / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "loss": last,
+        "config": {"workload": f"RetNet stack train step: {c['layers']} layers, d_model {c['heads'] * c['head_dim']}, {c['heads']} heads, "
+                               f"FFN {c['ffn']}, vocab {c['vocab']}, global batch {c['B']} x {c['T']}, micro-batch {mb}, "
+                               f"DDP over {world} GPU(s), AdamW", "l2": "activations far larger than L2"},
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
+                     "peak_source": src + " (sustained cuBLAS bf16)", "traffic": None,
+                     "note": "whole step, cuBLAS GEMMs dominate; retention kernels are about 2 % of the FLOPs"},
+        "e2e": {"value": toks / (ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": host_tokens.numel() * 8, "d2h_bytes_per_step": 4,
+                "note": "the timed step already copies its token ids from pinned host memory and reads the loss back"},
+        "clocks": clocks, "gpu_launches": launches}
+
+
+def run_stack(args):
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "the full-stack configuration has no CPU-sized reference run; "
+                              "the reference arm covers the operator workloads"}))
+        return
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    rec = stack_record(args, dev, rank, world, args.steps, args.warmup)
     if rank == 0:
-        toks = c["B"] * c["T"]
-        flops = model.flops_per_token(c["T"]) * toks
-        try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))); src = "measured"
-        except Exception:
-            peaks = {"bf16_tflops_sustained": 1400.0}; src = "fallback"
-        tf = flops / (ms * 1e-3) / 1e12
-        peak = peaks.get("bf16_tflops_sustained", 1400.0) * world
-        print(json.dumps({
-            "metric": "retnet_stack_train_tokens_per_s", "value": toks / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "loss": last,
-            "config": {"workload": f"RetNet stack train step: {c['layers']} layers, d_model {c['heads'] * c['head_dim']}, {c['heads']} heads, "
-                                   f"FFN {c['ffn']}, vocab {c['vocab']}, global batch {c['B']} x {c['T']}, micro-batch {mb}, "
-                                   f"DDP over {world} GPU(s), AdamW", "l2": "activations far larger than L2"},
-            "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
-                         "peak_source": src + " (sustained cuBLAS bf16)", "traffic": None,
-                         "note": "whole step, cuBLAS GEMMs dominate; retention kernels are about 2 % of the FLOPs"},
-            "e2e": {"value": toks / (ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": host_tokens.numel() * 8, "d2h_bytes_per_step": 4,
-                    "note": "the timed step already copies its token ids from pinned host memory and reads the loss back"},
-            "clocks": clocks, "gpu_launches": launches}), flush=True)
+        print(json.dumps(rec), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the kernels captured with ncu, scaled to the
+# full workload by the token-heads processed where the capture ran on a reduced batch; null where there is no capture.
+NCU_TRAFFIC = {
+    ("ns", "rev"): {"bytes": 1073.8e6 + 506.3e6, "source": "ncu, B=2 capture scaled x4 by token-heads"},
+    ("ns", "fwd"): {"bytes": 1053.0e6, "source": "ncu, B=2 capture scaled x4 by token-heads"},
+}
 
 
 # --------------------------------------------------------------------------------------------------
@@ -396,6 +432,8 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=0, help="c5 only: rows per micro-batch (0 = the workload's default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="leave out the sub-records of the default line (the same problem split over the ranks; the full-stack step)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.workload == "c5":
@@ -416,6 +454,7 @@ def main():
     import torch.distributed as dist
     import flash_pop_b200 as fp
     from flash_pop_b200 import _lib
+    from flash_pop_b200.parallel import partition
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
@@ -429,10 +468,10 @@ def main():
     q, k, v, dO = (t.to(dev, non_blocking=True) for t in (hq, hk, hv, hdO))
     torch.cuda.synchronize()
 
-    def op(q_, k_, v_):
+    def op(q_, k_, v_, decays=dec):
         if w["block"]:
-            return fp.flash_pop_retention(q_, k_, v_, None, dec, w["block"])[0]
-        return fp.fused_chunk_retention(q_, k_, v_, None, dec)[0]
+            return fp.flash_pop_retention(q_, k_, v_, None, decays, w["block"])[0]
+        return fp.fused_chunk_retention(q_, k_, v_, None, decays)[0]
 
     def step():
         ql, kl, vl = (t.detach().requires_grad_(True) for t in (q, k, v))
@@ -467,7 +506,7 @@ def main():
     clocks = sampler.stop() if sampler else None
 
     # per-launch device times for the roofline (same inputs, > L2, so no flush needed): the forward launch, and
-    # the two backward launches singled out by asking for only dQ / only dK,dV (the operator skips the other walk)
+    # the two backward walks singled out by asking for only dQ / only dK,dV (the operator skips the other walk)
     ms_fwd = event_time_ms(fwd_only, max(args.steps, 5))
     ms_bwd = max(ms - ms_fwd, 1e-6)
 
@@ -477,11 +516,15 @@ def main():
         wanted = [leaves[i] for i in of]
         return lambda: torch.autograd.grad(o, wanted, dO, retain_graph=True)
 
-    ms_dq = event_time_ms(only_grads((0,)), max(args.steps, 5))
-    ms_rev = event_time_ms(only_grads((1, 2)), max(args.steps, 5))
+    fn_dq, fn_rev = only_grads((0,)), only_grads((1, 2))
+    fn_dq(); fn_rev()
+    n0 = _lib.launch_count(); fn_dq(); launches_dq = _lib.launch_count() - n0
+    n0 = _lib.launch_count(); fn_rev(); launches_rev = _lib.launch_count() - n0
+    ms_dq = event_time_ms(fn_dq, max(args.steps, 5))
+    ms_rev = event_time_ms(fn_rev, max(args.steps, 5))
 
     # end to end: host (pinned) -> device, forward+backward, every result back to the host
-    e2e_ms = None
+    e2e_ms = copy_only_ms = None
     h2d = sum(t.numel() * 2 for t in (hq, hk, hv, hdO))
     d2h = (2 * hq.numel() + 2 * hv.numel()) * 2
     if not args.no_e2e:
@@ -489,11 +532,10 @@ def main():
             outs_host = [torch.empty_like(hv).pin_memory(), torch.empty_like(hq).pin_memory(),
                          torch.empty_like(hk).pin_memory(), torch.empty_like(hv).pin_memory()]
         if w["block"]:
-            def e2e_step():
-                nonlocal q, k, v, dO
+            def e2e_step(copy_only=False):
                 q.copy_(hq, non_blocking=True); k.copy_(hk, non_blocking=True)
                 v.copy_(hv, non_blocking=True); dO.copy_(hdO, non_blocking=True)
-                res = step()
+                res = (dO, q, k, v) if copy_only else step()
                 for dst, src in zip(outs_host, res):
                     dst.copy_(src, non_blocking=True)
         else:
@@ -501,13 +543,17 @@ def main():
             from flash_pop_b200.host_io import HostRetentionPipeline
             pipe = HostRetentionPipeline(hq, hv, dev)
 
-            def e2e_step():
-                pipe.run(hq, hk, hv, hdO, dec, *outs_host)
+            def e2e_step(copy_only=False):
+                pipe.run(hq, hk, hv, hdO, dec, *outs_host, copy_only=copy_only)
 
         e2e_step()
         barrier()
         e2e_ms = event_time_ms(e2e_step, max(3, min(args.steps, 5)))
         barrier()
+        # the same buffers, slices and streams without the kernels: what the host link alone allows
+        copy_only_ms = event_time_ms(lambda: e2e_step(True), max(3, min(args.steps, 5)))
+        barrier()
+        del outs_host
 
     # POP only: the prediction-token suffixes (one per block, 80 tokens each) run from the block states in place
     suffix = None
@@ -533,9 +579,46 @@ def main():
         s_ms, s_fwd = event_time_ms(suffix_step, args.steps), event_time_ms(suffix_fwd, args.steps)
         s_units = B * N * P * H
         s_bytes = (bf_ := bytes_per_token_head(dk, dv))[0] * s_units + bf_[1] * s_units
+        s_state_bytes = 2 * B * N * H * dk * dv * 2          # start states read, their gradients written
         suffix = {"ms_fwd_bwd": s_ms, "ms_fwd": s_fwd, "suffixes": B * N, "tokens_each": P,
-                  "hbm_gbs_algorithmic": s_bytes / (s_ms * 1e-3) / 1e9,
+                  "hbm_gbs_algorithmic": (s_bytes + s_state_bytes) / (s_ms * 1e-3) / 1e9,
+                  "algorithmic_bytes": s_bytes + s_state_bytes,
                   "note": "start states read in place from block_states; state gradients written back to d_block_states"}
+        del sq, sk, sv, sdo, blocks
+
+    # The same problem split over the ranks (strong scaling): every rank takes its piece of ONE B-row problem (seed 2,
+    # the rows of rank 0's own tensors) with flash_pop_b200.parallel.partition; no data crosses between GPUs.  Each
+    # piece is an under-filled launch, which the operator cuts into T-segments.
+    strong = None
+    if not args.no_extras and not w["block"]:
+        sh = partition(B, H, rank, world)
+        rows = range(sh.batch.start, sh.batch.stop)
+        if rank == 0:
+            piece = [t[sh.batch, :, sh.heads] for t in (q, k, v, dO)]
+        elif len(rows):
+            piece = [t.to(dev)[:, :, sh.heads] for t in make_host_inputs(w, seed=2, pin=False, rows=rows)]
+        else:
+            piece = None
+        ms_strong = 0.0
+        n_strong = 0
+        if piece is not None and piece[0].numel():
+            pq, pk, pv, pdo = piece
+            pdec = sh.take_decays(dec)
+
+            def strong_step():
+                leaves = [t.detach().requires_grad_(True) for t in (pq, pk, pv)]
+                o = op(*leaves, decays=pdec)
+                o.backward(pdo)
+            for _ in range(3):
+                strong_step()
+            n0 = _lib.launch_count(); strong_step(); n_strong = _lib.launch_count() - n0
+            barrier()
+            ms_strong = event_time_ms(strong_step, args.steps)
+        else:
+            barrier()
+        barrier()
+        strong = (ms_strong, n_strong)
+        del piece
 
     # the copy bandwidth of THIS GPU right now (read + write of a 1 GiB device-to-device copy): boxes of the pool differ,
     # and the kernel closest to the HBM roof follows it
@@ -546,11 +629,21 @@ def main():
     copy_gbs = 2 * src_buf.numel() / (event_time_ms(lambda: dst_buf.copy_(src_buf), 10) * 1e-3) / 1e9
     del src_buf, dst_buf
 
-    t_ms = torch.tensor([ms, ms_fwd, ms_bwd, e2e_ms or 0.0, ms_dq, ms_rev], device=dev, dtype=torch.float64)
+    t_ms = torch.tensor([ms, ms_fwd, ms_bwd, e2e_ms or 0.0, ms_dq, ms_rev, copy_only_ms or 0.0, strong[0] if strong else 0.0],
+                        device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
-    ms, ms_fwd, ms_bwd, e2e_max, ms_dq, ms_rev = t_ms.tolist()
+    ms, ms_fwd, ms_bwd, e2e_max, ms_dq, ms_rev, copy_max, strong_max = t_ms.tolist()
     _lib.device_status(dev)
+
+    # the full-stack training step (12 layers, DDP over the ranks, NCCL gradient all-reduce), a few steps
+    c5 = None
+    if not args.no_extras and args.workload == "ns":
+        import gc
+        del q, k, v, dO, hq, hk, hv, hdO, fn_dq, fn_rev      # (and what they keep alive: graphs holding the inputs)
+        gc.collect()
+        torch.cuda.empty_cache()
+        c5 = stack_record(args, dev, rank, world, steps=3, warmup=2, sample_clocks=True)
 
     if rank == 0:
         ff, fb = flops_per_token_head(dk, dv)
@@ -565,11 +658,33 @@ def main():
             peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
             peak_src = "fallback"
         value = total_flop / (ms * 1e-3) / 1e12
-        # Top kernel of the launch list (profiles/): the fused reverse walk (dK, dV, dS_0), one launch per step.  It
-        # reads Q, K, V, dO and writes dK, dV; DRAM traffic per launch from the ncu capture in profiles/ ("ns" only).
-        rev_bytes = 2 * (2 * dk + 2 * dv) * units + 2 * (dk + dv) * units
-        rev_traffic = {"ns": 1073.8e6 + 506.3e6}.get(args.workload)
-        achieved = rev_bytes / (ms_rev * 1e-3) / 1e9
+        pop_state = (2 * dk * dv * 2 * H * B * (T // w["block"])) if w["block"] else 0     # block states written / their gradients read
+        # the launches of a step with their algorithmic bytes: forward (read q,k,v; write o), the dQ walk (read dO,k,v; write
+        # dQ), the reverse walk(s) (read q,k,v,dO; write dK,dV) - one fused launch, or two launches where dv = 256
+        fused = launches_rev == 1 or launches_rev == 3
+        kernels = {
+            "fwd": {"kernel": "scan_kernel<MODE_FWD, forward>", "ms": ms_fwd, "bytes": bf * units + pop_state // 2},
+            "dq": {"kernel": "scan_kernel<MODE_DQ, forward> (dQ walk)", "ms": ms_dq, "bytes": 2 * (dk + 2 * dv + dk) * units,
+                   "launches": launches_dq},
+            "rev": {"kernel": "bwd_fused_kernel (reverse walk: dK, dV, dS0)" if fused else
+                              "scan_kernel reverse walks (dV + dS0, then dK): two launches timed together",
+                    "ms": ms_rev, "bytes": 2 * (2 * dk + 2 * dv) * units + 2 * (dk + dv) * units + pop_state // 2,
+                    "launches": launches_rev},
+        }
+
+        def roof(key):
+            kk = kernels[key]
+            gbs = kk["bytes"] / (kk["ms"] * 1e-3) / 1e9
+            tr = NCU_TRAFFIC.get((args.workload, key))
+            out = {"bound": "hbm", "kernel": kk["kernel"], "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                   "frac": gbs / peaks["hbm_gbs"], "peak_source": peak_src, "algorithmic_bytes": kk["bytes"], "ms_per_launch": kk["ms"],
+                   "traffic": tr["bytes"] if tr else None,
+                   "traffic_source": tr["source"] if tr else "no ncu capture of this kernel at this workload"}
+            if "launches" in kk:
+                out["launches"] = kk["launches"]
+            return out
+
+        top = max(kernels, key=lambda name: kernels[name]["ms"])       # the launch with the largest share of the step
         step_gbs = (bf + bb) * units / (ms * 1e-3) / 1e9
         line = {
             "metric": "chunked_retention_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s",
@@ -581,19 +696,10 @@ def main():
             "hbm_gbs_algorithmic": (bf + bb) * units / (ms * 1e-3) / 1e9,
             "ms_fwd": ms_fwd, "ms_bwd": ms_bwd, "ms_bwd_dq": ms_dq, "ms_bwd_dkdv": ms_rev,
             "path": {1: "cuda-core", 2: "tcgen05"}.get(path, "none"),
-            "config": {"workload": workload_name(args, w), "l2": "inputs (1 GB+) larger than the 126 MB L2; no flush",
-                       "flop_count": "algorithmic, causal half of intra-chunk tiles (C=64)"},
-            "roofline": {"bound": "hbm", "kernel": "bwd_fused_kernel (reverse walk: dK, dV, dS0; one launch per step, largest share)",
-                         "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                         "peak_source": peak_src, "traffic": rev_traffic, "algorithmic_bytes": rev_bytes, "ms_per_launch": ms_rev,
-                         "copy_gbs_this_gpu": copy_gbs, "frac_of_copy_here": achieved / copy_gbs},
-            "roofline_fwd": {"bound": "hbm", "kernel": "scan_kernel<MODE_FWD, forward>", "achieved": bf * units / (ms_fwd * 1e-3) / 1e9,
-                             "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": bf * units / (ms_fwd * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                             "algorithmic_bytes": bf * units, "ms_per_launch": ms_fwd},
-            "roofline_dq": {"bound": "hbm", "kernel": "scan_kernel<MODE_DQ, forward>", "achieved": bf * units / (ms_dq * 1e-3) / 1e9,
-                            "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": bf * units / (ms_dq * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                            "algorithmic_bytes": bf * units, "ms_per_launch": ms_dq},
-            "roofline_step": {"bound": "hbm", "kernels": "the three launches of a step (forward, dQ, fused reverse)", "achieved": step_gbs,
+            "config": op_config(args, w),
+            "roofline": dict(roof(top), copy_gbs_this_gpu=copy_gbs, frac_of_copy_here=roof(top)["achieved"] / copy_gbs),
+            "roofline_fwd": roof("fwd"), "roofline_dq": roof("dq"), "roofline_rev": roof("rev"),
+            "roofline_step": {"bound": "hbm", "kernels": "all launches of a step (forward, dQ walk, reverse walk)", "achieved": step_gbs,
                               "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": step_gbs / peaks["hbm_gbs"],
                               "algorithmic_bytes": (bf + bb) * units},
             "clocks": clocks,
@@ -603,13 +709,27 @@ def main():
             line["pop_suffixes"] = suffix
         if e2e_ms is not None:
             line["e2e"] = {"value": total_flop / (e2e_max * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_max,
-                           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+                           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                           "copy_only_ms": copy_max, "frac_of_copy_only": copy_max / e2e_max,
+                           "host_link_gbs_each_way": world * h2d / (copy_max * 1e-3) / 1e9,
+                           "note": "copy_only_ms = the same pinned buffers, slices and streams with the kernels left out"}
+        if strong is not None:
+            one_gpu_flop = (ff + fb) * units
+            line["strong"] = {"what": f"ONE problem of B={B} rows (seed 2) split over {world} rank(s) by batch row, then by heads; "
+                                      "no data exchange; under-filled pieces run as T-segments",
+                              "ms_per_step": strong_max, "value": one_gpu_flop / (strong_max * 1e-3) / 1e12, "unit": "TFLOP/s",
+                              "launches_per_step_rank0": strong[1],
+                              "speedup_vs_one_gpu": ms / strong_max, "efficiency": ms / strong_max / world,
+                              "one_gpu_ms": ms}
+        if c5 is not None:
+            line["c5"] = {kk: c5[kk] for kk in ("metric", "value", "unit", "ms_per_step", "steps", "warmup", "scaling", "loss", "config",
+                                              "roofline", "clocks", "gpu_launches")}
         if not args.no_cpu_baseline and world == 1:
             threads = os.cpu_count() or 1
-            tf, dt = cpu_port_tflops(w, 1, 2, threads)
+            passes = 3
+            tf, dt = cpu_reference_tflops(w, 1, passes, 1, threads)
             line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
-                                    "sample": f"1 of {B} batch rows (H={H}, T={T}), fp32 torch CPU, chunk {CHUNK}, "
-                                              f"best of 2 after a warm-up, {dt:.2f} s per pass"}
+                                    "sample": cpu_sample_text(w, 1, passes) + f", {dt:.2f} s per pass"}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

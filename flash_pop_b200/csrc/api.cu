@@ -35,6 +35,8 @@ std::atomic<int64_t> g_launches{0};
 
 struct Call {
   int dtype, B, T, H, dk, dv, block_size, n_blocks, flags;
+  bool state_f32;            // states are fp32 (always so for fp32 activations)
+  float* scratch; int64_t scratch_bytes;
   float gamma[FPB_MAX_HEADS];
   bool tensor_core_decays;   // every decay large enough for the gamma^-L rescaling of the tcgen05 path
 };
@@ -71,6 +73,10 @@ int check_dims(const fpb_dims* d, bool pop, Call* c) {
   if (d->H > 0 && !d->head_decays) return FPB_ERR_NULL_POINTER;
   c->dtype = d->dtype; c->B = d->B; c->T = d->T; c->H = d->H; c->dk = d->dk; c->dv = d->dv;
   c->flags = d->flags;
+  c->state_f32 = d->dtype == FPB_F32 || (d->flags & FPB_FLAG_STATE_F32) != 0;
+  if (d->workspace_bytes < 0 || (uintptr_t)d->workspace % 16) return FPB_ERR_BAD_WORKSPACE;
+  c->scratch = (d->workspace && d->workspace_bytes > 0) ? (float*)d->workspace : nullptr;
+  c->scratch_bytes = c->scratch ? d->workspace_bytes : 0;
   c->block_size = pop ? d->block_size : 0;
   c->n_blocks = pop ? d->T / d->block_size : 0;
   c->tensor_core_decays = true;
@@ -130,8 +136,10 @@ int forward(const Call& c, int64_t batch, SeqView q, SeqView k, SeqView v, State
     a.q = q; a.k = k; a.v = v; a.o = o; a.s0 = s0; a.s_out = s_out; a.block_states = block_states; a.sfx = sfx;
     a.B = (int)batch; a.T = c.T; a.H = c.H; a.dk = c.dk; a.dv = c.dv; a.dtype = c.dtype;
     a.block_size = c.block_size; a.n_blocks = c.n_blocks; a.gamma = c.gamma;
-    const int r = launch_umma_fwd(a, stream);
-    if (r == FPB_OK) return finish_launches(1, FPB_PATH_TCGEN05);
+    a.state_f32 = c.state_f32; a.scratch = c.scratch; a.scratch_bytes = c.scratch_bytes;
+    int n_launched = 0;
+    const int r = launch_umma_fwd(a, stream, &n_launched);
+    if (r == FPB_OK) return finish_launches(n_launched, FPB_PATH_TCGEN05);
     if (r != FPB_UMMA_NOT_APPLICABLE) return r;
   }
   WalkParams p;
@@ -139,7 +147,7 @@ int forward(const Call& c, int64_t batch, SeqView q, SeqView k, SeqView v, State
   own_is_dv(p, c);
   p.u = v; p.w = k; p.r = q; p.out = o; p.scale_w = rs;
   p.x0 = s0; p.x_out = s_out; p.block_out = block_states;
-  const int r = launch_walk(p, c.dtype, (int)batch, stream);
+  const int r = launch_walk(p, c.dtype, c.state_f32, (int)batch, stream);
   return r != FPB_OK ? r : finish_launches(1, FPB_PATH_SIMT);
 }
 
@@ -157,6 +165,7 @@ int backward(const Call& c, int64_t batch, SeqView q, SeqView k, SeqView v, Stat
     a.B = (int)batch; a.T = c.T; a.H = c.H; a.dk = c.dk; a.dv = c.dv; a.dtype = c.dtype;
     a.block_size = c.block_size; a.n_blocks = c.n_blocks; a.gamma = c.gamma;
     a.skip_dq = (c.flags & FPB_FLAG_SKIP_DQ) != 0; a.skip_dkdv = (c.flags & FPB_FLAG_SKIP_DKDV) != 0;
+    a.state_f32 = c.state_f32; a.scratch = c.scratch; a.scratch_bytes = c.scratch_bytes;
     int n_launched = 0;
     const int r = launch_umma_bwd(a, stream, &n_launched);
     if (r == FPB_OK) return finish_launches(n_launched, FPB_PATH_TCGEN05);
@@ -169,7 +178,7 @@ int backward(const Call& c, int64_t batch, SeqView q, SeqView k, SeqView v, Stat
     fill_common(p, c, +1, sfx_in);
     own_is_dk(p, c);
     p.u = k; p.w = v; p.r = dO; p.out = dQ; p.scale_u = rs; p.x0 = s0;
-    if ((r = launch_walk(p, c.dtype, (int)batch, stream)) != FPB_OK) return r;
+    if ((r = launch_walk(p, c.dtype, c.state_f32, (int)batch, stream)) != FPB_OK) return r;
     ++n;
   }
   if (!(c.flags & FPB_FLAG_SKIP_DKDV)) {
@@ -178,7 +187,7 @@ int backward(const Call& c, int64_t batch, SeqView q, SeqView k, SeqView v, Stat
     own_is_dv(p, c);
     p.u = dO; p.w = q; p.r = k; p.out = dV; p.scale_r = rs;
     p.x0 = d_s_out; p.x_out = d_s0; p.block_in = d_block_states;
-    if ((r = launch_walk(p, c.dtype, (int)batch, stream)) != FPB_OK) return r;
+    if ((r = launch_walk(p, c.dtype, c.state_f32, (int)batch, stream)) != FPB_OK) return r;
     // dK: reverse walk, transposed ownership
     SuffixStates no_write = sfx_grad;
     no_write.blocks = nullptr;
@@ -186,7 +195,7 @@ int backward(const Call& c, int64_t batch, SeqView q, SeqView k, SeqView v, Stat
     own_is_dk(p, c);
     p.u = q; p.w = dO; p.r = v; p.out = dK; p.scale_out = rs;
     p.x0 = d_s_out; p.block_in = d_block_states;
-    if ((r = launch_walk(p, c.dtype, (int)batch, stream)) != FPB_OK) return r;
+    if ((r = launch_walk(p, c.dtype, c.state_f32, (int)batch, stream)) != FPB_OK) return r;
     n += 2;
   }
   return finish_launches(n, FPB_PATH_SIMT);
@@ -295,7 +304,7 @@ int fpb_pop_suffix_bwd(const fpb_dims* dims, int32_t M, int32_t N, const fpb_seq
   if (M > 1 && c.B > 0 && c.H > 0 && (!block_states || !d_block_states)) return FPB_ERR_NULL_POINTER;
   FPB_TRY(check_device());
   if (c.B == 0 || c.H == 0) return FPB_OK;
-  const size_t esize = c.dtype == FPB_F32 ? 4 : 2;
+  const size_t esize = c.state_f32 ? 4 : 2;
   const size_t blk = (size_t)c.H * c.dk * c.dv * esize;
   // blocks that no suffix starts from get a zero gradient
   if (d_block_states && N > 0) {
@@ -498,11 +507,21 @@ const char* fpb_strerror(int status) {
     case FPB_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel gave up";
     case FPB_ERR_TENSOR_MAP: return "could not encode a TMA tensor map for a tensor";
     case FPB_ERR_TOO_LARGE: return "size beyond a fixed limit of this entry point";
+    case FPB_ERR_BAD_WORKSPACE: return "workspace pointer not 16-byte aligned or negative size";
     default: return "unknown status";
   }
 }
 
-int fpb_version(void) { return 100; }
+int fpb_version(void) { return 200; }
+
+int64_t fpb_workspace_bytes(const fpb_dims* dims) {
+  // what lets the emptiest pass of this shape (one CTA per batch row and head) split as far as it would
+  if (!dims || dims->B <= 0 || dims->H <= 0 || dims->T <= 0 || dims->dk <= 0 || dims->dv <= 0) return 0;
+  if (dims->dtype != FPB_BF16 || check_device() != FPB_OK) return 0;
+  const Segments sg = choose_segments((long long)dims->B * dims->H, 1, dims->T, 64, (long long)dims->B * dims->H,
+                                      (long long)dims->dk * dims->dv, 0, dims->B);
+  return sg.n > 1 ? (int64_t)dims->B * dims->H * sg.n * dims->dk * dims->dv * 4 : 0;
+}
 int fpb_last_path(void) { return tl_last_path; }
 int fpb_last_cuda_error(void) { return tl_last_cuda_error; }
 int64_t fpb_launch_count(void) { return g_launches.load(); }

@@ -47,7 +47,8 @@ struct WalkParams {
   float gamma[FPB_MAX_HEADS];
 };
 
-int launch_walk(const WalkParams& p, int dtype, int B, cudaStream_t stream);
+// `state_f32`: the states (x0, x_out, block states, suffix start states) are fp32 whatever the activations are
+int launch_walk(const WalkParams& p, int dtype, bool state_f32, int B, cudaStream_t stream);
 
 // One recurrent decoding step (retention_step.cu); `dtype` is that of q, k, v, o, `state_dtype` that of the states.
 int launch_retention_step(int dtype, int state_dtype, int B, int H, int dk, int dv, const float* gamma, SeqView q,
@@ -70,6 +71,30 @@ int launch_xent_fwd(int dtype, int64_t rows, int V, const void* logits, int64_t 
                     float* lse, cudaStream_t stream);
 int launch_xent_bwd(int dtype, int64_t rows, int V, const void* logits, int64_t row_stride, const int64_t* targets, const float* lse,
                     const float* scale, float row_weight, void* d_logits, int64_t d_stride, cudaStream_t stream);
+
+// Per-launch knobs of the tcgen05 kernels.  A release build always passes the defaults; the diagnostics build
+// (-DFPB_DIAGNOSTICS) exports setters so that tests can shorten the wait limit or compare schedules.
+struct WalkTuning {
+  long long wait_cycles;    // limit of every bounded wait inside a kernel, in clock64() ticks
+  int32_t idle_ns;          // suspend hint (ns) of a polling loop that found nothing to do
+  int32_t sc_early;         // walks whose scores do not read the scaled tile issue them as soon as the tiles landed
+  int32_t withhold_chunk;   // diagnostics only: the producer never loads this chunk of any sequence (-1 = none)
+};
+const WalkTuning& walk_tuning();
+
+// Cutting each sequence of an under-filled launch into `n` T-segments of `seg_len` tokens (see segment_scan.cu).
+struct Segments {
+  int32_t n, seg_len;       // n == 1: the sequences are walked whole
+};
+// `units` CTAs the launch would have unsplit, `ctas_per_sm` of them resident per SM; `align` = token count every
+// segment start must be a multiple of; state_floats = dk * dv; scratch holds B*H*n*state_floats floats.
+Segments choose_segments(long long units, int ctas_per_sm, int T, int align, long long batch_heads, long long state_floats,
+                         long long scratch_bytes, int B);
+// Start values of the segments from their local end values: in place over `seg` (B, H, n, dk, dv) fp32.
+//   forward : A_0 = start, A_{s+1} = gamma^len_s A_s + E_s ; seg[s] <- A_s ; end <- A_n
+//   reverse : A_{n-1} = start, A_{s-1} = gamma^len_s A_s + E_s ; seg[s] <- A_s ; end <- value carried past segment 0
+int launch_segment_combine(float* seg, Segments sg, int B, int T, int H, int dk, int dv, const float* gamma, bool reverse,
+                           StateView start, StateView end, bool state_f32, cudaStream_t stream);
 
 // Device status word shared by all kernels: 0 = fine; otherwise (role << 8 | barrier id) of the
 // first bounded wait that gave up.

@@ -66,10 +66,13 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity
   return ok != 0;
 }
 
-// Every wait in the kernels is bounded: after about a second of spinning (or as soon as another
-// thread of the CTA has given up, *abort_flag != 0) the wait returns false, and the caller records
-// which wait it was and leaves its loop.
+// Every wait in the kernels is bounded: after `limit` cycles of spinning (about a second by default; the launcher
+// writes the limit next to the CTA's abort flag in shared memory) or as soon as another thread of the CTA has given
+// up (*abort_flag != 0) the wait returns false, and the caller records which wait it was and leaves its loop.
 constexpr long long kWaitCycles = 1ll << 31;
+__device__ __forceinline__ long long wait_limit(volatile int* abort_flag) {
+  return *reinterpret_cast<volatile long long*>(abort_flag + 1);
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
@@ -77,7 +80,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 63) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitCycles) return false;
+      if (clock64() - t0 > wait_limit(abort_flag)) return false;
     }
   }
   return true;

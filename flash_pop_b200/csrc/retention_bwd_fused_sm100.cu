@@ -21,6 +21,10 @@
 // polls its barriers and runs whichever task is ready; every wait is bounded.  Tensor memory (512 columns at
 // dk = dv = 128): the M = 64 tiles are lane-interleaved (two per column range) — Sc1 x2, Sc2 x2, ACCV | ACCK —
 // and dG is double-buffered.
+#include <atomic>
+#include <cmath>
+#include <type_traits>
+
 #include "fpb_common.cuh"
 #include "ptx_sm100.cuh"
 #include "scan_common.cuh"
@@ -41,12 +45,17 @@ struct BwdParams {
   CUtensorMap map_q, map_k, map_v, map_do, map_dk, map_dv;
   bf16* dk_out; int64_t dk_sb, dk_st, dk_sh;
   bf16* dv_out; int64_t dv_sb, dv_st, dv_sh;
-  const bf16* g_start; int64_t gs_sb, gs_sh;     // gradient of the returned state (start of the reverse walk), or null
-  bf16* g_end; int64_t ge_sb, ge_sh;             // dS_0 (end of the reverse walk), or null
-  const bf16* block_grads;                       // POP: gradients of the block states (B, NB, H, dk, dv), or null
-  bf16* sfx_blocks; int32_t sfx_M, sfx_N;        // suffix calls: gradients of the start states taken from block states
+  // states are bf16 or fp32 (state_f32), strides in elements
+  const void* g_start; int64_t gs_sb, gs_sh;     // gradient of the returned state (start of the reverse walk), or null
+  void* g_end; int64_t ge_sb, ge_sh;             // dS_0 (end of the reverse walk), or null
+  const void* block_grads;                       // POP: gradients of the block states (B, NB, H, dk, dv), or null
+  void* sfx_blocks; int32_t sfx_M, sfx_N;        // suffix calls: gradients of the start states taken from block states
   int32_t sfx_G;                                 // suffixes one CTA walks back to back as one sequence (>= 1)
   int32_t T, H, dk, dv, block_size, n_blocks;
+  int32_t state_f32;
+  int32_t n_seg, seg_len;                        // T-segments (segment_scan.cu): blockIdx.z = batch * n_seg + segment
+  const float* seg_states;                       // fp32 (B, H, n_seg, dk, dv): G after the last token of each segment
+  WalkTuning tune;
   int32_t* status;
   long long* trace;
   float log2g[FPB_MAX_HEADS];
@@ -54,7 +63,8 @@ struct BwdParams {
 
 enum { B_FULL = 0, B_EMPTY = 3, B_VRDY = 6, B_SCFULL = 9, B_PRDY = 11, B_ACCFULL = 13, B_ACCFREE = 14, B_DSFULL = 15,
        B_DSFREE = 17, B_SBRDY = 19, B_SBFREE = 20, B_COUNT = 21 };
-constexpr int OFF_TMEM_SLOT = B_COUNT * 8, OFF_ABORT = OFF_TMEM_SLOT + 4, BAR_PAGE = 256;
+constexpr int OFF_TMEM_SLOT = B_COUNT * 8, OFF_ABORT = OFF_TMEM_SLOT + 4, OFF_LIMIT = OFF_ABORT + 4, BAR_PAGE = 256;
+static_assert(OFF_LIMIT % 8 == 0 && OFF_LIMIT + 8 <= BAR_PAGE, "the wait limit sits right after the abort flag");
 
 template <int DK, int DV>
 struct BCfg {
@@ -91,7 +101,8 @@ struct BCfg {
   static constexpr int NS = DK == 128 ? WCOLS : WCOLS / 2;
 };
 
-template <int DK, int DV>
+// SF32: the call's state tensors (gradient of the returned state, dS_0, block-state gradients) are fp32.
+template <int DK, int DV, bool SF32>
 __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(const __grid_constant__ BwdParams p) {
   using G = BCfg<DK, DV>;
   extern __shared__ __align__(1024) uint8_t sm[];
@@ -104,10 +115,15 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + G::OFF_BAR + OFF_TMEM_SLOT);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int h = blockIdx.y, b = blockIdx.z;
+  const int h = blockIdx.y;
+  const int b = p.n_seg > 1 ? (int)blockIdx.z / p.n_seg : (int)blockIdx.z;
+  const int seg = p.n_seg > 1 ? (int)blockIdx.z % p.n_seg : 0;
+  // this CTA walks tokens [t0, t_end) of the sequence; chunk positions are absolute (t0 is a chunk and block multiple)
+  const int t0 = seg * p.seg_len;
+  const int t_end = p.n_seg > 1 ? min(t0 + p.seg_len, p.T) : p.T;
   const float lg = p.log2g[h];
   const float rs = rsqrtf((float)p.dk);
-  const int NC = chunk_count(p.T, p.block_size);
+  const int NC = chunk_count(t_end - t0, p.block_size);
   auto bar = [&](int slot) { return sbase + G::OFF_BAR + slot * 8; };
   auto stage_of = [&](int n) { return n % G::STAGES; };
   auto stage_ph = [&](int n) { return (uint32_t)((n / G::STAGES) & 1); };
@@ -128,6 +144,7 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
     mbar_init(bar(B_SBRDY), G::N_STATE); mbar_init(bar(B_SBFREE), 1);
     fence_mbar_init();
     *abort_flag = 0;
+    *reinterpret_cast<volatile long long*>(sm + G::OFF_BAR + OFF_LIMIT) = p.tune.wait_cycles;
     prefetch_tmap(&p.map_q); prefetch_tmap(&p.map_k); prefetch_tmap(&p.map_v); prefetch_tmap(&p.map_do);
     prefetch_tmap(&p.map_dk); prefetch_tmap(&p.map_dv);
   }
@@ -137,7 +154,7 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
   tc_fence_after();
   const uint32_t tm = *tmem_slot;
 
-  Chunk first{p.T, 0};
+  Chunk first{t_end, 0};
   prev_chunk(first, p.block_size);
 
   // =============================================================================================
@@ -149,6 +166,7 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
         const int s = stage_of(c);
         if (!mbar_wait(bar(B_EMPTY + s), stage_ph(c) ^ 1, abort_flag)) { FPB_GIVE_UP(0x100 | B_EMPTY); break; }
         FPB_TRACE(14, c);
+        if (c == p.tune.withhold_chunk) { prev_chunk(ck, p.block_size); continue; }   // diagnostics: this chunk never arrives
         const uint32_t st = sbase + G::OFF_STAGE + s * G::STAGE_BYTES;
         mbar_arrive_expect_tx(bar(B_FULL + s), G::STAGE_BYTES);
 #pragma unroll
@@ -165,9 +183,9 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
         prev_chunk(ck, p.block_size);
       }
       if (*abort_flag) {   // let the copies in flight land before the CTA's shared memory is released
-        for (int i = max(0, issued - G::STAGES); i < issued; ++i) {
-          const long long t0 = clock64();
-          while (!mbar_try_wait(bar(B_FULL + stage_of(i)), stage_ph(i)) && clock64() - t0 < kWaitCycles) {}
+        for (int i = max(0, issued - G::STAGES); i < issued && p.tune.withhold_chunk < 0; ++i) {
+          const long long w0 = clock64();
+          while (!mbar_try_wait(bar(B_FULL + stage_of(i)), stage_ph(i)) && clock64() - w0 < wait_limit(abort_flag)) {}
         }
       }
     }
@@ -371,9 +389,9 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
           epilogue(n_e, ck_e, true);
           break;
         } else if (n_p < NC && n_p < n_e + G::NP) {
-          mbar_try_wait_hint(bar(B_SCFULL + (n_p & 1)), (n_p >> 1) & 1, 200);
+          mbar_try_wait_hint(bar(B_SCFULL + (n_p & 1)), (n_p >> 1) & 1, p.tune.idle_ns);
         } else {
-          mbar_try_wait_hint(bar(B_ACCFULL), n_e & 1, 200);
+          mbar_try_wait_hint(bar(B_ACCFULL), n_e & 1, p.tune.idle_ns);
         }
       }
       if (t == 0) tma_store_wait_all0();
@@ -388,11 +406,15 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
     auto row_of = [&](int i) { return DK == 128 ? q4 * 32 + lane : q4 * 16 + (lane >> 2) + 8 * ((i >> 1) & 1); };
     auto col_of = [&](int i) { return DK == 128 ? wcol0 + i : wcol0 + 8 * (i >> 2) + 2 * (lane & 3) + (i & 1); };
 
-    const int64_t state_elems = (int64_t)p.dk * p.dv;
+    const int64_t state_elems = (int64_t)(DK * DV);
     // start: gradient of the returned state (none for suffix calls, whose end states are dropped);
     // end: dS_0, or for suffix m > 0 of a row the gradient of block state m-1
-    const bf16* x_start = nullptr;
-    bf16* x_end = nullptr;
+    const void* x_start = nullptr;
+    void* x_end = nullptr;
+    constexpr std::bool_constant<SF32> state_t{};
+    constexpr std::true_type scratch_t{};
+    constexpr int esz = SF32 ? 4 : 2;
+    auto at = [&](const void* base, int64_t elems) { return (void*)((const char*)base + elems * esz); };
     // suffix calls: the batch index is (row, group of sfx_G consecutive suffixes); the walk goes through the group's
     // suffixes from the last to the first, and what it carries when it leaves suffix m is the gradient of the state
     // that suffix started from
@@ -401,18 +423,41 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
     constexpr bool GROUPED = DK == 64 && DV == 64;
     const int sfx_g = GROUPED ? p.sfx_G : 1;
     const int groups = p.sfx_M > 0 ? p.sfx_M / sfx_g : 1;
-    auto sfx_grad = [&](int m) -> bf16* {
+    auto sfx_grad = [&](int m) -> void* {
       const int sfx_row = b / groups;
-      if (m == 0) return p.g_end ? p.g_end + sfx_row * p.ge_sb + h * p.ge_sh : nullptr;
-      return p.sfx_blocks ? p.sfx_blocks + (((int64_t)sfx_row * p.sfx_N + (m - 1)) * p.H + h) * state_elems : nullptr;
+      if (m == 0) return p.g_end ? at(p.g_end, sfx_row * p.ge_sb + h * p.ge_sh) : nullptr;
+      return p.sfx_blocks ? at(p.sfx_blocks, (((int64_t)sfx_row * p.sfx_N + (m - 1)) * p.H + h) * state_elems) : nullptr;
     };
-    if (p.sfx_M > 0) {
+    if (p.n_seg > 1) {
+      // T-segments: G after this piece's last token was put into fp32 scratch by the scan, which also wrote dS_0
+      x_start = p.seg_states + (((int64_t)b * p.H + h) * p.n_seg + seg) * state_elems;
+    } else if (p.sfx_M > 0) {
       if (sfx_g == 1) x_end = sfx_grad(b % groups);    // grouped walks store at every suffix start, inside the loop
     } else {
-      if (p.g_start) x_start = p.g_start + b * p.gs_sb + h * p.gs_sh;
-      if (p.g_end) x_end = p.g_end + b * p.ge_sb + h * p.ge_sh;
+      if (p.g_start) x_start = at(p.g_start, b * p.gs_sb + h * p.gs_sh);
+      if (p.g_end) x_end = at(p.g_end, b * p.ge_sb + h * p.ge_sh);
     }
-    auto load_global = [&](const bf16* src, bool accumulate) {
+    auto load_global = [&](const void* src_, auto f32, bool accumulate) {
+      if constexpr (decltype(f32)::value) {
+        const float* src = (const float*)src_;
+        if (DK == 128) {
+          const float* rowp = src + (int64_t)row_of(0) * p.dv + wcol0;
+#pragma unroll
+          for (int i = 0; i < G::NS; i += 4) {
+            const float4 val = *reinterpret_cast<const float4*>(rowp + i);
+            S[i] = (accumulate ? S[i] : 0.f) + val.x; S[i + 1] = (accumulate ? S[i + 1] : 0.f) + val.y;
+            S[i + 2] = (accumulate ? S[i + 2] : 0.f) + val.z; S[i + 3] = (accumulate ? S[i + 3] : 0.f) + val.w;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < G::NS; i += 2) {
+            const float2 f = *reinterpret_cast<const float2*>(src + (int64_t)row_of(i) * p.dv + col_of(i));
+            S[i] = (accumulate ? S[i] : 0.f) + f.x;
+            S[i + 1] = (accumulate ? S[i + 1] : 0.f) + f.y;
+          }
+        }
+      } else {
+      const bf16* src = (const bf16*)src_;
       if (DK == 128) {
         const bf16* rowp = src + (int64_t)row_of(0) * p.dv + wcol0;
 #pragma unroll
@@ -434,12 +479,27 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
           S[i + 1] = (accumulate ? S[i + 1] : 0.f) + f.y;
         }
       }
+      }
     };
     auto inject = [&](int end) {
       if (p.block_size > 0 && p.block_grads && end % p.block_size == 0 && end / p.block_size - 1 < p.n_blocks)
-        load_global(p.block_grads + (((int64_t)b * p.n_blocks + (end / p.block_size - 1)) * p.H + h) * state_elems, true);
+        load_global(at(p.block_grads, (((int64_t)b * p.n_blocks + (end / p.block_size - 1)) * p.H + h) * state_elems),
+                    state_t, true);
     };
-    auto store_global = [&](bf16* dst) {
+    auto store_global = [&](void* dst_) {
+      if constexpr (SF32) {
+        float* dst = (float*)dst_;
+        if (DK == 128) {
+          float* rowp = dst + (int64_t)row_of(0) * p.dv + wcol0;
+#pragma unroll
+          for (int i = 0; i < G::NS; i += 4) *reinterpret_cast<float4*>(rowp + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < G::NS; i += 2)
+            *reinterpret_cast<float2*>(dst + (int64_t)row_of(i) * p.dv + col_of(i)) = make_float2(S[i], S[i + 1]);
+        }
+      } else {
+      bf16* dst = (bf16*)dst_;
       if (DK == 128) {
         bf16* rowp = dst + (int64_t)row_of(0) * p.dv + wcol0;
 #pragma unroll
@@ -453,6 +513,7 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
 #pragma unroll
         for (int i = 0; i < G::NS; i += 2)
           *reinterpret_cast<uint32_t*>(dst + (int64_t)row_of(i) * p.dv + col_of(i)) = pack_bf16(S[i], S[i + 1]);
+      }
       }
     };
     // Gb: [DV/64 column blocks][DK rows][128 bytes], 16-byte pieces XOR-swizzled by (row & 7): an MN-major B
@@ -504,7 +565,10 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
       mbar_arrive(bar(B_VRDY + s));
     };
 
-    if (x_start) load_global(x_start, false);
+    if (x_start) {
+      if (p.n_seg > 1) load_global(x_start, scratch_t, false);
+      else load_global(x_start, state_t, false);
+    }
     else {
 #pragma unroll
       for (int i = 0; i < G::NS; ++i) S[i] = 0.f;
@@ -546,7 +610,7 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
           mbar_arrive(bar(B_DSFREE + (n_u & 1)));
           ++n_u;
           if (GROUPED && sfx_g > 1 && ck_u.a % p.block_size == 0) {   // that was the first chunk of a suffix
-            bf16* dst = sfx_grad((b % groups) * sfx_g + ck_u.a / p.block_size);
+            void* dst = sfx_grad((b % groups) * sfx_g + ck_u.a / p.block_size);
             if (dst) store_global(dst);
 #pragma unroll
             for (int i = 0; i < G::NS; ++i) S[i] = 0.f;      // the suffix before it ends in a state nobody reads
@@ -560,8 +624,8 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
         }
         if (progress) patience.progress();
         else if (patience.exhausted(abort_flag)) { FPB_GIVE_UP(0x400 | (n_u & 0xff)); break; }
-        else if (publish_due) mbar_try_wait_hint(bar(B_SBFREE), (n_u - 1) & 1, 200);
-        else mbar_try_wait_hint(bar(B_DSFULL + (n_u & 1)), (n_u >> 1) & 1, 200);
+        else if (publish_due) mbar_try_wait_hint(bar(B_SBFREE), (n_u - 1) & 1, p.tune.idle_ns);
+        else mbar_try_wait_hint(bar(B_DSFULL + (n_u & 1)), (n_u >> 1) & 1, p.tune.idle_ns);
       }
     }
     if (x_end && !*abort_flag) store_global(x_end);
@@ -573,39 +637,44 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tm, G::TM_COLS); }
 }
 
-template <int DK, int DV>
+template <int DK, int DV, bool SF32>
 int launch_fused_t(const BwdParams& p, dim3 grid, cudaStream_t stream) {
   using G = BCfg<DK, DV>;
-  static bool configured[64] = {};
+  static std::atomic<bool> configured[64];
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64 || !configured[dev]) {
-    if (cudaFuncSetAttribute(bwd_fused_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM) != cudaSuccess)
+  if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
+    if (cudaFuncSetAttribute(bwd_fused_kernel<DK, DV, SF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM) != cudaSuccess)
       return FPB_ERR_LAUNCH;
-    if (dev >= 0 && dev < 64) configured[dev] = true;
+    if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
   }
-  bwd_fused_kernel<DK, DV><<<grid, G::NTHREADS, G::SMEM, stream>>>(p);
+  bwd_fused_kernel<DK, DV, SF32><<<grid, G::NTHREADS, G::SMEM, stream>>>(p);
   return FPB_OK;
 }
 
-bool state_ok(const StateView& s) { return !s.data || ((uintptr_t)s.data % 16 == 0 && s.sb % 8 == 0 && s.sh % 8 == 0); }
+bool state_ok(const StateView& s, bool f32) {
+  const int64_t m = f32 ? 4 : 8;
+  return !s.data || ((uintptr_t)s.data % 16 == 0 && s.sb % m == 0 && s.sh % m == 0);
+}
+int gcd_int(int a, int b) { while (b) { const int t = a % b; a = b; b = t; } return a; }
 
 }  // namespace
 
 // dK, dV and dS_0 in one reverse walk.  FPB_UMMA_NOT_APPLICABLE when the shape is not one the kernel is built for.
-int launch_bwd_fused(const UmmaBwdArgs& a, cudaStream_t stream) {
+int launch_bwd_fused(const UmmaBwdArgs& a, cudaStream_t stream, int* n_launched) {
   const bool dims_ok = (a.dk == 64 || a.dk == 128) && (a.dv == 64 || a.dv == 128);
   if (!dims_ok || a.dtype != FPB_BF16 || a.T <= 0 || a.B > 65535 || a.H > 65535) return FPB_UMMA_NOT_APPLICABLE;
   if (!tma_addressable(a.q, 2) || !tma_addressable(a.k, 2) || !tma_addressable(a.v, 2) || !tma_addressable(a.dO, 2) ||
       !tma_addressable(a.dK, 2) || !tma_addressable(a.dV, 2))
     return FPB_UMMA_NOT_APPLICABLE;
-  if (!state_ok(a.d_s_out) || !state_ok(a.d_s0) || (uintptr_t)a.d_block_states % 16 || (uintptr_t)a.sfx_grad.blocks % 16)
+  if (!state_ok(a.d_s_out, a.state_f32) || !state_ok(a.d_s0, a.state_f32) || (uintptr_t)a.d_block_states % 16 ||
+      (uintptr_t)a.sfx_grad.blocks % 16)
     return FPB_UMMA_NOT_APPLICABLE;
   BwdParams p;
   int r;
   int B = a.B, T = a.T, block_size = a.block_size;
   const int H = a.H;
-  // suffix calls: G consecutive suffixes of a row as one sequence per CTA (see launch_pass in retention_scan_sm100.cu)
+  // suffix calls: G consecutive suffixes of a row as one sequence per CTA (see launch_one in retention_scan_sm100.cu)
   SeqView q = a.q, k = a.k, v = a.v, dO = a.dO, dK = a.dK, dV = a.dV;
   int G = 1;
   if (a.sfx_grad.M > 1 && a.block_size == 0) {
@@ -617,6 +686,21 @@ int launch_bwd_fused(const UmmaBwdArgs& a, cudaStream_t stream) {
       for (SeqView* s : {&q, &k, &v, &dO, &dK, &dV}) s->sb *= G;
     }
   }
+  // under-filled: cut the sequences into T-segments (segment_scan.cu) - local values of G per piece from a reverse
+  // state-only walk over (Q, dO), the scan (which also writes dS_0), then this kernel once per piece
+  Segments sg{1, 0};
+  if (segments_enabled() && a.scratch && a.sfx_grad.M == 0) {
+    const int align = a.block_size > 0 ? C / gcd_int(C, a.block_size) * a.block_size : C;
+    sg = choose_segments((long long)H * B, 1, T, align, (long long)B * H, (long long)a.dk * a.dv, a.scratch_bytes, B);
+  }
+  if (sg.n > 1) {
+    if ((r = launch_segment_states(a.q, a.dO, true, a.d_block_states, a.gamma, B, T, H, a.dk, a.dv, a.block_size, a.n_blocks,
+                                   a.state_f32, sg, a.scratch, stream)) != FPB_OK)
+      return r;
+    if ((r = launch_segment_combine(a.scratch, sg, B, T, H, a.dk, a.dv, a.gamma, true, a.d_s_out, a.d_s0, a.state_f32, stream)) != FPB_OK)
+      return r;
+    *n_launched += 2;
+  }
   if ((r = make_seq_map(&p.map_q, q, B, T, H, a.dk, C)) != FPB_OK) return r;
   if ((r = make_seq_map(&p.map_k, k, B, T, H, a.dk, C)) != FPB_OK) return r;
   if ((r = make_seq_map(&p.map_v, v, B, T, H, a.dv, C)) != FPB_OK) return r;
@@ -625,20 +709,27 @@ int launch_bwd_fused(const UmmaBwdArgs& a, cudaStream_t stream) {
   if ((r = make_seq_map(&p.map_dv, dV, B, T, H, a.dv, C)) != FPB_OK) return r;
   p.dk_out = (bf16*)dK.data; p.dk_sb = dK.sb; p.dk_st = dK.st; p.dk_sh = dK.sh;
   p.dv_out = (bf16*)dV.data; p.dv_sb = dV.sb; p.dv_st = dV.st; p.dv_sh = dV.sh;
-  p.g_start = (const bf16*)a.d_s_out.data; p.gs_sb = a.d_s_out.sb; p.gs_sh = a.d_s_out.sh;
-  p.g_end = (bf16*)a.d_s0.data; p.ge_sb = a.d_s0.sb; p.ge_sh = a.d_s0.sh;
-  p.block_grads = (const bf16*)a.d_block_states;
-  p.sfx_blocks = (bf16*)a.sfx_grad.blocks; p.sfx_M = a.sfx_grad.M; p.sfx_N = a.sfx_grad.N; p.sfx_G = G;
+  const bool split = sg.n > 1;
+  p.g_start = split ? nullptr : a.d_s_out.data; p.gs_sb = a.d_s_out.sb; p.gs_sh = a.d_s_out.sh;
+  p.g_end = split ? nullptr : a.d_s0.data; p.ge_sb = a.d_s0.sb; p.ge_sh = a.d_s0.sh;
+  p.block_grads = a.d_block_states;
+  p.sfx_blocks = a.sfx_grad.blocks; p.sfx_M = a.sfx_grad.M; p.sfx_N = a.sfx_grad.N; p.sfx_G = G;
   p.T = T; p.H = H; p.dk = a.dk; p.dv = a.dv; p.block_size = block_size; p.n_blocks = a.n_blocks;
+  p.state_f32 = a.state_f32 ? 1 : 0;
+  p.n_seg = sg.n; p.seg_len = sg.seg_len; p.seg_states = a.scratch;
+  p.tune = walk_tuning();
   p.status = device_status_ptr();
   p.trace = debug_trace_ptr();
   if (!p.status) return FPB_ERR_LAUNCH;
   for (int h = 0; h < H; ++h) p.log2g[h] = (float)std::log2((double)a.gamma[h]);
-  const dim3 grid(1, H, B);
-  if (a.dk == 128 && a.dv == 128) return launch_fused_t<128, 128>(p, grid, stream);
-  if (a.dk == 64 && a.dv == 64) return launch_fused_t<64, 64>(p, grid, stream);
-  if (a.dk == 64 && a.dv == 128) return launch_fused_t<64, 128>(p, grid, stream);
-  return launch_fused_t<128, 64>(p, grid, stream);
+  const dim3 grid(1, H, B * sg.n);
+#define FPB_FUSED_CASE(DK_, DV_) \
+  if (a.dk == DK_ && a.dv == DV_) r = a.state_f32 ? launch_fused_t<DK_, DV_, true>(p, grid, stream) : launch_fused_t<DK_, DV_, false>(p, grid, stream)
+  r = FPB_ERR_BAD_SHAPE;
+  FPB_FUSED_CASE(128, 128); FPB_FUSED_CASE(64, 64); FPB_FUSED_CASE(64, 128); FPB_FUSED_CASE(128, 64);
+#undef FPB_FUSED_CASE
+  if (r == FPB_OK) ++*n_launched;
+  return r;
 }
 
 }  // namespace fpb

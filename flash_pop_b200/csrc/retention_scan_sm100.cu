@@ -43,9 +43,18 @@
 // tile and a 16-row TMA store (tiles wider than 64 columns), or straight from tensor memory to global memory
 // (64-column tiles).  No barrier joins the score warps.
 //
+// Under-filled launches.  When batch x heads x tiles covers less than half of the GPU, the launcher cuts every sequence
+// into T-segments (segment_scan.cu): a STATE_ONLY instance of this kernel computes each segment's local end state
+// (increments only, no scores, no output), a small scan turns those into the segments' start states, and the walk
+// proper then runs one CTA per (batch, head, tile, segment) from its start state in fp32 scratch memory.
+//
 // Suffix calls (thousands of sequences of a few chunks, each starting from its own state and dropping its end
 // state) may be regrouped by the launcher: G consecutive suffixes of a row as one sequence of G*T tokens with block
 // size T, the state replaced at every suffix start - same results, one CTA set-up per G suffixes.
+#include <atomic>
+#include <cmath>
+#include <type_traits>
+
 #include "fpb_common.cuh"
 #include "ptx_sm100.cuh"
 #include "scan_common.cuh"
@@ -67,15 +76,20 @@ constexpr int N_SCORE = 128;
 struct ScanParams {
   CUtensorMap map_x, map_k, map_v, map_out;   // map_out: 16-row boxes
   bf16* out; int64_t out_sb, out_st, out_sh;
-  const bf16* s0; int64_t s0_sb, s0_sh;
-  bf16* s_out; int64_t so_sb, so_sh;
-  bf16* block_states;            // forward walk: states after full blocks (written)
-  const bf16* block_grads;       // reverse walk: gradients of those states (read)
-  bf16* sfx_blocks; int32_t sfx_M, sfx_N;   // suffix calls: start states (forward) / their gradients (reverse)
+  // states are bf16 or fp32 (state_f32), strides in elements
+  const void* s0; int64_t s0_sb, s0_sh;
+  void* s_out; int64_t so_sb, so_sh;
+  void* block_states;            // forward walk: states after full blocks (written)
+  const void* block_grads;       // reverse walk: gradients of those states (read)
+  void* sfx_blocks; int32_t sfx_M, sfx_N;   // suffix calls: start states (forward) / their gradients (reverse)
   int32_t sfx_G;                 // suffixes walked back to back by one CTA as one sequence of sfx_G * block_size tokens (>= 1)
   int32_t T, H, dk, dv, block_size, n_blocks;
   int32_t sched_bs;              // block size the chunk schedule is cut at: block_size, or 0 when block states are
                                  // emitted from inside full chunks (forward walk, 64 x 64 tiles, see EMIT below)
+  int32_t state_f32;             // element type of s0, s_out, block states / gradients and suffix start states
+  int32_t n_seg, seg_len;        // T-segments: blockIdx.z = batch * n_seg + segment, segment s covers tokens [s * seg_len, ...)
+  float* seg_states;             // fp32 (B, H, n_seg, dk, dv): start values of the segments (local end values in a STATE_ONLY pass)
+  WalkTuning tune;
   int32_t* status;
   long long* trace;              // diagnostics: per-chunk clock64() stamps of CTA (0,0,0), or null
   float log2g[FPB_MAX_HEADS];
@@ -84,7 +98,8 @@ struct ScanParams {
 // barrier slots (8 bytes each) at the start of the barrier page, then two 4-byte words
 enum { B_FULL = 0, B_EMPTY = 3, B_VRDY = 6, B_SCFULL = 9, B_PRDY = 11, B_ACCFULL = 13, B_ACCFREE = 15, B_DSFULL = 17,
        B_DSFREE = 19, B_SBRDY = 21, B_SBFREE = 22, B_DSPFULL = 23, B_DSPFREE = 24, B_COUNT = 25 };
-constexpr int OFF_TMEM_SLOT = B_COUNT * 8, OFF_ABORT = OFF_TMEM_SLOT + 4, BAR_PAGE = 256;
+constexpr int OFF_TMEM_SLOT = B_COUNT * 8, OFF_ABORT = OFF_TMEM_SLOT + 4, OFF_LIMIT = OFF_ABORT + 4, BAR_PAGE = 256;
+static_assert(OFF_LIMIT % 8 == 0 && OFF_LIMIT + 8 <= BAR_PAGE, "the wait limit sits right after the abort flag");
 
 template <int MODE, int R, int CC>
 struct Cfg {
@@ -138,7 +153,10 @@ struct Cfg {
   static constexpr int NS = R == 128 ? WCOLS : WCOLS / 2;
 };
 
-template <int MODE, int REV, int R, int CC>
+// SO ("state only"): the walk computes nothing but the state recurrence from a zero start and leaves its end value, fp32,
+// in p.seg_states - the first pass of a T-segmented call.
+// SF32: the call's state tensors (start / end state, block states and their gradients, suffix start states) are fp32.
+template <int MODE, int REV, int R, int CC, bool SO, bool SF32>
 __global__ void __launch_bounds__(Cfg<MODE, R, CC>::NTHREADS, Cfg<MODE, R, CC>::MIN_CTAS)
 scan_kernel(const __grid_constant__ ScanParams p) {
   using G = Cfg<MODE, R, CC>;
@@ -152,12 +170,17 @@ scan_kernel(const __grid_constant__ ScanParams p) {
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + G::OFF_BAR + OFF_TMEM_SLOT);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int tile = blockIdx.x, h = blockIdx.y;
+  const int b = p.n_seg > 1 ? (int)blockIdx.z / p.n_seg : (int)blockIdx.z;
+  const int seg = p.n_seg > 1 ? (int)blockIdx.z % p.n_seg : 0;
+  // this CTA walks tokens [t0, t_end) of the sequence; chunk positions are absolute (t0 is a chunk and block multiple)
+  const int t0 = seg * p.seg_len;
+  const int t_end = p.n_seg > 1 ? min(t0 + p.seg_len, p.T) : p.T;
   const int row0 = MODE == MODE_FWD ? 0 : tile * R;     // state rows [row0, row0+R) of dk
   const int col0 = MODE == MODE_FWD ? tile * CC : 0;    // state cols [col0, col0+CC) of dv
   const float lg = p.log2g[h];
   const float rs = rsqrtf((float)p.dk);
-  const int NC = chunk_count(p.T, p.sched_bs);
+  const int NC = chunk_count(t_end - t0, p.sched_bs);
   auto bar = [&](int slot) { return sbase + G::OFF_BAR + slot * 8; };
   auto stage_of = [&](int n) { return n % G::STAGES; };
   auto stage_ph = [&](int n) { return (uint32_t)((n / G::STAGES) & 1); };
@@ -177,6 +200,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
     mbar_init(bar(B_DSPFULL), 1); mbar_init(bar(B_DSPFREE), G::N_STATE);
     fence_mbar_init();
     *abort_flag = 0;
+    *reinterpret_cast<volatile long long*>(sm + G::OFF_BAR + OFF_LIMIT) = p.tune.wait_cycles;
     prefetch_tmap(&p.map_x); prefetch_tmap(&p.map_k); prefetch_tmap(&p.map_v); prefetch_tmap(&p.map_out);
   }
   if (warp == 1) { tmem_alloc(sbase + G::OFF_BAR + OFF_TMEM_SLOT, G::TM_COLS); tmem_relinquish(); }
@@ -189,12 +213,12 @@ scan_kernel(const __grid_constant__ ScanParams p) {
   // it, or 0 when there is none (block sizes above 64 are the only ones walked this way: at most one per chunk)
   const bool emit = G::EMIT && !REV && p.sched_bs == 0 && p.block_size > 0 && p.block_states != nullptr;
   auto mid_end = [&](int n) {
-    const int a = n * C, L = min(C, p.T - a);
+    const int a = t0 + n * C, L = min(C, t_end - a);
     const int e = (a / p.block_size + 1) * p.block_size;
     return (e < a + L && e / p.block_size - 1 < p.n_blocks) ? e - a : 0;
   };
-  Chunk first{REV ? p.T : 0, 0};
-  advance<REV>(first, p.T, p.sched_bs);
+  Chunk first{REV ? t_end : t0, 0};
+  advance<REV>(first, t_end, p.sched_bs);
 
   // =============================================================================================
   if (warp == 0) {                                   // ---------------- TMA producer
@@ -205,22 +229,26 @@ scan_kernel(const __grid_constant__ ScanParams p) {
         const int s = stage_of(c);
         if (!mbar_wait(bar(B_EMPTY + s), stage_ph(c) ^ 1, abort_flag)) { FPB_GIVE_UP(0x100 | B_EMPTY); break; }
         FPB_TRACE(14, c);
+        if (c == p.tune.withhold_chunk) { advance<REV>(ck, t_end, p.sched_bs); continue; }   // diagnostics: this chunk never arrives
         const uint32_t st = sbase + G::OFF_STAGE + s * G::STAGE_BYTES;
-        mbar_arrive_expect_tx(bar(B_FULL + s), G::STAGE_BYTES);
+        mbar_arrive_expect_tx(bar(B_FULL + s), SO ? G::K_BYTES + G::V_BYTES : G::STAGE_BYTES);
         const int xcol0 = MODE == MODE_FWD ? row0 : col0;
+        if (!SO) {
 #pragma unroll
-        for (int cb = 0; cb < G::W1 / 64; ++cb) tma_load_4d(st + cb * 8192, &p.map_x, bar(B_FULL + s), xcol0 + cb * 64, ck.a, h, b);
+          for (int cb = 0; cb < G::W1 / 64; ++cb) tma_load_4d(st + cb * 8192, &p.map_x, bar(B_FULL + s), xcol0 + cb * 64, ck.a, h, b);
+        }
 #pragma unroll
         for (int cb = 0; cb < R / 64; ++cb) tma_load_4d(st + G::X_BYTES + cb * 8192, &p.map_k, bar(B_FULL + s), row0 + cb * 64, ck.a, h, b);
 #pragma unroll
         for (int cb = 0; cb < CC / 64; ++cb) tma_load_4d(st + G::X_BYTES + G::K_BYTES + cb * 8192, &p.map_v, bar(B_FULL + s), col0 + cb * 64, ck.a, h, b);
         ++issued;
-        advance<REV>(ck, p.T, p.sched_bs);
+        advance<REV>(ck, t_end, p.sched_bs);
       }
       if (*abort_flag) {   // let the copies in flight land before the CTA's shared memory is released
-        for (int i = max(0, issued - G::STAGES); i < issued; ++i) {
-          const long long t0 = clock64();
-          while (!mbar_try_wait(bar(B_FULL + stage_of(i)), stage_ph(i)) && clock64() - t0 < kWaitCycles) {}
+        // (with a withheld chunk the stage numbering of the last copies is off by one: those were consumed anyway)
+        for (int i = max(0, issued - G::STAGES); i < issued && p.tune.withhold_chunk < 0; ++i) {
+          const long long w0 = clock64();
+          while (!mbar_try_wait(bar(B_FULL + stage_of(i)), stage_ph(i)) && clock64() - w0 < wait_limit(abort_flag)) {}
         }
       }
     }
@@ -252,11 +280,11 @@ scan_kernel(const __grid_constant__ ScanParams p) {
       // Next chunk to issue for each of the four products, and the next stage to hand back to the producer.
       // Each product of chunk n is issued when its inputs are there; the tensor pipe runs them in issue order.
       int n_sc = 0, n_ds = 0, n_qs = 0, n_pv = 0, n_rel = 0;
-      int n_dsp = emit ? 0 : 0x7fffffff, m_dsp = 0;   // chunks whose partial increment is settled; partials issued
+      int n_dsp = (emit && !SO) ? 0 : 0x7fffffff, m_dsp = 0;   // chunks whose partial increment is settled; partials issued
       // a stage goes back to the producer as soon as all four products of its chunk have been issued (issuing
       // blocks while the tensor pipe is busy, so this is checked after every group, not once per round)
       auto release = [&]() {
-        while (n_rel < n_pv && n_rel < n_ds && n_rel < n_sc && n_rel < n_dsp) {
+        while ((SO || (n_rel < n_pv && n_rel < n_sc)) && n_rel < n_ds && n_rel < n_dsp) {
           if (leader) { umma_commit(bar(B_EMPTY + stage_of(n_rel))); FPB_TRACE(5, n_rel); }
           ++n_rel;
         }
@@ -265,12 +293,22 @@ scan_kernel(const __grid_constant__ ScanParams p) {
       // operands out of shared memory, so each barrier phase is tested until it has been seen complete once and
       // never again.  "V scaled" implies "tiles landed" (the state warps waited for them), so the products wait
       // for that one barrier only.
-      int n_data = 0;
+      int n_data = 0, n_full = 0;
       auto data_ready = [&](int n) {
         if (n < n_data) return true;
         if (!ready(B_VRDY + stage_of(n_data), stage_ph(n_data))) return false;
         ++n_data;
         return n < n_data;
+      };
+      // The scores of a MODE_FWD walk read X and K only, not the tile the state warps rescale in place: they may go
+      // as soon as the copies have landed, so that the chain scores -> P' -> intra-chunk term starts a rescaling early.
+      auto scores_ready = [&](int n) {
+        if (MODE != MODE_FWD || !p.tune.sc_early) return data_ready(n);
+        if (n < n_data || n < n_full) return true;
+        if (n_full < n_data) n_full = n_data;
+        if (!ready(B_FULL + stage_of(n_full), stage_ph(n_full))) return false;
+        ++n_full;
+        return n < n_full;
       };
       Patience patience{0, 0};
       while (n_rel < NC) {             // until every product of every chunk has been issued
@@ -279,7 +317,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
         // increment -> state -> next chunk's state term).
         // scores Sc = X K^T (FWD) | X Veta^T (DQ); its buffer is free once P' of chunk n - NSC has been taken out,
         // which the intra-chunk term of that chunk has waited for
-        if (n_sc < NC && n_sc < n_pv + G::NSC && data_ready(n_sc)) {
+        if (!SO && n_sc < NC && n_sc < n_pv + G::NSC && scores_ready(n_sc)) {
           const uint64_t so = (uint64_t)(stage_of(n_sc) * STAGE16);
           tc_fence_after();
           const uint32_t d = tm + tm_sc(n_sc);
@@ -306,7 +344,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
           release();
         }
         // EMIT: partial increment of the chunk whose full increment has just been issued (same operands, first k-steps)
-        if (G::EMIT && n_dsp < n_ds) {
+        if (G::EMIT && !SO && n_dsp < n_ds) {
           const int pmid = mid_end(n_dsp);
           if (pmid == 0) { ++n_dsp; progress = true; release(); }
           else if (m_dsp == 0 || ready(B_DSPFREE, (m_dsp - 1) & 1)) {
@@ -321,7 +359,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
           }
         }
         // state term: ACC = X Sb (FWD) | X Sb^T (DQ)
-        if (n_qs < NC && data_ready(n_qs) && (n_qs < G::NACC || ready(B_ACCFREE + n_qs % G::NACC, ((n_qs / G::NACC) & 1) ^ 1)) &&
+        if (!SO && n_qs < NC && data_ready(n_qs) && (n_qs < G::NACC || ready(B_ACCFREE + n_qs % G::NACC, ((n_qs / G::NACC) & 1) ^ 1)) &&
             ready(B_SBRDY, n_qs & 1)) {
           const uint64_t so = (uint64_t)(stage_of(n_qs) * STAGE16);
           if (leader) FPB_TRACE(2, n_qs);
@@ -341,7 +379,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
           ++n_qs; progress = true;
         }
         // intra-chunk term: ACC += P' Veta (FWD) | P' K (DQ); needs the state term of the same chunk issued before
-        if (n_pv < n_qs && ready(B_PRDY + n_pv % G::NP, (n_pv / G::NP) & 1)) {   // the state term has seen the data
+        if (!SO && n_pv < n_qs && ready(B_PRDY + n_pv % G::NP, (n_pv / G::NP) & 1)) {   // the state term has seen the data
           const uint64_t so = (uint64_t)(stage_of(n_pv) * STAGE16);
           if (leader) FPB_TRACE(15, n_pv);
           tc_fence_after();
@@ -422,7 +460,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
           *reinterpret_cast<uint32_t*>(stg + half * 8192 + (r_lo + 8) * 128 + ((g ^ ((r_lo + 8) & 7)) << 4) + cpair * 2) = hi;
         }
       }
-      const bool whole_box = ck.L == C || ck.a + ck.L >= p.T;   // rows beyond L are past the sequence end: TMA clips them
+      const bool whole_box = ck.L == C || ck.a + ck.L >= p.T;    // rows beyond L are past the sequence end: TMA clips them
       const int wrow0 = q4 * 16;                                // this warp's rows [wrow0, wrow0 + 16)
       const int ocol0 = MODE == MODE_FWD ? col0 : row0;
       if (whole_box) {
@@ -480,7 +518,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
       if (t == 0) FPB_TRACE(10, n);
     };
 
-    if (NC > 0) {
+    if (NC > 0 && !SO) {
       // P' may run ahead of the epilogues by the number of P' buffers: buffer n % NP is free again once the
       // intra-chunk product of chunk n - NP has run, which epilogue n - NP has waited for
       int n_p = 0, n_e = 0, n_acc = 0;      // n_acc: chunks whose accumulator this thread has seen complete
@@ -497,12 +535,12 @@ scan_kernel(const __grid_constant__ ScanParams p) {
         if (n_p < NC && n_p < n_acc + G::NP && mbar_test_wait(bar(B_SCFULL + n_p % G::NSC), (n_p / G::NSC) & 1)) {
           if (t == 0) FPB_TRACE(6, n_p);
           make_p(n_p, ck_p.L);
-          ++n_p; advance<REV>(ck_p, p.T, p.sched_bs);
+          ++n_p; advance<REV>(ck_p, t_end, p.sched_bs);
           patience.progress();
         } else if (n_e < n_acc) {
           if (G::DIRECT_OUT) epilogue_direct(n_e, ck_e);
           else epilogue(n_e, ck_e);
-          ++n_e; advance<REV>(ck_e, p.T, p.sched_bs);
+          ++n_e; advance<REV>(ck_e, t_end, p.sched_bs);
           patience.progress();
         } else if (patience.exhausted(abort_flag)) {
           FPB_GIVE_UP(0x300 | (n_e & 0xff));
@@ -511,8 +549,8 @@ scan_kernel(const __grid_constant__ ScanParams p) {
           // idle: sleep in hardware on the barrier most likely to complete next (leaves the issue slots to the
           // warps that have work, wakes at once when that barrier completes)
           const bool want_p = n_p < NC && n_p < n_acc + G::NP;
-          if (want_p) mbar_try_wait_hint(bar(B_SCFULL + n_p % G::NSC), (n_p / G::NSC) & 1, 200);
-          else mbar_try_wait_hint(bar(B_ACCFULL + n_acc % G::NACC), (n_acc / G::NACC) & 1, 200);
+          if (want_p) mbar_try_wait_hint(bar(B_SCFULL + n_p % G::NSC), (n_p / G::NSC) & 1, p.tune.idle_ns);
+          else mbar_try_wait_hint(bar(B_ACCFULL + n_acc % G::NACC), (n_acc / G::NACC) & 1, p.tune.idle_ns);
         }
       }
       if (!G::DIRECT_OUT && lane == 0) tma_store_wait_all0();
@@ -537,26 +575,57 @@ scan_kernel(const __grid_constant__ ScanParams p) {
     // suffix call, batch index = (row, m): suffix m of a row starts from s0[row] (m == 0) or from block
     // state m-1, its end state is dropped (zero gradient), and the reverse walk's end goes to the
     // gradient of that start state.
-    const bf16* x_start = nullptr;
-    bf16* x_end = nullptr;
+    // (the call's states are bf16 or fp32: SF32; the segment scratch is always fp32)
+    const void* x_start = nullptr;
+    void* x_end = nullptr;
+    constexpr std::bool_constant<SF32> state_t{};
+    constexpr std::true_type scratch_t{};
+    constexpr int esz = SF32 ? 4 : 2;
+    auto at = [&](const void* base, int64_t elems) { return (void*)((const char*)base + elems * esz); };
     // suffix calls: the batch index is (row, group of sfx_G consecutive suffixes)
     const int groups = p.sfx_M > 0 ? p.sfx_M / p.sfx_G : 1;
     const int sfx_row = b / groups, sfx_m0 = (b % groups) * p.sfx_G;
-    auto sfx_start = [&](int m) -> const bf16* {       // where suffix m of this row starts from (forward walks)
-      if (m == 0) return p.s0 ? p.s0 + sfx_row * p.s0_sb + h * p.s0_sh : nullptr;
-      return p.sfx_blocks ? p.sfx_blocks + (((int64_t)sfx_row * p.sfx_N + (m - 1)) * p.H + h) * state_elems : nullptr;
+    auto sfx_start = [&](int m) -> const void* {       // where suffix m of this row starts from (forward walks)
+      if (m == 0) return p.s0 ? at(p.s0, sfx_row * p.s0_sb + h * p.s0_sh) : nullptr;
+      return p.sfx_blocks ? at(p.sfx_blocks, (((int64_t)sfx_row * p.sfx_N + (m - 1)) * p.H + h) * state_elems) : nullptr;
     };
-    if (p.sfx_M > 0) {
+    if (SO || p.n_seg > 1) {
+      // T-segments: a STATE_ONLY pass leaves the local end value in this segment's scratch slot; the walk proper
+      // starts from the value the scan put there and writes no end state (the scan did)
+      float* slot = p.seg_states + (((int64_t)b * p.H + h) * p.n_seg + seg) * state_elems;
+      if (SO) x_end = slot;
+      else x_start = slot;
+    } else if (p.sfx_M > 0) {
       const int row = sfx_row, m = sfx_m0;
-      bf16* blk = (m > 0 && p.sfx_blocks) ? p.sfx_blocks + (((int64_t)row * p.sfx_N + (m - 1)) * p.H + h) * state_elems : nullptr;
+      void* blk = (m > 0 && p.sfx_blocks) ? at(p.sfx_blocks, (((int64_t)row * p.sfx_N + (m - 1)) * p.H + h) * state_elems) : nullptr;
       if (!REV) x_start = sfx_start(m);
-      else x_end = m == 0 ? (p.s_out ? p.s_out + row * p.so_sb + h * p.so_sh : nullptr) : blk;
+      else x_end = m == 0 ? (p.s_out ? at(p.s_out, row * p.so_sb + h * p.so_sh) : nullptr) : blk;
     } else {
-      if (p.s0) x_start = p.s0 + b * p.s0_sb + h * p.s0_sh;
-      if (p.s_out) x_end = p.s_out + b * p.so_sb + h * p.so_sh;
+      if (p.s0) x_start = at(p.s0, b * p.s0_sb + h * p.s0_sh);
+      if (p.s_out) x_end = at(p.s_out, b * p.so_sb + h * p.so_sh);
     }
 
-    auto load_global = [&](const bf16* src, bool accumulate) {
+    auto load_global = [&](const void* src_, auto f32, bool accumulate) {
+      if constexpr (decltype(f32)::value) {
+        const float* src = (const float*)src_;
+        if (R == 128) {
+          const float* rowp = src + (int64_t)(row0 + row_of(0)) * p.dv + col0 + wcol0;
+#pragma unroll
+          for (int i = 0; i < G::NS; i += 4) {
+            const float4 val = *reinterpret_cast<const float4*>(rowp + i);
+            S[i] = (accumulate ? S[i] : 0.f) + val.x; S[i + 1] = (accumulate ? S[i + 1] : 0.f) + val.y;
+            S[i + 2] = (accumulate ? S[i + 2] : 0.f) + val.z; S[i + 3] = (accumulate ? S[i + 3] : 0.f) + val.w;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < G::NS; i += 2) {
+            const float2 f = *reinterpret_cast<const float2*>(src + (int64_t)(row0 + row_of(i)) * p.dv + col0 + col_of(i));
+            S[i] = (accumulate ? S[i] : 0.f) + f.x;
+            S[i + 1] = (accumulate ? S[i + 1] : 0.f) + f.y;
+          }
+        }
+      } else {
+      const bf16* src = (const bf16*)src_;
       if (R == 128) {
         const bf16* rowp = src + (int64_t)(row0 + row_of(0)) * p.dv + col0 + wcol0;
 #pragma unroll
@@ -579,13 +648,28 @@ scan_kernel(const __grid_constant__ ScanParams p) {
           S[i + 1] = (accumulate ? S[i + 1] : 0.f) + f.y;
         }
       }
+      }
     };
     // reverse walks: add the gradient of block state n where block n ends (chunk end == (n+1) * block_size)
     auto inject = [&](int end) {
       if (REV && p.block_size > 0 && p.block_grads && end % p.block_size == 0 && end / p.block_size - 1 < p.n_blocks)
-        load_global(p.block_grads + (((int64_t)b * p.n_blocks + (end / p.block_size - 1)) * p.H + h) * state_elems, true);
+        load_global(at(p.block_grads, (((int64_t)b * p.n_blocks + (end / p.block_size - 1)) * p.H + h) * state_elems),
+                    state_t, true);
     };
-    auto store_global = [&](bf16* dst) {
+    auto store_global = [&](void* dst_, auto f32) {
+      if constexpr (decltype(f32)::value) {
+        float* dst = (float*)dst_;
+        if (R == 128) {
+          float* rowp = dst + (int64_t)(row0 + row_of(0)) * p.dv + col0 + wcol0;
+#pragma unroll
+          for (int i = 0; i < G::NS; i += 4) *reinterpret_cast<float4*>(rowp + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < G::NS; i += 2)
+            *reinterpret_cast<float2*>(dst + (int64_t)(row0 + row_of(i)) * p.dv + col0 + col_of(i)) = make_float2(S[i], S[i + 1]);
+        }
+      } else {
+      bf16* dst = (bf16*)dst_;
       if (R == 128) {
         bf16* rowp = dst + (int64_t)(row0 + row_of(0)) * p.dv + col0 + wcol0;
 #pragma unroll
@@ -599,6 +683,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
 #pragma unroll
         for (int i = 0; i < G::NS; i += 2)
           *reinterpret_cast<uint32_t*>(dst + (int64_t)(row0 + row_of(i)) * p.dv + col0 + col_of(i)) = pack_bf16(S[i], S[i + 1]);
+      }
       }
     };
     // bf16 copy of the state in shared memory: [CC/64 column blocks][R rows][128 bytes], 16-byte
@@ -651,7 +736,10 @@ scan_kernel(const __grid_constant__ ScanParams p) {
       mbar_arrive(bar(B_VRDY + s));
     };
 
-    if (x_start) load_global(x_start, false);
+    if (x_start) {
+      if (!SO && p.n_seg > 1) load_global(x_start, scratch_t, false);
+      else load_global(x_start, state_t, false);
+    }
     else {
 #pragma unroll
       for (int i = 0; i < G::NS; ++i) S[i] = 0.f;
@@ -664,7 +752,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
       //   Sb(n) publish the bf16 copy of the state at the start of chunk n; it must happen between U(n-1) and U(n),
       //         and after the state-term product of chunk n-1 has finished reading the previous copy
       int n_v = 0, n_u = 0, m_part = 0;
-      bool publish_due = true, partial_due = emit && mid_end(0) > 0;   // partial_due: chunk n_u has a block end inside
+      bool publish_due = !SO, partial_due = emit && !SO && mid_end(0) > 0;   // partial_due: chunk n_u has a block end inside
       Chunk ck_v = first, ck_u = first;
       inject(first.a + first.L);
       Patience patience{0, 0};
@@ -673,7 +761,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
         if (n_v < NC && mbar_test_wait(bar(B_FULL + stage_of(n_v)), stage_ph(n_v))) {
           scale_v(n_v, ck_v.L);
           if (t == 0) FPB_TRACE(11, n_v);
-          ++n_v; advance<REV>(ck_v, p.T, p.sched_bs);
+          ++n_v; advance<REV>(ck_v, t_end, p.sched_bs);
           progress = true;
         }
         if (publish_due) {
@@ -687,16 +775,19 @@ scan_kernel(const __grid_constant__ ScanParams p) {
             tc_fence_after();
             const int pmid = mid_end(n_u);
             const float gp = exp2f((float)pmid * lg), up = exp2f(-(float)(ck_u.L - pmid) * lg) * rs;
-            bf16* dst = p.block_states + (((int64_t)b * p.n_blocks + ((ck_u.a + pmid) / p.block_size - 1)) * p.H + h) * state_elems;
+            void* dst_ = at(p.block_states, (((int64_t)b * p.n_blocks + ((ck_u.a + pmid) / p.block_size - 1)) * p.H + h) * state_elems);
 #pragma unroll
             for (int i0 = 0; i0 < G::NS; i0 += 16) {
               uint32_t r[16];
               tmem_ld_16x256b_x4(tm + lane_base + G::TM_DSP + wcol0 + i0 * 2, r);
               tmem_wait_ld();
 #pragma unroll
-              for (int i = 0; i < 16; i += 2)
-                *reinterpret_cast<uint32_t*>(dst + (int64_t)(row0 + row_of(i0 + i)) * p.dv + col0 + col_of(i0 + i)) =
-                    pack_bf16(fmaf(gp, S[i0 + i], up * __uint_as_float(r[i])), fmaf(gp, S[i0 + i + 1], up * __uint_as_float(r[i + 1])));
+              for (int i = 0; i < 16; i += 2) {
+                const float lo = fmaf(gp, S[i0 + i], up * __uint_as_float(r[i])), hi = fmaf(gp, S[i0 + i + 1], up * __uint_as_float(r[i + 1]));
+                const int64_t off = (int64_t)(row0 + row_of(i0 + i)) * p.dv + col0 + col_of(i0 + i);
+                if (SF32) *reinterpret_cast<float2*>((float*)dst_ + off) = make_float2(lo, hi);
+                else *reinterpret_cast<uint32_t*>((bf16*)dst_ + off) = pack_bf16(lo, hi);
+              }
             }
             tc_fence_before();
             mbar_arrive(bar(B_DSPFREE));
@@ -719,34 +810,37 @@ scan_kernel(const __grid_constant__ ScanParams p) {
           tc_fence_before();
           mbar_arrive(bar(B_DSFREE + (n_u & 1)));   // the increment has been read: the one after next may overwrite it
           const int end = ck_u.a + ck_u.L;
-          if (!REV && p.block_size > 0 && p.block_states && end % p.block_size == 0 && end / p.block_size - 1 < p.n_blocks)
-            store_global(p.block_states + (((int64_t)b * p.n_blocks + (end / p.block_size - 1)) * p.H + h) * state_elems);
+          if (!REV && !SO && p.block_size > 0 && p.block_states && end % p.block_size == 0 && end / p.block_size - 1 < p.n_blocks)
+            store_global(at(p.block_states, (((int64_t)b * p.n_blocks + (end / p.block_size - 1)) * p.H + h) * state_elems), state_t);
           ++n_u;
           if (n_u < NC) {
-            advance<REV>(ck_u, p.T, p.sched_bs);
-            if (!REV && p.sfx_G > 1 && ck_u.a % p.block_size == 0) {
+            advance<REV>(ck_u, t_end, p.sched_bs);
+            if (!REV && !SO && p.sfx_G > 1 && ck_u.a % p.block_size == 0) {
               // grouped suffixes: the next chunk opens the next suffix, which starts from its own state
-              const bf16* src = sfx_start(sfx_m0 + ck_u.a / p.block_size);
-              if (src) load_global(src, false);
+              const void* src = sfx_start(sfx_m0 + ck_u.a / p.block_size);
+              if (src) load_global(src, state_t, false);
               else {
 #pragma unroll
                 for (int i = 0; i < G::NS; ++i) S[i] = 0.f;
               }
             }
             inject(ck_u.a + ck_u.L);
-            publish_due = true;
-            partial_due = emit && mid_end(n_u) > 0;
+            publish_due = !SO;
+            partial_due = emit && !SO && mid_end(n_u) > 0;
           }
           progress = true;
         }
         if (progress) patience.progress();
         else if (patience.exhausted(abort_flag)) { FPB_GIVE_UP(0x400 | (n_u & 0xff)); break; }
-        else if (publish_due) mbar_try_wait_hint(bar(B_SBFREE), (n_u - 1) & 1, 200);   // idle: sleep on the likely next
-        else if (G::EMIT && partial_due) mbar_try_wait_hint(bar(B_DSPFULL), m_part & 1, 200);
-        else mbar_try_wait_hint(bar(B_DSFULL + (n_u & 1)), (n_u >> 1) & 1, 200);
+        else if (publish_due) mbar_try_wait_hint(bar(B_SBFREE), (n_u - 1) & 1, p.tune.idle_ns);   // idle: sleep on the likely next
+        else if (G::EMIT && partial_due) mbar_try_wait_hint(bar(B_DSPFULL), m_part & 1, p.tune.idle_ns);
+        else mbar_try_wait_hint(bar(B_DSFULL + (n_u & 1)), (n_u >> 1) & 1, p.tune.idle_ns);
       }
     }
-    if (x_end && !*abort_flag) store_global(x_end);
+    if (x_end && !*abort_flag) {
+      if (SO) store_global(x_end, scratch_t);
+      else store_global(x_end, state_t);
+    }
   }
 
   // ---------------- teardown
@@ -755,37 +849,64 @@ scan_kernel(const __grid_constant__ ScanParams p) {
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tm, G::TM_COLS); }
 }
 
-template <int MODE, int REV, int R, int CC>
+template <int MODE, int REV, int R, int CC, bool SO, bool SF32>
 int launch_scan_t(const ScanParams& p, dim3 grid, cudaStream_t stream) {
   using G = Cfg<MODE, R, CC>;
-  static bool configured[64] = {};
+  static std::atomic<bool> configured[64];
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64 || !configured[dev]) {
-    if (cudaFuncSetAttribute(scan_kernel<MODE, REV, R, CC>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM) != cudaSuccess)
+  if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
+    if (cudaFuncSetAttribute(scan_kernel<MODE, REV, R, CC, SO, SF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM) != cudaSuccess)
       return FPB_ERR_LAUNCH;
-    if (dev >= 0 && dev < 64) configured[dev] = true;
+    if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
   }
-  scan_kernel<MODE, REV, R, CC><<<grid, G::NTHREADS, G::SMEM, stream>>>(p);
+  scan_kernel<MODE, REV, R, CC, SO, SF32><<<grid, G::NTHREADS, G::SMEM, stream>>>(p);
   return FPB_OK;
 }
 template <int MODE, int R, int CC>
-int launch_scan(const ScanParams& p, bool rev, dim3 grid, cudaStream_t stream) {
-  return rev ? launch_scan_t<MODE, 1, R, CC>(p, grid, stream) : launch_scan_t<MODE, 0, R, CC>(p, grid, stream);
+int launch_scan(const ScanParams& p, bool rev, bool state_only, dim3 grid, cudaStream_t stream) {
+  const bool f32 = p.state_f32 != 0;
+  if constexpr (MODE == MODE_FWD) {   // the state-only pass exists for the tilings of the output walks
+    // (a state-only pass starts from zero and ends in fp32 scratch; only the block gradients of a reverse POP walk are typed)
+    if (state_only) {
+      if (!rev) return launch_scan_t<MODE, 0, R, CC, true, false>(p, grid, stream);
+      return f32 ? launch_scan_t<MODE, 1, R, CC, true, true>(p, grid, stream) : launch_scan_t<MODE, 1, R, CC, true, false>(p, grid, stream);
+    }
+  }
+  if (state_only) return FPB_ERR_BAD_SHAPE;
+  if (f32) return rev ? launch_scan_t<MODE, 1, R, CC, false, true>(p, grid, stream) : launch_scan_t<MODE, 0, R, CC, false, true>(p, grid, stream);
+  return rev ? launch_scan_t<MODE, 1, R, CC, false, false>(p, grid, stream) : launch_scan_t<MODE, 0, R, CC, false, false>(p, grid, stream);
 }
 
-int g_tile_pref = 1;            // 1: 128x128 state tiles where they apply; 0: 64-wide tiles (two CTAs per SM)
-int g_sfx_group = 16;           // most suffixes one CTA walks back to back (1: one CTA per suffix)
-int g_sfx_min_ctas = 3 * 296;   // ... as long as that many CTAs remain (three waves of two CTAs per SM)
-int g_pop_emit = 1;             // 1: POP forward walks over full chunks where block states can come from partial increments
-int g_fused_bwd = 1;            // 1: dK, dV, dS_0 in one fused reverse walk where it applies; 0: two separate walks
-long long* g_trace = nullptr;   // set by fpb_debug_trace
+// Scheduling choices.  A release build fixes them; the diagnostics build (-DFPB_DIAGNOSTICS) exports setters so that
+// tests can run the alternative schedules against each other.
+#ifdef FPB_DIAGNOSTICS
+#define FPB_KNOB int
+#else
+#define FPB_KNOB constexpr int
+#endif
+FPB_KNOB g_tile_pref = 1;            // 1: 128x128 state tiles where they apply; 0: 64-wide tiles (two CTAs per SM)
+FPB_KNOB g_sfx_group = 16;           // most suffixes one CTA walks back to back (1: one CTA per suffix)
+FPB_KNOB g_sfx_min_ctas = 3 * 296;   // ... as long as that many CTAs remain (three waves of two CTAs per SM)
+FPB_KNOB g_pop_emit = 1;             // 1: POP forward walks over full chunks where block states can come from partial increments
+FPB_KNOB g_fused_bwd = 1;            // 1: dK, dV, dS_0 in one fused reverse walk where it applies; 0: two separate walks
+FPB_KNOB g_segments = 1;             // 1: under-filled launches are cut into T-segments when the caller gave scratch memory
+#ifdef FPB_DIAGNOSTICS
+long long* g_trace = nullptr;        // set by fpb_debug_trace
+WalkTuning g_tuning{kWaitCycles, 200, 1, -1};
+#else
+constexpr long long* g_trace = nullptr;
+constexpr WalkTuning g_tuning{kWaitCycles, 200, 1, -1};
+#endif
 
-bool aligned_state(const StateView& s) { return !s.data || ((uintptr_t)s.data % 16 == 0 && s.sb % 8 == 0 && s.sh % 8 == 0); }
+bool aligned_state(const StateView& s, bool f32) {
+  const int64_t m = f32 ? 4 : 8;
+  return !s.data || ((uintptr_t)s.data % 16 == 0 && s.sb % m == 0 && s.sh % m == 0);
+}
 
 // Which (mode, dk, dv) combinations the kernel is instantiated for.
 bool scan_supported(int mode, int dk, int dv) {
-  if (mode == MODE_FWD) return (dk == 64 || dk == 128) && (dv == 64 || dv == 128 || dv == 256);
+  (void)mode;
   return (dk == 64 || dk == 128) && (dv == 64 || dv == 128 || dv == 256);
 }
 
@@ -797,18 +918,38 @@ struct PassArgs {
   SuffixStates sfx;
   const float* gamma;
   int B, T, H, dk, dv, block_size, n_blocks;
+  bool state_f32;
+  float* scratch; int64_t scratch_bytes;   // fp32 scratch for T-segments, or null
 };
 
 bool pass_applicable(const PassArgs& a) {
   if (!scan_supported(a.mode, a.dk, a.dv)) return false;
   if (!tma_addressable(a.x, 2) || !tma_addressable(a.k, 2) || !tma_addressable(a.v, 2) || !tma_addressable(a.out, 2)) return false;
-  if (!aligned_state(a.start) || !aligned_state(a.end)) return false;
+  if (!aligned_state(a.start, a.state_f32) || !aligned_state(a.end, a.state_f32)) return false;
   if ((uintptr_t)a.block_states % 16 || (uintptr_t)a.block_grads % 16 || (uintptr_t)a.sfx.blocks % 16) return false;
   return a.B <= 65535 && a.H <= 65535 && a.T > 0;
 }
 
-int launch_pass(const PassArgs& a, cudaStream_t stream) {
-  const int xw = a.mode == MODE_FWD ? a.dk : a.dv, ow = a.mode == MODE_FWD ? a.dv : a.dk;
+// state tile and CTAs per SM of the instance a pass runs on
+struct Tiling { int R, CC, tiles, ctas_per_sm; };
+Tiling tiling_of(int mode, int dk, int dv) {
+  if (mode == MODE_FWD) {         // state tile: all dk rows x CC columns of dv
+    if (dk == 128 && dv % 128 == 0 && g_tile_pref) return {128, 128, dv / 128, 1};
+    if (dk == 128) return {128, 64, dv / 64, 2};
+    return {64, 64, dv / 64, 2};
+  }                               // state tile: R rows of dk x all dv columns
+  if (dv == 128 && dk % 128 == 0 && g_tile_pref) return {128, 128, dk / 128, 1};
+  if (dv == 64) return {64, 64, dk / 64, 2};
+  if (dv == 128) return {64, 128, dk / 64, 2};
+  return {64, 256, dk / 64, 1};
+}
+
+int gcd_int(int a, int b) { while (b) { const int t = a % b; a = b; b = t; } return a; }
+
+// One launch of the kernel: the walk itself, or (state_only) the local end values of its T-segments.
+int launch_one(const PassArgs& a, Segments sg, bool state_only, cudaStream_t stream) {
+  const int mode = state_only ? MODE_FWD : a.mode;
+  const int xw = mode == MODE_FWD ? a.dk : a.dv, ow = mode == MODE_FWD ? a.dv : a.dk;
   const int B = a.B, T = a.T, H = a.H, dk = a.dk, dv = a.dv;
   ScanParams p;
   int r;
@@ -817,11 +958,11 @@ int launch_pass(const PassArgs& a, cudaStream_t stream) {
   // start (block size = suffix length, so no chunk straddles two suffixes): the CTA's set-up and pipeline fill are
   // paid once per G suffixes.  G is the largest divisor of M that still leaves a few waves of CTAs.
   int G = 1;
-  SeqView x = a.x, k = a.k, v = a.v, out = a.out;
+  SeqView x = state_only ? a.k : a.x, k = a.k, v = a.v, out = state_only ? a.v : a.out;   // a state-only pass reads k and v only
   int Bk = B, Tk = T, block_size = a.block_size;
   if (a.sfx.M > 1 && !a.rev && g_sfx_group && a.block_size == 0 && x.sb == (int64_t)T * x.st && k.sb == (int64_t)T * k.st &&
       v.sb == (int64_t)T * v.st && out.sb == (int64_t)T * out.st) {
-    G = choose_suffix_group(a.sfx.M, (long long)(B / a.sfx.M) * H * (a.mode == MODE_FWD ? (dv + 127) / 128 : (dk + 127) / 128));
+    G = choose_suffix_group(a.sfx.M, (long long)(B / a.sfx.M) * H * (mode == MODE_FWD ? (dv + 127) / 128 : (dk + 127) / 128));
     if (G > 1) {
       Bk = B / G; Tk = T * G; block_size = T;
       x.sb *= G; k.sb *= G; v.sb *= G; out.sb *= G;
@@ -832,15 +973,20 @@ int launch_pass(const PassArgs& a, cudaStream_t stream) {
   if ((r = make_seq_map(&p.map_v, v, Bk, Tk, H, dv, C)) != FPB_OK) return r;
   if ((r = make_seq_map(&p.map_out, out, Bk, Tk, H, ow, 16)) != FPB_OK) return r;   // one score warp's 16 rows
   p.out = (bf16*)out.data; p.out_sb = out.sb; p.out_st = out.st; p.out_sh = out.sh;
-  p.s0 = (const bf16*)a.start.data; p.s0_sb = a.start.sb; p.s0_sh = a.start.sh;
-  p.s_out = (bf16*)a.end.data; p.so_sb = a.end.sb; p.so_sh = a.end.sh;
-  p.block_states = (bf16*)a.block_states;
-  p.block_grads = (const bf16*)a.block_grads;
-  p.sfx_blocks = (bf16*)a.sfx.blocks; p.sfx_M = a.sfx.M; p.sfx_N = a.sfx.N; p.sfx_G = G;
+  const bool split = sg.n > 1;
+  // a segmented walk starts from the scratch slots and leaves no end value (the scan wrote it)
+  p.s0 = split ? nullptr : a.start.data; p.s0_sb = a.start.sb; p.s0_sh = a.start.sh;
+  p.s_out = split ? nullptr : a.end.data; p.so_sb = a.end.sb; p.so_sh = a.end.sh;
+  p.block_states = state_only ? nullptr : a.block_states;
+  p.block_grads = a.block_grads;
+  p.sfx_blocks = a.sfx.blocks; p.sfx_M = a.sfx.M; p.sfx_N = a.sfx.N; p.sfx_G = G;
   p.T = Tk; p.H = H; p.dk = dk; p.dv = dv; p.block_size = block_size; p.n_blocks = a.n_blocks;
+  p.state_f32 = a.state_f32 ? 1 : 0;
+  p.n_seg = sg.n; p.seg_len = sg.seg_len; p.seg_states = a.scratch;
+  p.tune = g_tuning;
   // POP forward at 64 x 64: full chunks, block states from partial increments (block sizes above 64 that are multiples
   // of 16 but not of 64 - for those the block-aligned schedule already is the full-chunk one)
-  const bool emit = g_pop_emit && a.mode == MODE_FWD && !a.rev && a.block_states && dk == 64 && dv == 64 &&
+  const bool emit = g_pop_emit && mode == MODE_FWD && !a.rev && a.block_states && dk == 64 && dv == 64 &&
                     block_size > 64 && block_size % 16 == 0 && block_size % 64 != 0 && G == 1;
   p.sched_bs = emit ? 0 : block_size;
   p.status = device_status_ptr();
@@ -848,24 +994,43 @@ int launch_pass(const PassArgs& a, cudaStream_t stream) {
   if (!p.status) return FPB_ERR_LAUNCH;
   for (int h = 0; h < H; ++h) p.log2g[h] = (float)std::log2((double)a.gamma[h]);
 
-#define FPB_SCAN_CASE(MODE_, R_, CC_, TILES_) return launch_scan<MODE_, R_, CC_>(p, a.rev, dim3((TILES_), H, Bk), stream)
-  if (a.mode == MODE_FWD) {       // state tile: all dk rows x CC columns of dv
-    if (dk == 128 && dv % 128 == 0 && g_tile_pref) FPB_SCAN_CASE(MODE_FWD, 128, 128, dv / 128);
-    if (dk == 128) FPB_SCAN_CASE(MODE_FWD, 128, 64, dv / 64);
-    if (dk == 64) FPB_SCAN_CASE(MODE_FWD, 64, 64, dv / 64);
-  } else {                        // state tile: R rows of dk x all dv columns
-    if (dv == 128 && dk % 128 == 0 && g_tile_pref) FPB_SCAN_CASE(MODE_DQ, 128, 128, dk / 128);
-    if (dv == 64) FPB_SCAN_CASE(MODE_DQ, 64, 64, dk / 64);
-    if (dv == 128) FPB_SCAN_CASE(MODE_DQ, 64, 128, dk / 64);
-    if (dv == 256) FPB_SCAN_CASE(MODE_DQ, 64, 256, dk / 64);
-  }
+  const Tiling t = tiling_of(mode, dk, dv);
+  const dim3 grid(t.tiles, H, Bk * sg.n);
+#define FPB_SCAN_CASE(MODE_, R_, CC_) \
+  if (mode == MODE_ && t.R == R_ && t.CC == CC_) return launch_scan<MODE_, R_, CC_>(p, a.rev, state_only, grid, stream)
+  FPB_SCAN_CASE(MODE_FWD, 128, 128); FPB_SCAN_CASE(MODE_FWD, 128, 64); FPB_SCAN_CASE(MODE_FWD, 64, 64);
+  FPB_SCAN_CASE(MODE_DQ, 128, 128); FPB_SCAN_CASE(MODE_DQ, 64, 64); FPB_SCAN_CASE(MODE_DQ, 64, 128); FPB_SCAN_CASE(MODE_DQ, 64, 256);
 #undef FPB_SCAN_CASE
   return FPB_ERR_BAD_SHAPE;
+}
+
+// A pass = one launch, or three when the launch would leave most of the GPU idle and the caller gave scratch memory:
+// local end values of T-segments, the scan over them, the walk proper from the segments' start values.
+int launch_pass(const PassArgs& a, cudaStream_t stream, int* n_launched) {
+  Segments sg{1, 0};
+  if (g_segments && a.scratch && a.sfx.M == 0 && a.B * 16 <= 65535) {
+    const Tiling t = tiling_of(a.mode, a.dk, a.dv);
+    const int align = a.block_size > 0 ? C / gcd_int(C, a.block_size) * a.block_size : C;   // segment starts: chunk and block multiples
+    sg = choose_segments((long long)t.tiles * a.H * a.B, t.ctas_per_sm, a.T, align, (long long)a.B * a.H, (long long)a.dk * a.dv,
+                         a.scratch_bytes, a.B);
+  }
+  int r;
+  if (sg.n > 1) {
+    if ((r = launch_one(a, sg, true, stream)) != FPB_OK) return r;
+    if ((r = launch_segment_combine(a.scratch, sg, a.B, a.T, a.H, a.dk, a.dv, a.gamma, a.rev, a.start, a.end, a.state_f32, stream)) != FPB_OK)
+      return r;
+    *n_launched += 2;
+  }
+  if ((r = launch_one(a, sg, false, stream)) != FPB_OK) return r;
+  ++*n_launched;
+  return FPB_OK;
 }
 
 }  // namespace
 
 long long* debug_trace_ptr() { return g_trace; }
+const WalkTuning& walk_tuning() { return g_tuning; }
+bool segments_enabled() { return g_segments != 0; }
 
 int choose_suffix_group(int M, long long units) {
   for (int cand = g_sfx_group; cand > 1; --cand)
@@ -873,25 +1038,47 @@ int choose_suffix_group(int M, long long units) {
   return 1;
 }
 
-// Diagnostics hook (not part of the public header): install a device buffer of 64*16 int64 that the next
-// launches fill with clock64() stamps of their first CTA; null removes it.
+#ifdef FPB_DIAGNOSTICS
+// Hooks of the diagnostics build (not part of the public header).
+// Install a device buffer of 64*16 int64 that the next launches fill with clock64() stamps of their first CTA; null removes it.
 extern "C" void fpb_debug_trace(void* device_buffer) { g_trace = (long long*)device_buffer; }
-// Diagnostics hook: choose between the 128x128 state tiles (1, default) and the 64-wide ones (0).
+// Choose between the 128x128 state tiles (1, default) and the 64-wide ones (0).
 extern "C" void fpb_debug_tile_pref(int wide) { g_tile_pref = wide; }
-// Diagnostics hook: upper limit of the suffixes one CTA walks back to back (1 = one CTA per suffix) and the number of
-// CTAs that must remain.
+// Upper limit of the suffixes one CTA walks back to back (1 = one CTA per suffix) and the number of CTAs that must remain.
 extern "C" void fpb_debug_suffix_group(int g, int min_ctas) { g_sfx_group = g < 1 ? 1 : g; if (min_ctas > 0) g_sfx_min_ctas = min_ctas; }
-// Diagnostics hook: 0 makes every POP forward walk cut its chunks at block ends.
+// 0 makes every POP forward walk cut its chunks at block ends.
 extern "C" void fpb_debug_pop_emit(int on) { g_pop_emit = on; }
-// Diagnostics hook: 0 runs the dV and dK walks as two launches instead of the fused reverse kernel.
+// 0 runs the dV and dK walks as two launches instead of the fused reverse kernel.
 extern "C" void fpb_debug_fused_bwd(int on) { g_fused_bwd = on; }
+// 0 never cuts sequences into T-segments.
+extern "C" void fpb_debug_segments(int on) { g_segments = on; }
+// Wait limit in clock ticks (<= 0: the default of about a second), idle suspend hint in ns, early scores on / off, and the
+// chunk the producers withhold (-1: none; makes every role's wait on it run out).
+extern "C" void fpb_debug_tuning(long long wait_cycles, int idle_ns, int sc_early, int withhold_chunk) {
+  g_tuning.wait_cycles = wait_cycles > 0 ? wait_cycles : kWaitCycles;
+  g_tuning.idle_ns = idle_ns > 0 ? idle_ns : 200;
+  g_tuning.sc_early = sc_early;
+  g_tuning.withhold_chunk = withhold_chunk;
+}
+#endif
 
-int launch_umma_fwd(const UmmaFwdArgs& a, cudaStream_t stream) {
+int launch_umma_fwd(const UmmaFwdArgs& a, cudaStream_t stream, int* n_launched) {
+  *n_launched = 0;
   if (a.dtype != FPB_BF16) return FPB_UMMA_NOT_APPLICABLE;
   PassArgs f{MODE_FWD, false, a.q, a.k, a.v, a.o, a.s0, a.s_out, a.block_states, nullptr, a.sfx, a.gamma,
-             a.B, a.T, a.H, a.dk, a.dv, a.block_size, a.n_blocks};
+             a.B, a.T, a.H, a.dk, a.dv, a.block_size, a.n_blocks, a.state_f32, a.scratch, a.scratch_bytes};
   if (!pass_applicable(f)) return FPB_UMMA_NOT_APPLICABLE;
-  return launch_pass(f, stream);
+  return launch_pass(f, stream, n_launched);
+}
+
+// Local end values of the T-segments of a walk over (k, v): used by the fused reverse kernel, whose own file has no
+// state-only instance (its first pass is the reverse MODE_FWD walk with (k, v) := (q, dO)).
+int launch_segment_states(SeqView k, SeqView v, bool rev, const void* block_grads, const float* gamma, int B, int T, int H, int dk,
+                          int dv, int block_size, int n_blocks, bool state_f32, Segments sg, float* scratch, cudaStream_t stream) {
+  const StateView none{nullptr, 0, 0};
+  PassArgs a{MODE_FWD, rev, k, k, v, v, none, none, nullptr, block_grads, SuffixStates{0, 0, nullptr}, gamma,
+             B, T, H, dk, dv, block_size, n_blocks, state_f32, scratch, 0};
+  return launch_one(a, sg, true, stream);
 }
 
 // Backward = three independent walks: dQ (forward walk over the states), dV + dS_0 and dK (reverse
@@ -903,31 +1090,25 @@ int launch_umma_bwd(const UmmaBwdArgs& a, cudaStream_t stream, int* n_launched) 
   // dQ needs the states at chunk starts only, never a block state: its walk ignores the POP block structure and
   // takes full 64-token chunks (fewer chunks than the block-aligned schedule whenever the block is not a multiple of 64)
   PassArgs dq{MODE_DQ, false, a.dO, a.k, a.v, a.dQ, a.s0, none, nullptr, nullptr, a.sfx_in, a.gamma,
-              a.B, a.T, a.H, a.dk, a.dv, 0, 0};
+              a.B, a.T, a.H, a.dk, a.dv, 0, 0, a.state_f32, a.scratch, a.scratch_bytes};
   PassArgs dv{MODE_FWD, true, a.k, a.q, a.dO, a.dV, a.d_s_out, a.d_s0, nullptr, a.d_block_states, a.sfx_grad, a.gamma,
-              a.B, a.T, a.H, a.dk, a.dv, a.block_size, a.n_blocks};
+              a.B, a.T, a.H, a.dk, a.dv, a.block_size, a.n_blocks, a.state_f32, a.scratch, a.scratch_bytes};
   SuffixStates no_write = a.sfx_grad;
   no_write.blocks = nullptr;
   PassArgs dk{MODE_DQ, true, a.v, a.q, a.dO, a.dK, a.d_s_out, none, nullptr, a.d_block_states, no_write, a.gamma,
-              a.B, a.T, a.H, a.dk, a.dv, a.block_size, a.n_blocks};
+              a.B, a.T, a.H, a.dk, a.dv, a.block_size, a.n_blocks, a.state_f32, a.scratch, a.scratch_bytes};
   if ((!a.skip_dq && !pass_applicable(dq)) || (!a.skip_dkdv && (!pass_applicable(dv) || !pass_applicable(dk))))
     return FPB_UMMA_NOT_APPLICABLE;
   int r;
-  if (!a.skip_dq) {
-    if ((r = launch_pass(dq, stream)) != FPB_OK) return r;
-    ++*n_launched;
-  }
+  if (!a.skip_dq && (r = launch_pass(dq, stream, n_launched)) != FPB_OK) return r;
   if (a.skip_dkdv) return FPB_OK;
   if (g_fused_bwd) {
-    r = launch_bwd_fused(a, stream);
-    if (r == FPB_OK) { ++*n_launched; return FPB_OK; }
+    r = launch_bwd_fused(a, stream, n_launched);
+    if (r == FPB_OK) return FPB_OK;
     if (r != FPB_UMMA_NOT_APPLICABLE) return r;
   }
-  if ((r = launch_pass(dv, stream)) != FPB_OK) return r;
-  ++*n_launched;
-  if ((r = launch_pass(dk, stream)) != FPB_OK) return r;
-  ++*n_launched;
-  return FPB_OK;
+  if ((r = launch_pass(dv, stream, n_launched)) != FPB_OK) return r;
+  return launch_pass(dk, stream, n_launched);
 }
 
 }  // namespace fpb

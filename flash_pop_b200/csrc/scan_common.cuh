@@ -50,13 +50,18 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     *abort_flag = 1;                                                  \
   } while (0)
 
-// diagnostics: stamp event `slot` (0..15) of chunk `c` for CTA (0,0,0) when a trace buffer is installed
+// diagnostics build: stamp event `slot` (0..15) of chunk `c` for CTA (0,0,0) when a trace buffer is installed
+#ifdef FPB_DIAGNOSTICS
 #define FPB_TRACE(slot, c)                                                                              \
   do {                                                                                                  \
     if (p.trace && (blockIdx.x | blockIdx.y | blockIdx.z) == 0 && (c) < 64) p.trace[(c) * 16 + (slot)] = clock64(); \
   } while (0)
+#else
+#define FPB_TRACE(slot, c) do { } while (0)
+#endif
 
-// A polling loop that made no progress: true when it should give up (another thread did, or ~1 s passed).
+// A polling loop that made no progress: true when it should give up (another thread did, or the CTA's wait limit,
+// kept in shared memory right after the abort flag, has passed since the last progress).
 struct Patience {
   long long t_last;
   int idle;
@@ -64,7 +69,7 @@ struct Patience {
   __device__ __forceinline__ bool exhausted(volatile int* abort_flag) {
     if (idle == 0) t_last = clock64();
     if ((++idle & 31) != 0) return false;
-    return *abort_flag != 0 || clock64() - t_last > kWaitCycles;
+    return *abort_flag != 0 || clock64() - t_last > wait_limit(abort_flag);
   }
 };
 

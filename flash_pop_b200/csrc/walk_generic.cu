@@ -37,7 +37,8 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float
 // of one own index on different banks while preserving 16-byte alignment.
 template <int NPT> __device__ __forceinline__ int pad_red(int red) { return red + (red / NPT) * 4; }
 
-template <typename T, int NPT>
+// T: element type of the activations, TS: element type of the states
+template <typename T, typename TS, int NPT>
 __global__ void __launch_bounds__(WALK_THREADS) walk_kernel(const __grid_constant__ WalkParams p) {
   constexpr int RED_PAD = KS * NPT + KS * 4;
   __shared__ __align__(16) float s_w[TT][RED_PAD];
@@ -58,29 +59,29 @@ __global__ void __launch_bounds__(WALK_THREADS) walk_kernel(const __grid_constan
   const float post = p.dir > 0 ? 1.0f : gamma;
 
   // where this (batch, head)'s start state lives
-  const T* x0 = nullptr;
-  T* x_end = nullptr;
+  const TS* x0 = nullptr;
+  TS* x_end = nullptr;
   if (p.sfx.M > 0) {
     const int row = b / p.sfx.M, m = b % p.sfx.M;
     const int64_t state_elems = (int64_t)p.dk * p.dv;
     if (m == 0) {
-      if (p.x0.data) x0 = (const T*)p.x0.data + row * p.x0.sb + h * p.x0.sh;
-      if (p.x_out.data) x_end = (T*)p.x_out.data + row * p.x_out.sb + h * p.x_out.sh;
+      if (p.x0.data) x0 = (const TS*)p.x0.data + row * p.x0.sb + h * p.x0.sh;
+      if (p.x_out.data) x_end = (TS*)p.x_out.data + row * p.x_out.sb + h * p.x_out.sh;
     } else if (p.sfx.blocks) {   // null in the reverse pass that does not own the state gradient
-      T* blk = (T*)p.sfx.blocks + (((int64_t)row * p.sfx.N + (m - 1)) * p.H + h) * state_elems;
+      TS* blk = (TS*)p.sfx.blocks + (((int64_t)row * p.sfx.N + (m - 1)) * p.H + h) * state_elems;
       if (p.dir > 0) x0 = blk; else x_end = blk;
     }
     if (p.dir < 0) x0 = nullptr;   // suffix end states are dropped: their gradient is zero
   } else {
-    if (p.x0.data) x0 = (const T*)p.x0.data + b * p.x0.sb + h * p.x0.sh;
-    if (p.x_out.data) x_end = (T*)p.x_out.data + b * p.x_out.sb + h * p.x_out.sh;
+    if (p.x0.data) x0 = (const TS*)p.x0.data + b * p.x0.sb + h * p.x0.sh;
+    if (p.x_out.data) x_end = (TS*)p.x_out.data + b * p.x_out.sb + h * p.x_out.sh;
   }
 
   float X[NPT];
 #pragma unroll
   for (int i = 0; i < NPT; ++i) {
     const int red = red0 + i;
-    X[i] = (x0 && own_ok && red < p.n_red) ? to_f<T>(x0[red * p.x_stride_red + own * p.x_stride_own]) : 0.0f;
+    X[i] = (x0 && own_ok && red < p.n_red) ? to_f<TS>(x0[red * p.x_stride_red + own * p.x_stride_own]) : 0.0f;
   }
 
   const T* gu = (const T*)p.u.data + b * p.u.sb + h * p.u.sh;
@@ -113,11 +114,11 @@ __global__ void __launch_bounds__(WALK_THREADS) walk_kernel(const __grid_constan
       const bool block_end = p.block_size > 0 && (t + 1) % p.block_size == 0 &&
                              (t + 1) / p.block_size - 1 < p.n_blocks;
       if (p.dir < 0 && block_end && p.block_in && own_ok) {
-        const T* g = (const T*)p.block_in +
+        const TS* g = (const TS*)p.block_in +
                      (((int64_t)b * p.n_blocks + ((t + 1) / p.block_size - 1)) * p.H + h) * state_elems;
 #pragma unroll
         for (int i = 0; i < NPT; ++i)
-          if (red0 + i < p.n_red) X[i] += to_f<T>(g[(red0 + i) * p.x_stride_red + own * p.x_stride_own]);
+          if (red0 + i < p.n_red) X[i] += to_f<TS>(g[(red0 + i) * p.x_stride_red + own * p.x_stride_own]);
       }
       const float u = s_u[tt][own_l];
       const float* w = &s_w[tt][pad_red<NPT>(red0)];
@@ -134,11 +135,11 @@ __global__ void __launch_bounds__(WALK_THREADS) walk_kernel(const __grid_constan
       acc += __shfl_xor_sync(0xffffffffu, acc, 2);
       if (part == 0) s_o[tt][own_l] = acc * p.scale_out;
       if (p.dir > 0 && block_end && p.block_out && own_ok) {
-        T* g = (T*)p.block_out +
+        TS* g = (TS*)p.block_out +
                (((int64_t)b * p.n_blocks + ((t + 1) / p.block_size - 1)) * p.H + h) * state_elems;
 #pragma unroll
         for (int i = 0; i < NPT; ++i)
-          if (red0 + i < p.n_red) g[(red0 + i) * p.x_stride_red + own * p.x_stride_own] = from_f<T>(X[i]);
+          if (red0 + i < p.n_red) g[(red0 + i) * p.x_stride_red + own * p.x_stride_own] = from_f<TS>(X[i]);
       }
 #pragma unroll
       for (int i = 0; i < NPT; ++i) X[i] *= post;
@@ -155,25 +156,27 @@ __global__ void __launch_bounds__(WALK_THREADS) walk_kernel(const __grid_constan
   if (x_end && own_ok) {
 #pragma unroll
     for (int i = 0; i < NPT; ++i)
-      if (red0 + i < p.n_red) x_end[(red0 + i) * p.x_stride_red + own * p.x_stride_own] = from_f<T>(X[i]);
+      if (red0 + i < p.n_red) x_end[(red0 + i) * p.x_stride_red + own * p.x_stride_own] = from_f<TS>(X[i]);
   }
 }
 
-template <typename T>
+template <typename T, typename TS>
 int launch_t(const WalkParams& p, int B, cudaStream_t stream) {
-  dim3 grid((p.n_own + OWN_TILE - 1) / OWN_TILE, p.H, B);
-  if (p.n_red <= 64) walk_kernel<T, 16><<<grid, WALK_THREADS, 0, stream>>>(p);
-  else if (p.n_red <= 128) walk_kernel<T, 32><<<grid, WALK_THREADS, 0, stream>>>(p);
-  else if (p.n_red <= 256) walk_kernel<T, 64><<<grid, WALK_THREADS, 0, stream>>>(p);
+  // the batch goes into grid.z: launch_walk refuses more than 65535 rows
+  const dim3 grid((p.n_own + OWN_TILE - 1) / OWN_TILE, p.H, B);
+  if (p.n_red <= 64) walk_kernel<T, TS, 16><<<grid, WALK_THREADS, 0, stream>>>(p);
+  else if (p.n_red <= 128) walk_kernel<T, TS, 32><<<grid, WALK_THREADS, 0, stream>>>(p);
+  else if (p.n_red <= 256) walk_kernel<T, TS, 64><<<grid, WALK_THREADS, 0, stream>>>(p);
   else return FPB_ERR_BAD_SHAPE;
   return FPB_OK;
 }
 
 }  // namespace
 
-int launch_walk(const WalkParams& p, int dtype, int B, cudaStream_t stream) {
-  if (dtype == FPB_F32) return launch_t<float>(p, B, stream);
-  if (dtype == FPB_BF16) return launch_t<__nv_bfloat16>(p, B, stream);
+int launch_walk(const WalkParams& p, int dtype, bool state_f32, int B, cudaStream_t stream) {
+  if (B > 65535) return FPB_ERR_TOO_LARGE;
+  if (dtype == FPB_F32) return launch_t<float, float>(p, B, stream);
+  if (dtype == FPB_BF16) return state_f32 ? launch_t<__nv_bfloat16, float>(p, B, stream) : launch_t<__nv_bfloat16, __nv_bfloat16>(p, B, stream);
   return FPB_ERR_BAD_DTYPE;
 }
 

@@ -11,7 +11,7 @@ from typing import Optional, Sequence
 
 import torch
 
-from flash_pop_b200.fused_retention import fused_chunk_retention
+from flash_pop_b200.fused_retention import retention_forward_backward_into
 
 
 class HostRetentionPipeline:
@@ -27,9 +27,11 @@ class HostRetentionPipeline:
         self.v, self.do, self.o, self.dv = mk(like_v), mk(like_v), mk(like_v), mk(like_v)
         self.s_in, self.s_comp, self.s_out = (torch.cuda.Stream(self.device) for _ in range(3))
 
-    def run(self, hq, hk, hv, hdo, head_decays: Sequence[float], ho, hdq, hdk, hdv) -> None:
+    def run(self, hq, hk, hv, hdo, head_decays: Sequence[float], ho, hdq, hdk, hdv, copy_only: bool = False) -> None:
         """Reads hq, hk, hv, hdo (host), writes ho, hdq, hdk, hdv (host).  Returns when everything has been queued
-        and the calling stream has been made to wait for it."""
+        and the calling stream has been made to wait for it.  The kernels write their results straight into the
+        staging buffers (the C ABI takes output pointers), so a slice costs its two PCIe crossings and nothing else.
+        `copy_only` queues the same copies on the same streams without the kernels: what the host link alone allows."""
         cur = torch.cuda.current_stream(self.device)
         for s in (self.s_in, self.s_comp, self.s_out):
             s.wait_stream(cur)
@@ -40,11 +42,9 @@ class HostRetentionPipeline:
                 landed = self.s_in.record_event()
             with torch.cuda.stream(self.s_comp):
                 self.s_comp.wait_event(landed)
-                q, k, v = (t[a:b].detach().requires_grad_(True) for t in (self.q, self.k, self.v))
-                o, _ = fused_chunk_retention(q, k, v, None, head_decays)
-                o.backward(self.do[a:b])
-                self.o[a:b].copy_(o.detach())
-                self.dq[a:b].copy_(q.grad); self.dk[a:b].copy_(k.grad); self.dv[a:b].copy_(v.grad)
+                if not copy_only:
+                    retention_forward_backward_into(self.q[a:b], self.k[a:b], self.v[a:b], self.do[a:b], head_decays,
+                                                    self.o[a:b], self.dq[a:b], self.dk[a:b], self.dv[a:b])
                 done = self.s_comp.record_event()
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(done)

@@ -17,6 +17,7 @@ _OK_DTYPES = (torch.bfloat16, torch.float32)
 def _aligned(t: Tensor, nbytes: int) -> Tensor:
     """`t` (B,T,H,d) with unit inner stride and pointer/strides that allow `nbytes`-wide accesses, copied if not."""
     vec = nbytes // t.element_size()
+    t = _lib.unit_inner(t)      # also copies expanded / overlapping views, which the C ABI refuses
     ok = t.stride(-1) == 1 and t.data_ptr() % nbytes == 0 and all(s % vec == 0 for s in t.stride()[:-1])
     return t if ok else t.contiguous()
 

@@ -15,13 +15,13 @@ from typing import Optional, Sequence
 import torch
 
 from flash_pop_b200 import _lib
-from flash_pop_b200.fused_retention import _flags, _prepare
+from flash_pop_b200.fused_retention import _flags, _prepare, _state_dtype
 
 
 class FlashPOPRetention(torch.autograd.Function):
 
     @staticmethod
-    def forward(ctx, q, k, v, s, head_decays: Sequence[float], block_size: int):
+    def forward(ctx, q, k, v, s, head_decays: Sequence[float], block_size: int, state_dtype: Optional[torch.dtype] = None):
         head_decays = tuple(float(g) for g in head_decays)
         block_size = int(block_size)
         q, k, v, s = _prepare(q, k, v, s, head_decays)
@@ -29,16 +29,19 @@ class FlashPOPRetention(torch.autograd.Function):
         dv = v.shape[-1]
         if block_size <= 0:
             raise ValueError("block_size must be positive")
+        sdt = _state_dtype(q, s, state_dtype)
+        if s is not None and s.dtype != sdt:
+            s = s.to(sdt)
         o = torch.empty((B, T, H, dv), device=q.device, dtype=q.dtype)
-        block_states = torch.empty((B, T // block_size, H, dk, dv), device=q.device, dtype=q.dtype)
-        flags = _flags()
+        block_states = torch.empty((B, T // block_size, H, dk, dv), device=q.device, dtype=sdt)
+        flags = _flags() | (_lib.FLAG_STATE_F32 if sdt != q.dtype else 0)
         with torch.cuda.device(q.device):
-            d = _lib.dims(q, dv, head_decays, block_size=block_size, flags=flags)
+            d = _lib.dims(q, dv, head_decays, block_size=block_size, flags=flags, workspace=True)
             _lib.check(_lib.lib().fpb_pop_retention_fwd(d, _lib.seq(q), _lib.seq(k), _lib.seq(v), _lib.state(s),
                                                         _lib.seq(o), block_states.data_ptr(),
                                                         _lib.stream_ptr(q.device)))
         ctx.save_for_backward(q, k, v, s)
-        ctx.head_decays, ctx.block_size, ctx.flags = head_decays, block_size, flags
+        ctx.head_decays, ctx.block_size, ctx.flags, ctx.state_dtype = head_decays, block_size, flags, sdt
         ctx.set_materialize_grads(False)
         return o, block_states
 
@@ -50,8 +53,9 @@ class FlashPOPRetention(torch.autograd.Function):
         if dO is None:
             dO = torch.zeros((B, T, H, dv), device=q.device, dtype=q.dtype)
         dO = _lib.unit_inner(dO.to(q.dtype))
+        sdt = ctx.state_dtype
         if d_block_states is not None:
-            d_block_states = d_block_states.to(q.dtype).contiguous()
+            d_block_states = d_block_states.to(sdt).contiguous()
         need_q = ctx.needs_input_grad[0]
         need_s = s is not None and ctx.needs_input_grad[3]
         need_kv = ctx.needs_input_grad[1] or ctx.needs_input_grad[2] or need_s
@@ -59,15 +63,15 @@ class FlashPOPRetention(torch.autograd.Function):
         dQ = torch.empty_like(q) if need_q else None
         dK = torch.empty_like(k) if need_kv else None
         dV = torch.empty_like(v) if need_kv else None
-        dS = torch.empty((B, H, dk, dv), device=q.device, dtype=q.dtype) if need_s else None
+        dS = torch.empty((B, H, dk, dv), device=q.device, dtype=sdt) if need_s else None
         if need_q or need_kv:
             with torch.cuda.device(q.device):
-                d = _lib.dims(q, dv, ctx.head_decays, block_size=ctx.block_size, flags=flags)
+                d = _lib.dims(q, dv, ctx.head_decays, block_size=ctx.block_size, flags=flags, workspace=True)
                 _lib.check(_lib.lib().fpb_pop_retention_bwd(
                     d, _lib.seq(q), _lib.seq(k), _lib.seq(v), _lib.state(s), _lib.seq(dO),
                     None if d_block_states is None else d_block_states.data_ptr(),
                     _lib.seq(dQ), _lib.seq(dK), _lib.seq(dV), _lib.state(dS), _lib.stream_ptr(q.device)))
-        return dQ, dK, dV, dS, None, None
+        return dQ, dK, dV, dS, None, None, None
 
 
 flash_pop_retention = FlashPOPRetention.apply
@@ -88,10 +92,13 @@ class POPSuffixRetention(torch.autograd.Function):
         if M > N + 1:
             raise ValueError(f"{M} suffixes per row need at least {M - 1} block states, got {N}")
         fq, fk, fv = (_lib.unit_inner(t.flatten(0, 1)) for t in (sq, sk, sv))
-        s = _lib.state_tensor(s)
+        sdt = block_states.dtype
+        if sdt != sq.dtype and not (sdt == torch.float32 and sq.dtype == torch.bfloat16):
+            raise ValueError("block_states must have the dtype of the suffix tensors, or be float32 under bfloat16 activations")
+        s = _lib.state_tensor(None if s is None else s.to(sdt))
         block_states = block_states.contiguous()
         o = torch.empty((B * M, P, H, dv), device=sq.device, dtype=sq.dtype)
-        flags = _flags()
+        flags = _flags() | (_lib.FLAG_STATE_F32 if sdt != sq.dtype else 0)
         with torch.cuda.device(sq.device):
             d = _lib.dims(fq, dv, head_decays, flags=flags, batch=B)
             _lib.check(_lib.lib().fpb_pop_suffix_fwd(d, M, N, _lib.seq(fq), _lib.seq(fk), _lib.seq(fv), _lib.state(s),
@@ -108,7 +115,7 @@ class POPSuffixRetention(torch.autograd.Function):
         dv = fv.shape[-1]
         dO = _lib.unit_inner(dO.to(fq.dtype).flatten(0, 1))
         dQ, dK, dV = torch.empty_like(fq), torch.empty_like(fk), torch.empty_like(fv)
-        dS = torch.empty((B, H, dk, dv), device=fq.device, dtype=fq.dtype) if s is not None else None
+        dS = torch.empty((B, H, dk, dv), device=fq.device, dtype=block_states.dtype) if s is not None else None
         dBS = torch.empty_like(block_states)
         with torch.cuda.device(fq.device):
             d = _lib.dims(fq, dv, ctx.head_decays, flags=ctx.flags, batch=B)

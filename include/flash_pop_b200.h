@@ -3,8 +3,9 @@
  *
  * This is the whole boundary between a host framework and the CUDA code: plain pointers,
  * sizes and a cudaStream_t.  No entry point allocates, frees or keeps device memory, none
- * synchronises the host, all are stream-ordered and re-entrant.  Every entry point returns
- * an fpb_status (0 = ok); nothing aborts or traps.
+ * synchronises the host, all are stream-ordered and re-entrant (the only state the library keeps is
+ * per-thread caches of encoded tensor maps and per-device "kernel configured" flags).  Every entry
+ * point returns an fpb_status (0 = ok); nothing aborts or traps.
  *
  * Tensor conventions (the reference's own, flash_pop/fused_retention/fused_chunk_fwd.py:96-101):
  *   q, k          (B, T, H, dk)      element strides (stride_b, stride_t, stride_h), inner stride 1
@@ -38,7 +39,8 @@ typedef enum fpb_status {
   FPB_ERR_LAUNCH = 8,          /* cudaGetLastError() after a launch, see fpb_last_cuda_error */
   FPB_ERR_DEVICE_TIMEOUT = 9,  /* a bounded in-kernel wait gave up (reported by fpb_device_status) */
   FPB_ERR_TENSOR_MAP = 10,     /* cuTensorMapEncodeTiled refused the tensor */
-  FPB_ERR_TOO_LARGE = 11       /* size beyond a fixed limit of this entry point */
+  FPB_ERR_TOO_LARGE = 11,      /* size beyond a fixed limit of this entry point */
+  FPB_ERR_BAD_WORKSPACE = 12   /* workspace pointer misaligned or size negative */
 } fpb_status;
 
 typedef enum fpb_dtype { FPB_BF16 = 0, FPB_F32 = 1 } fpb_dtype;
@@ -50,7 +52,11 @@ enum {
   FPB_FLAG_FORCE_SIMT = 1,  /* take the CUDA-core fp32-math kernels even where the tensor-core ones apply */
   /* backward entry points only: leave out a part nobody needs (its output tensors may then have data == NULL) */
   FPB_FLAG_SKIP_DQ = 2,     /* no dQ: skips the forward walk that recomputes the states */
-  FPB_FLAG_SKIP_DKDV = 4    /* no dK, dV, dS_0 (nor suffix state gradients): skips the reverse walk */
+  FPB_FLAG_SKIP_DKDV = 4,   /* no dK, dV, dS_0 (nor suffix state gradients): skips the reverse walk */
+  /* Every state tensor of the call (s0, s_out, d_s_out, d_s0, block_states, d_block_states) is fp32 although the
+   * activations are bf16: a state carried from one call to the next (a long sequence fed in pieces,
+   * flash_pop/retnet.py:548-558) is then not re-rounded to bf16 at every hand-off.  Implied for fp32 activations. */
+  FPB_FLAG_STATE_F32 = 8
 };
 
 /* A (B, T, H, d) activation. */
@@ -71,7 +77,18 @@ typedef struct fpb_dims {
   int32_t block_size;   /* POP entry points only: tokens per block (> 0) */
   int32_t flags;
   const double* head_decays; /* host, H entries */
+  /* Optional device scratch memory (16-byte aligned), used only during the call.  A walk is one CTA per (batch, head,
+   * state tile); a call with few of them leaves most SMs idle.  Given scratch memory, such a call cuts every sequence
+   * into T-segments that run concurrently (local end states -> a scan over them -> the walk per segment).  NULL / 0:
+   * sequences are walked whole.  fpb_workspace_bytes says how much a shape can use; less means fewer segments. */
+  void* workspace;
+  int64_t workspace_bytes;
 } fpb_dims;
+
+/* Scratch bytes that let a call of this shape (dtype, B, T, H, dk, dv) split its walks as far as the current device
+ * makes worthwhile; 0 when the launch fills the device anyway.  No counterpart in the reference, whose grid is fixed
+ * by the shape (flash_pop/fused_retention/fused_chunk_fwd.py:119). */
+int64_t fpb_workspace_bytes(const fpb_dims* dims);
 
 /*
  * Forward of fused chunked retention.

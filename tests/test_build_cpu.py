@@ -10,13 +10,14 @@ import pytest
 
 from flash_pop_b200 import _lib
 
-LIMITS = {                                  # (kernel, template arguments of the hot instance) -> max spill-store bytes
-    ("bwd_fused_kernel", "128ELi128"): 64,
-    ("scan_kernel", "0ELi0ELi128ELi128"): 64,          # forward
-    ("scan_kernel", "1ELi0ELi128ELi128"): 64,          # dQ
-    ("bwd_fused_kernel", "64ELi64"): 0,
-    ("scan_kernel", "0ELi0ELi64ELi64"): 16,
-    ("scan_kernel", "1ELi0ELi64ELi64"): 16,
+# (kernel, template arguments of the hot instance: bf16 states, full walk) -> max spill-store bytes
+LIMITS = {
+    ("bwd_fused_kernel", "128ELi128ELb0E"): 64,
+    ("scan_kernel", "0ELi0ELi128ELi128ELb0ELb0E"): 64,          # forward
+    ("scan_kernel", "1ELi0ELi128ELi128ELb0ELb0E"): 64,          # dQ
+    ("bwd_fused_kernel", "64ELi64ELb0E"): 0,
+    ("scan_kernel", "0ELi0ELi64ELi64ELb0ELb0E"): 16,
+    ("scan_kernel", "1ELi0ELi64ELi64ELb0ELb0E"): 16,
 }
 
 

@@ -134,3 +134,33 @@ def test_bad_arguments_raise():
         fp.fused_chunk_retention(q.cpu(), q.cpu(), q.cpu(), None, (0.9, 0.9))
     with pytest.raises(ValueError):
         fp.flash_pop_retention(q, q, q, None, (0.9, 0.9), 0)
+
+
+def test_expanded_upstream_gradients_are_accepted():
+    """A loss that sums the output over tokens or heads hands the backward an expand()-ed dO (stride 0 along that
+    dimension), and q, k, v may themselves be expanded views: both are valid graphs for the reference operator and
+    must be here too (they are made contiguous before they reach the C ABI)."""
+    import flash_pop_b200 as fp
+    B, T, H, d = 2, 150, 3, 64
+    decays = orc.head_decays(H, (5, 12))
+    q, k, v, s, g = make_inputs(55, B, T, H, d, d, torch.bfloat16)
+    w_t = torch.randn(B, H, d, generator=g)
+    w_h = torch.randn(B, T, d, generator=g)
+    leaves = [t.cuda().requires_grad_(True) for t in (q, k, v, s)]
+    o, _ = fp.fused_chunk_retention(*leaves, decays)
+    ((o.float().sum(1) * w_t.cuda()).sum() + (o.float().sum(2) * w_h.cuda()).sum()).backward()
+    ref = [t.double().requires_grad_(True) for t in (q, k, v, s)]
+    o_ref, _ = orc.retention_chunkwise(*ref, decays, 64)
+    ((o_ref.sum(1) * w_t.double()).sum() + (o_ref.sum(2) * w_h.double()).sum()).backward()
+    for name, got, want in zip(("dQ", "dK", "dV", "dS0"), leaves, ref):
+        check(name, got.grad, want.grad, torch.bfloat16)
+    # the same with dO itself an expanded tensor, and with an expanded v
+    dO = torch.randn(B, 1, H, d, generator=g).to(torch.bfloat16).cuda().expand(B, T, H, d)
+    v1 = v[:, :1].cuda().expand(B, T, H, d)
+    ql, kl = (t.cuda().requires_grad_(True) for t in (q, k))
+    o, _ = fp.fused_chunk_retention(ql, kl, v1, None, decays)
+    o.backward(dO)
+    qr, kr = (t.double().requires_grad_(True) for t in (q, k))
+    o_ref, _ = orc.retention_chunkwise(qr, kr, v[:, :1].double().expand(B, T, H, d), None, decays, 64)
+    o_ref.backward(dO.cpu().double())
+    check("O", o, o_ref, torch.bfloat16), check("dQ", ql.grad, qr.grad, torch.bfloat16), check("dK", kl.grad, kr.grad, torch.bfloat16)

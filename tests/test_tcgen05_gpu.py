@@ -199,11 +199,8 @@ def test_host_memory_pipeline_equals_direct_call():
 def test_grouped_suffix_walks_equal_one_cta_per_suffix(M, N, P, d):
     """Consecutive suffixes of a row walked by one CTA as one sequence (state replaced at every suffix start) give
     bit for bit what one CTA per suffix gives, forward and backward; odd counts and strided tensors fall back."""
-    import ctypes
     import flash_pop_b200 as fp
     from flash_pop_b200 import _lib
-    hook = _lib.lib().fpb_debug_suffix_group
-    hook.argtypes = [ctypes.c_int, ctypes.c_int]
     B, H = 2, 3
     decays = orc.head_decays(H, (5, 12))
     g = torch.Generator().manual_seed(M * 100 + P)
@@ -211,16 +208,18 @@ def test_grouped_suffix_walks_equal_one_cta_per_suffix(M, N, P, d):
     s0 = (torch.randn(B, H, d, d, generator=g) * d ** -0.5).to(BF).cuda()
     blocks = (torch.randn(B, N, H, d, d, generator=g) * d ** -0.5).to(BF).cuda()
     results = []
-    try:
-        for limit, floor in ((1, 1), (16, 1)):
-            hook(limit, floor)
-            leaves = [t.detach().clone().requires_grad_(True) for t in (sq, sk, sv, s0, blocks)]
-            o = fp.pop_suffix_retention(leaves[0], leaves[1], leaves[2], leaves[3], leaves[4], decays)
-            assert _lib.last_path() == _lib.PATH_TCGEN05
-            o.backward(sdo)
-            results.append([o.detach()] + [t.grad for t in leaves])
-    finally:
-        hook(16, 3 * 296)
+    with _lib.diagnostics_build() as diag:      # the schedule hooks exist in the diagnostics build only
+        try:
+            for limit, floor in ((1, 1), (16, 1)):
+                diag.fpb_debug_suffix_group(limit, floor)
+                leaves = [t.detach().clone().requires_grad_(True) for t in (sq, sk, sv, s0, blocks)]
+                o = fp.pop_suffix_retention(leaves[0], leaves[1], leaves[2], leaves[3], leaves[4], decays)
+                assert _lib.last_path() == _lib.PATH_TCGEN05
+                o.backward(sdo)
+                results.append([o.detach()] + [t.grad for t in leaves])
+            _lib.device_status()
+        finally:
+            diag.fpb_debug_suffix_group(16, 3 * 296)
     for a, b in zip(*results):
         assert torch.equal(a, b)
     qd, kd, vd = (t.double().cpu() for t in (sq, sk, sv))
@@ -233,24 +232,23 @@ def test_grouped_suffix_walks_equal_one_cta_per_suffix(M, N, P, d):
 def test_block_states_from_partial_increments_match_the_block_aligned_walk(T, block):
     """POP forward at d = 64: the walk over full chunks with block states taken from partial state increments against
     the walk that cuts its chunks at block ends (same kernel, hook), and against the oracle."""
-    import ctypes
     import flash_pop_b200 as fp
     from flash_pop_b200 import _lib
-    hook = _lib.lib().fpb_debug_pop_emit
-    hook.argtypes = [ctypes.c_int]
     B, H, d = 2, 4, 64
     decays = orc.head_decays(H, (5, 12))
     q, k, v, s0, _ = make_inputs(T + block, B, T, H, d, d, BF)
     outs = []
-    try:
-        for on in (0, 1):
-            hook(on)
-            with torch.no_grad():
-                o, bs = fp.flash_pop_retention(q.cuda(), k.cuda(), v.cuda(), s0.cuda(), decays, block)
-            assert _lib.last_path() == _lib.PATH_TCGEN05
-            outs.append((o.cpu(), bs.cpu()))
-    finally:
-        hook(1)
+    with _lib.diagnostics_build() as diag:
+        try:
+            for on in (0, 1):
+                diag.fpb_debug_pop_emit(on)
+                with torch.no_grad():
+                    o, bs = fp.flash_pop_retention(q.cuda(), k.cuda(), v.cuda(), s0.cuda(), decays, block)
+                assert _lib.last_path() == _lib.PATH_TCGEN05
+                outs.append((o.cpu(), bs.cpu()))
+            _lib.device_status()
+        finally:
+            diag.fpb_debug_pop_emit(1)
     o_ref, bs_ref = orc.pop_retention(q.double(), k.double(), v.double(), s0.double(), decays, block)
     for o, bs in outs:
         check("o", o, o_ref, BF)
