@@ -73,15 +73,19 @@ def build(force: bool = False, verbose: bool = False, diagnostics: bool = True) 
     for path, extra in jobs:
         if not force and not _stale(path):
             continue
-        cmd = [nvcc, *NVCC_FLAGS, *extra, "-o", path, *sources()]
+        tmp = path + ".partial"                 # built beside the target and renamed: a reader never sees half a library
+        cmd = [nvcc, *NVCC_FLAGS, *extra, "-o", tmp, *sources()]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
             print(" ".join(cmd))
-        procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)))
-    for cmd, proc in procs:
+        procs.append((path, tmp, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)))
+    for path, tmp, proc in procs:
         out, err = proc.communicate()
         if proc.returncode != 0:
+            if os.path.exists(tmp):
+                os.remove(tmp)
             raise RuntimeError("nvcc failed:\n" + out + err)
+        os.replace(tmp, path)
         if verbose:
             print(err)
     return LIB_PATH
@@ -116,6 +120,17 @@ _SIGNATURES = {
                               ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p],
     "fpb_cross_entropy_bwd": [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p,
                               ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p],
+    "fpb_adaln_fwd": [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_float, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p,
+                      ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p],
+    "fpb_adaln_bwd": [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_float, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p,
+                      ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                      ctypes.c_void_p],
+    "fpb_gate_residual_fwd": [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p,
+                              ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64,
+                              ctypes.c_void_p],
+    "fpb_gate_residual_bwd": [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p,
+                              ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p,
+                              ctypes.c_void_p],
     "fpb_device_status": [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)],
 }
 # hooks of the diagnostics build only

@@ -459,6 +459,78 @@ int fpb_layernorm_bwd(int64_t rows, int32_t d, int32_t dtype, float eps, const v
 }
 
 namespace {
+// a (mod_rows, d) operand shared by rows_per_mod consecutive rows of the activations
+int check_mod(int64_t rows, int32_t d, int32_t dtype, const void* ptr, int64_t mod_stride, int64_t rows_per_mod) {
+  if (rows_per_mod <= 0) return FPB_ERR_BAD_SHAPE;
+  if (rows == 0) return FPB_OK;
+  if (!ptr) return FPB_ERR_NULL_POINTER;
+  const int vec = dtype == FPB_F32 ? 4 : 8;
+  const int64_t mod_rows = (rows + rows_per_mod - 1) / rows_per_mod;
+  if ((mod_rows > 1 && mod_stride < d) || mod_stride % vec || (uintptr_t)ptr % 16) return FPB_ERR_BAD_STRIDE;
+  return FPB_OK;
+}
+}  // namespace
+
+int fpb_adaln_fwd(int64_t rows, int32_t d, int32_t dtype, float eps, const void* x, int64_t x_stride, const void* shift,
+                  const void* scale, int64_t mod_stride, int64_t rows_per_mod, void* y, int64_t y_stride, fpb_stream_t stream) {
+  FPB_TRY(check_norm(rows, d, dtype, x, x_stride, y, y_stride));
+  FPB_TRY(check_mod(rows, d, dtype, shift, mod_stride, rows_per_mod)); FPB_TRY(check_mod(rows, d, dtype, scale, mod_stride, rows_per_mod));
+  FPB_TRY(check_device());
+  if (rows == 0) return FPB_OK;
+  launch_adaln(dtype, false, rows, d, eps, x, x_stride, shift, scale, mod_stride, rows_per_mod, y, y_stride, nullptr, 0, nullptr,
+               nullptr, nullptr, (cudaStream_t)stream);
+  return finish_launches(1, -1);
+}
+
+int fpb_adaln_bwd(int64_t rows, int32_t d, int32_t dtype, float eps, const void* x, int64_t x_stride, const void* scale,
+                  int64_t mod_stride, int64_t rows_per_mod, const void* d_y, int64_t dy_stride, void* d_x, float* d_shift,
+                  float* d_scale, fpb_stream_t stream) {
+  FPB_TRY(check_norm(rows, d, dtype, x, x_stride, d_y, dy_stride));
+  FPB_TRY(check_mod(rows, d, dtype, scale, mod_stride, rows_per_mod));
+  if (rows > 0 && (!d_x || !d_shift || !d_scale)) return FPB_ERR_NULL_POINTER;
+  if ((uintptr_t)d_x % 16) return FPB_ERR_BAD_STRIDE;
+  FPB_TRY(check_device());
+  if (rows == 0) return FPB_OK;
+  // the kernel adds its partial sums into the two gradient matrices
+  const size_t gbytes = (size_t)((rows + rows_per_mod - 1) / rows_per_mod) * d * sizeof(float);
+  if (cudaMemsetAsync(d_shift, 0, gbytes, (cudaStream_t)stream) != cudaSuccess ||
+      cudaMemsetAsync(d_scale, 0, gbytes, (cudaStream_t)stream) != cudaSuccess)
+    return finish_launches(0, -1);
+  launch_adaln(dtype, true, rows, d, eps, x, x_stride, nullptr, scale, mod_stride, rows_per_mod, nullptr, 0, d_y, dy_stride, d_x,
+               d_shift, d_scale, (cudaStream_t)stream);
+  return finish_launches(1, -1);
+}
+
+int fpb_gate_residual_fwd(int64_t rows, int32_t d, int32_t dtype, const void* x, int64_t x_stride, const void* branch,
+                          int64_t branch_stride, const void* gate, int64_t mod_stride, int64_t rows_per_mod, void* out,
+                          int64_t out_stride, fpb_stream_t stream) {
+  FPB_TRY(check_norm(rows, d, dtype, x, x_stride, out, out_stride));
+  FPB_TRY(check_norm(rows, d, dtype, branch, branch_stride, out, out_stride));
+  FPB_TRY(check_mod(rows, d, dtype, gate, mod_stride, rows_per_mod));
+  FPB_TRY(check_device());
+  if (rows == 0) return FPB_OK;
+  launch_gate_residual(dtype, false, rows, d, x, x_stride, branch, branch_stride, gate, mod_stride, rows_per_mod, out, out_stride,
+                       nullptr, nullptr, (cudaStream_t)stream);
+  return finish_launches(1, -1);
+}
+
+int fpb_gate_residual_bwd(int64_t rows, int32_t d, int32_t dtype, const void* branch, int64_t branch_stride, const void* gate,
+                          int64_t mod_stride, int64_t rows_per_mod, const void* d_out, int64_t dout_stride, void* d_branch,
+                          float* d_gate, fpb_stream_t stream) {
+  FPB_TRY(check_norm(rows, d, dtype, branch, branch_stride, d_out, dout_stride));
+  FPB_TRY(check_mod(rows, d, dtype, gate, mod_stride, rows_per_mod));
+  if (rows > 0 && (!d_branch || !d_gate)) return FPB_ERR_NULL_POINTER;
+  if ((uintptr_t)d_branch % 16) return FPB_ERR_BAD_STRIDE;
+  FPB_TRY(check_device());
+  if (rows == 0) return FPB_OK;
+  const size_t gbytes = (size_t)((rows + rows_per_mod - 1) / rows_per_mod) * d * sizeof(float);
+  if (cudaMemsetAsync(d_gate, 0, gbytes, (cudaStream_t)stream) != cudaSuccess) return finish_launches(0, -1);
+  launch_gate_residual(dtype, true, rows, d, d_out, dout_stride, branch, branch_stride, gate, mod_stride, rows_per_mod, nullptr, 0,
+                       d_branch, d_gate, (cudaStream_t)stream);
+  return finish_launches(1, -1);
+}
+
+namespace {
 int check_xent(int64_t rows, int32_t V, int32_t dtype, const void* logits, int64_t row_stride) {
   if (rows < 0 || V <= 0) return FPB_ERR_BAD_SHAPE;
   if (rows >= (1ll << 31)) return FPB_ERR_TOO_LARGE;

@@ -66,6 +66,14 @@ int launch_layernorm(int dtype, bool backward, int64_t rows, int d, float eps, c
                      const float* w, const float* b, void* y, int64_t y_stride, const void* dy, void* dx, float* dw,
                      float* db, cudaStream_t stream);
 
+// Adaptive LayerNorm modulation and gated residual with row-broadcast operands (adaln_fused.cu).
+int launch_adaln(int dtype, bool backward, int64_t rows, int d, float eps, const void* x, int64_t x_stride, const void* shift,
+                 const void* scale, int64_t mod_stride, int64_t rows_per_mod, void* y, int64_t y_stride, const void* dy,
+                 int64_t dy_stride, void* dx, float* d_shift, float* d_scale, cudaStream_t stream);
+int launch_gate_residual(int dtype, bool backward, int64_t rows, int d, const void* x_or_dout, int64_t x_stride, const void* branch,
+                         int64_t branch_stride, const void* gate, int64_t mod_stride, int64_t rows_per_mod, void* out,
+                         int64_t out_stride, void* d_branch, float* d_gate, cudaStream_t stream);
+
 // Softmax cross entropy of (rows x V) logits against int64 targets (loss_fused.cu).
 int launch_xent_fwd(int dtype, int64_t rows, int V, const void* logits, int64_t row_stride, const int64_t* targets, float* loss,
                     float* lse, cudaStream_t stream);

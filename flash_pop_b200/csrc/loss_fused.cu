@@ -82,10 +82,11 @@ __global__ void __launch_bounds__(XENT_THREADS) xent_fwd_kernel(const T* __restr
 
 // d_logits[row, j] = (softmax_j - [j == target]) * scale[0] * row_weight, row_weight = 1 / rows for the mean loss
 template <typename T>
-__global__ void __launch_bounds__(XENT_THREADS) xent_bwd_kernel(const T* __restrict__ logits, int64_t row_stride, int V,
+// logits and d_logits may be the same buffer (each thread reads an element before it writes it): no __restrict__ on them
+__global__ void __launch_bounds__(XENT_THREADS) xent_bwd_kernel(const T* logits, int64_t row_stride, int V,
                                                                const int64_t* __restrict__ targets, const float* __restrict__ lse,
                                                                const float* __restrict__ scale, float row_weight,
-                                                               T* __restrict__ d_logits, int64_t d_stride) {
+                                                               T* d_logits, int64_t d_stride) {
   constexpr int N = Vec16<T>::N;
   const int64_t row = blockIdx.x;
   const T* x = logits + row * row_stride;

@@ -11,7 +11,7 @@ import torch
 import torch.nn as nn
 from torch import Tensor
 
-from flash_pop_b200.modules.adaln import AdaLayerNorm, AdaLayerNormZero
+from flash_pop_b200.modules.adaln import AdaLayerNorm, AdaLayerNormZero, _to_tokens, gated_residual
 from flash_pop_b200.recurrent_state import RecurrentState
 from flash_pop_b200.retnet import ActivationString, MultiScaleRetention, RetNetDecoder, _get_activation_fn
 from flash_pop_b200.xpos_emb import XPos
@@ -67,14 +67,16 @@ class DiffusionRetNetDecoderLayer(nn.Module):
         return self.dropout(self.linear2(x))
 
     def _blocks(self, x: Tensor, c: Tensor, retention_fn) -> Tuple[Tensor, Tensor]:
-        x, gate = self.ada_ln1(x, c)
+        # the gates stay (B, Tm, D) rows of the modulation MLP's output; norm + modulation and gate + residual are one
+        # kernel each (flash_pop_b200.layer_ops)
+        x, gate = self.ada_ln1.forward_rows(x, c)
         y, state = retention_fn(x)
-        y = y * gate
-        if self.use_post_retention_dropout:
-            y = self.dropout(y)
-        x = x + y
-        x, gate = self.ada_ln2(x, c)
-        return x + self._feedforward_block(x) * gate, state
+        if self.use_post_retention_dropout and self.training and self.dropout.p > 0:
+            x = x + self.dropout(y * _to_tokens(gate, x.size(1)))
+        else:
+            x = gated_residual(x, y, gate)
+        x, gate = self.ada_ln2.forward_rows(x, c)
+        return gated_residual(x, self._feedforward_block(x), gate), state
 
     def forward_chunkwise(self, x: Tensor, c: Tensor, start_idx: int, prev_state: Optional[Tensor] = None):
         return self._blocks(x, c, lambda h: self.retention.forward_chunkwise(h, start_idx=start_idx, prev_state=prev_state))

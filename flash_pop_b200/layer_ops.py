@@ -117,7 +117,7 @@ def _rows(t: Tensor) -> Tensor:
     """(rows, d) view with unit inner stride and a 16-byte aligned row pitch, copied if that is not what `t` is."""
     t2 = t.reshape(-1, t.size(-1))
     vec = 16 // t2.element_size()
-    ok = t2.stride(1) == 1 and t2.data_ptr() % 16 == 0 and (t2.size(0) <= 1 or t2.stride(0) % vec == 0)
+    ok = t2.stride(1) == 1 and t2.data_ptr() % 16 == 0 and (t2.size(0) <= 1 or (t2.stride(0) >= t2.size(1) and t2.stride(0) % vec == 0))
     return t2 if ok else t2.contiguous()
 
 
@@ -172,6 +172,126 @@ def norm_in_fp32(module: torch.nn.LayerNorm, x: Tensor) -> Tensor:
     return module(x.float()).to(dtype=x.dtype)
 
 
+# ---- adaptive LayerNorm modulation and gated residual (diffusion RetNet) ---------------------------------------------------
+def row_broadcast_supported(x: Tensor, *mods: Tensor) -> bool:
+    """x: (B, T, D) activations; mods: (B, Tm, D) operands each shared by T / Tm consecutive tokens (views into the
+    modulation MLP's output are fine)."""
+    if not (x.is_cuda and x.dim() == 3 and layer_norm_supported(x, x.shape[-1])):
+        return False
+    B, T, D = x.shape
+    for m in mods:
+        if not (m.is_cuda and m.dim() == 3 and m.dtype == x.dtype and m.shape[0] == B and m.shape[2] == D and m.shape[1] > 0
+                and T % m.shape[1] == 0 and m.shape[1] == mods[0].shape[1]):
+            return False
+    return True
+
+
+def _mod_rows(m: Tensor):
+    """A (B, Tm, D) modulation operand as the C ABI reads it: pointer to its first row and the row pitch.  A chunk of the
+    MLP's (B, Tm, n D) output qualifies in place when its rows are evenly spaced; anything else is copied."""
+    B, Tm, D = m.shape
+    vec = 16 // m.element_size()
+    even = m.stride(2) == 1 and (B == 1 or Tm == 1 or m.stride(0) == Tm * m.stride(1))
+    pitch = m.stride(1) if Tm > 1 else (m.stride(0) if B > 1 else D)
+    if not (even and m.data_ptr() % 16 == 0 and pitch % vec == 0 and pitch >= D):
+        m = m.contiguous()
+        pitch = D
+    return m, pitch
+
+
+class AdaLNModulate(torch.autograd.Function):
+    """y = LayerNorm(x) * (1 + scale) + shift with (B, Tm, D) shift / scale broadcast over T / Tm tokens each: one
+    kernel forward, one backward (which also sums the gradients of shift and scale over the tokens that share them)."""
+
+    @staticmethod
+    def forward(ctx, x, shift, scale, eps):
+        B, T, D = x.shape
+        Tm = shift.shape[1]
+        x2 = _rows(x)
+        shift_r, pitch_a = _mod_rows(shift)
+        scale_r, pitch_b = _mod_rows(scale)
+        if pitch_a != pitch_b:                                   # one pitch serves both operands
+            shift_r, scale_r, pitch_a = shift_r.contiguous(), scale_r.contiguous(), D
+        rows = x2.shape[0]
+        y = torch.empty((rows, D), device=x.device, dtype=x.dtype)
+        with torch.cuda.device(x.device):
+            _lib.check(_lib.lib().fpb_adaln_fwd(rows, D, _lib.dtype_code(x2), eps, _ptr(x2), x2.stride(0) if rows > 1 else D,
+                                                _ptr(shift_r), _ptr(scale_r), pitch_a, T // Tm, _ptr(y), D,
+                                                _lib.stream_ptr(x.device)))
+        ctx.save_for_backward(x2, scale_r)
+        ctx.eps, ctx.shape, ctx.pitch, ctx.Tm = eps, x.shape, pitch_a, Tm
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, scale_r = ctx.saved_tensors
+        B, T, D = ctx.shape
+        rows = x2.shape[0]
+        dy2 = _rows(dy.to(x2.dtype))
+        x_in = x2 if (rows <= 1 or x2.stride(0) == D) else x2.contiguous()     # d_x is written with x's row pitch
+        dx = torch.empty((rows, D), device=x2.device, dtype=x2.dtype)
+        d_shift = torch.empty((B * ctx.Tm, D), device=x2.device, dtype=torch.float32)
+        d_scale = torch.empty_like(d_shift)
+        with torch.cuda.device(x2.device):
+            _lib.check(_lib.lib().fpb_adaln_bwd(rows, D, _lib.dtype_code(x2), ctx.eps, _ptr(x_in), D, _ptr(scale_r), ctx.pitch,
+                                                T // ctx.Tm, _ptr(dy2), dy2.stride(0) if rows > 1 else D, _ptr(dx), _ptr(d_shift),
+                                                _ptr(d_scale), _lib.stream_ptr(x2.device)))
+        as_mod = lambda t: t.view(B, ctx.Tm, D).to(x2.dtype)
+        return dx.view(ctx.shape), as_mod(d_shift), as_mod(d_scale), None
+
+
+class GateResidual(torch.autograd.Function):
+    """out = x + gate * branch with a (B, Tm, D) gate broadcast over T / Tm tokens each."""
+
+    @staticmethod
+    def forward(ctx, x, branch, gate):
+        B, T, D = x.shape
+        Tm = gate.shape[1]
+        x2, b2 = _rows(x), _rows(branch.to(x.dtype))
+        gate_r, pitch = _mod_rows(gate)
+        rows = x2.shape[0]
+        out = torch.empty((rows, D), device=x.device, dtype=x.dtype)
+        with torch.cuda.device(x.device):
+            _lib.check(_lib.lib().fpb_gate_residual_fwd(rows, D, _lib.dtype_code(x2), _ptr(x2), x2.stride(0) if rows > 1 else D, _ptr(b2),
+                                                        b2.stride(0) if rows > 1 else D, _ptr(gate_r), pitch, T // Tm, _ptr(out), D,
+                                                        _lib.stream_ptr(x.device)))
+        ctx.save_for_backward(b2, gate_r)
+        ctx.shape, ctx.pitch, ctx.Tm = x.shape, pitch, Tm
+        return out.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, d_out):
+        b2, gate_r = ctx.saved_tensors
+        B, T, D = ctx.shape
+        rows = b2.shape[0]
+        d2 = _rows(d_out.to(b2.dtype))
+        b_in = b2 if (rows <= 1 or b2.stride(0) == D) else b2.contiguous()
+        d_branch = torch.empty((rows, D), device=b2.device, dtype=b2.dtype)
+        d_gate = torch.empty((B * ctx.Tm, D), device=b2.device, dtype=torch.float32)
+        with torch.cuda.device(b2.device):
+            _lib.check(_lib.lib().fpb_gate_residual_bwd(rows, D, _lib.dtype_code(b2), _ptr(b_in), D, _ptr(gate_r), ctx.pitch,
+                                                        T // ctx.Tm, _ptr(d2), d2.stride(0) if rows > 1 else D, _ptr(d_branch),
+                                                        _ptr(d_gate), _lib.stream_ptr(b2.device)))
+        return d_out, d_branch.view(ctx.shape), d_gate.view(B, ctx.Tm, D).to(b2.dtype)
+
+
+def adaln_modulate(x: Tensor, shift: Tensor, scale: Tensor, eps: float) -> Tensor:
+    """``LayerNorm(x.float()).to(x.dtype) * (1 + scale) + shift`` for (B, T, D) x and (B, Tm, D) shift / scale (T % Tm == 0,
+    each modulation row shared by T / Tm consecutive tokens).  One kernel each way where the shapes qualify."""
+    if row_broadcast_supported(x, shift, scale):
+        return AdaLNModulate.apply(x, shift, scale, eps)
+    rep = x.shape[1] // shift.shape[1]
+    xn = torch.nn.functional.layer_norm(x.float(), x.shape[-1:], None, None, eps).to(x.dtype)
+    return xn * (1 + scale.repeat_interleave(rep, dim=1)) + shift.repeat_interleave(rep, dim=1)
+
+
+def gate_residual(x: Tensor, branch: Tensor, gate: Tensor) -> Tensor:
+    """``x + branch * gate`` for (B, T, D) x / branch and a (B, Tm, D) gate shared by T / Tm consecutive tokens."""
+    if row_broadcast_supported(x, gate) and branch.shape == x.shape and branch.is_cuda:
+        return GateResidual.apply(x, branch, gate)
+    return x + branch * gate.repeat_interleave(x.shape[1] // gate.shape[1], dim=1)
+
+
 # ---- softmax cross entropy for the language-model head --------------------------------------------------------------
 def cross_entropy_supported(logits: Tensor, targets: Tensor) -> bool:
     vec = 16 // max(logits.element_size(), 1)
@@ -212,7 +332,13 @@ class FusedCrossEntropy(torch.autograd.Function):
 
 
 def cross_entropy(logits: Tensor, targets: Tensor) -> Tensor:
-    """Mean cross entropy of (rows, V) logits against int64 targets, as ``F.cross_entropy(logits.float(), targets)``."""
+    """Softmax cross entropy of (rows, V) logits against int64 targets, fp32 arithmetic, averaged over ALL rows: a row
+    whose target lies outside [0, V) (PyTorch's ignore_index -100 among them) adds zero loss and gets a zero gradient
+    but still counts in the denominator.  With every target in range this is ``F.cross_entropy(logits.float(), targets)``.
+    Both paths below follow this one rule; which one runs depends only on the logits' alignment."""
     if cross_entropy_supported(logits, targets):
         return FusedCrossEntropy.apply(logits, targets)
-    return torch.nn.functional.cross_entropy(logits.float(), targets)
+    valid = (targets >= 0) & (targets < logits.size(-1))
+    safe = torch.where(valid, targets, torch.zeros_like(targets))
+    per_row = torch.nn.functional.cross_entropy(logits.float(), safe, reduction="none")
+    return (per_row * valid.to(per_row.dtype)).sum() / max(logits.size(0), 1)

@@ -8,7 +8,7 @@ from typing import Optional, Tuple
 import torch
 import torch.nn as nn
 
-from flash_pop_b200.layer_ops import norm_in_fp32
+from flash_pop_b200.layer_ops import adaln_modulate, gate_residual
 
 
 def modulate(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
@@ -54,8 +54,25 @@ class _AdaNormBase(nn.Module):
         if self.lora_hidden_dim is not None:
             nn.init.zeros_(self.modulation[-2].weight)
 
-    def _parts(self, x, c):
-        return apply_modulation(c, self.modulation, x.shape).chunk(self.n_chunks, dim=-1), norm_in_fp32(self.norm, x)
+    def modulation_rows(self, x: torch.Tensor, c: torch.Tensor):
+        """The modulation MLP on the conditioning, NOT broadcast to the activations: `n_chunks` tensors (B, Tm, D), each
+        row shared by T / Tm consecutive tokens of x - Tm = 1 for c (B, D), T' for c (B, T', D), T for c (B, T, D)."""
+        assert x.dim() == 3, f"Expected x to have 3 dims, got {x.dim()}"
+        B, T = x.shape[0], x.shape[1]
+        if c.dim() == 2:
+            c = c.unsqueeze(1)
+        assert c.dim() == 3, f"Got c.dim={c.dim()}"
+        assert c.size(1) == T or T % c.size(1) == 0, f"Got incompatible shapes: {tuple(x.shape)}, {tuple(c.shape)}"
+        return self.modulation(c).chunk(self.n_chunks, dim=-1)
+
+    def modulated_norm(self, x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+        """norm(x) * (1 + scale) + shift, the fp32 LayerNorm and the modulation in one kernel each way on CUDA."""
+        return adaln_modulate(x, shift, scale, self.norm.eps)
+
+
+def _to_tokens(m: torch.Tensor, T: int) -> torch.Tensor:
+    """(B, Tm, D) modulation rows as the (B, T, D) tensor the reference's modules hand out."""
+    return m.expand(-1, T, -1) if m.size(1) == 1 else (m if m.size(1) == T else m.repeat_interleave(T // m.size(1), dim=1))
 
 
 class AdaLayerNorm(_AdaNormBase):
@@ -63,8 +80,8 @@ class AdaLayerNorm(_AdaNormBase):
     n_chunks = 2
 
     def forward(self, x: torch.Tensor, c: torch.Tensor) -> torch.Tensor:
-        (shift, scale), xn = self._parts(x, c)
-        return modulate(xn, shift, scale)
+        shift, scale = self.modulation_rows(x, c)
+        return self.modulated_norm(x, shift, scale)
 
 
 class AdaLayerNormZero(_AdaNormBase):
@@ -72,5 +89,15 @@ class AdaLayerNormZero(_AdaNormBase):
     n_chunks = 3
 
     def forward(self, x: torch.Tensor, c: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-        (shift, scale, gate), xn = self._parts(x, c)
-        return modulate(xn, shift, scale), gate
+        shift, scale, gate = self.modulation_rows(x, c)
+        return self.modulated_norm(x, shift, scale), _to_tokens(gate, x.size(1))
+
+    def forward_rows(self, x: torch.Tensor, c: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """As forward, with the gate left as its (B, Tm, D) rows for `gated_residual`."""
+        shift, scale, gate = self.modulation_rows(x, c)
+        return self.modulated_norm(x, shift, scale), gate
+
+
+def gated_residual(x: torch.Tensor, branch: torch.Tensor, gate_rows: torch.Tensor) -> torch.Tensor:
+    """x + branch * gate with the gate given as (B, Tm, D) rows (AdaLayerNormZero.forward_rows)."""
+    return gate_residual(x, branch, gate_rows)

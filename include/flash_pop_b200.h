@@ -15,6 +15,8 @@
  * The operator scales k by 1/sqrt(dk) itself (flash_pop/fused_retention/reference.py:57).
  * head_decays is a HOST array of H doubles, gamma_h in [0, 1]  (the reference passes a Python
  * tuple of floats: flash_pop/fused_retention/__init__.py:13,20).
+ * Limits: H <= 256, dk, dv <= 256, and at most 65535 sequences per call (B, or B * M for the suffix entry points):
+ * the batch is a grid dimension.  Larger batches return FPB_ERR_TOO_LARGE; split them.
  */
 #ifndef FLASH_POP_B200_H_
 #define FLASH_POP_B200_H_
@@ -206,14 +208,41 @@ int fpb_layernorm_bwd(int64_t rows, int32_t d, int32_t dtype, float eps, const v
                       float* d_bias, fpb_stream_t stream);
 
 /*
+ * Adaptive LayerNorm modulation and gated residual of the diffusion RetNet layers, one streaming kernel each way.
+ *   fpb_adaln_fwd:          y = LayerNorm(x) * (1 + scale) + shift     (no affine parameters, biased variance, fp32 arithmetic)
+ *   fpb_gate_residual_fwd:  out = x + gate * branch
+ * x, y, branch, out: `rows` rows of d elements as for fpb_layernorm_*.  shift / scale / gate are rows of the modulation
+ * MLP's output read in place: row m (elements `mod_stride` apart, 16-byte aligned, the activations' type) serves the
+ * rows_per_mod consecutive rows m * rows_per_mod ... of x - all tokens of a batch row, the tokens of a frame, or one.
+ * The backward entry points overwrite the fp32 gradients d_shift / d_scale / d_gate, (ceil(rows / rows_per_mod), d)
+ * contiguous, with sums over the rows that share a modulation row (atomic adds: last bits depend on the order);
+ * fpb_adaln_bwd writes d_x with x's row stride, fpb_gate_residual_bwd writes d_branch with branch's (d_x of the
+ * residual is d_out itself).
+ * Replace modulate / AdaLayerNorm / AdaLayerNormZero (flash_pop/modules/adaln.py:13-15,90-99,154-166) and the gated
+ * residuals of DiffusionRetNetDecoderLayer (flash_pop/diffusion_retnet.py:133-146).
+ */
+int fpb_adaln_fwd(int64_t rows, int32_t d, int32_t dtype, float eps, const void* x, int64_t x_stride, const void* shift,
+                  const void* scale, int64_t mod_stride, int64_t rows_per_mod, void* y, int64_t y_stride, fpb_stream_t stream);
+int fpb_adaln_bwd(int64_t rows, int32_t d, int32_t dtype, float eps, const void* x, int64_t x_stride, const void* scale,
+                  int64_t mod_stride, int64_t rows_per_mod, const void* d_y, int64_t dy_stride, void* d_x, float* d_shift,
+                  float* d_scale, fpb_stream_t stream);
+int fpb_gate_residual_fwd(int64_t rows, int32_t d, int32_t dtype, const void* x, int64_t x_stride, const void* branch,
+                          int64_t branch_stride, const void* gate, int64_t mod_stride, int64_t rows_per_mod, void* out,
+                          int64_t out_stride, fpb_stream_t stream);
+int fpb_gate_residual_bwd(int64_t rows, int32_t d, int32_t dtype, const void* branch, int64_t branch_stride, const void* gate,
+                          int64_t mod_stride, int64_t rows_per_mod, const void* d_out, int64_t dout_stride, void* d_branch,
+                          float* d_gate, fpb_stream_t stream);
+
+/*
  * Softmax cross entropy of `rows` rows of V logits (bf16 or fp32, `row_stride` elements apart, 16-byte aligned rows)
  * against int64 targets, fp32 arithmetic, for the language-model head of the full-stack training workload (the
  * reference has no loss of its own; this replaces the cast-to-fp32 + log_softmax + nll_loss passes of PyTorch).
  * The forward writes per row loss[r] = logsumexp(x_r) - x_r[target] and lse[r] (kept for the backward); a target
- * outside [0, V) gives loss 0 and a zero gradient row.  The backward writes
+ * outside [0, V) (PyTorch's ignore_index = -100 among them) gives loss 0 and a zero gradient row; such rows still count
+ * in row_weight = 1 / rows, i.e. the mean is over ALL rows.  The backward writes
  *   d_logits[r, j] = (exp(x[r, j] - lse[r]) - [j == target_r]) * scale[0] * row_weight
  * in the logits' type (`scale`: device pointer to the upstream gradient of the reduced loss; row_weight = 1 / rows
- * for a mean).  d_logits may be the logits buffer itself.
+ * for a mean over all rows).  d_logits may be the logits buffer itself (each element is read before it is written).
  */
 int fpb_cross_entropy_fwd(int64_t rows, int32_t V, int32_t dtype, const void* logits, int64_t row_stride,
                           const int64_t* targets, float* loss, float* lse, fpb_stream_t stream);

@@ -168,3 +168,109 @@ def test_cross_entropy_forward_and_backward(dtype, rows, V):
     rr = ((x.grad.double() - xd.grad).square().mean().sqrt() / xd.grad.square().mean().sqrt()).item()
     assert rr < (5e-3 if dtype == BF else 2e-5), rr
     assert x.grad.dtype == dtype and float(x.grad[0].abs().max()) == 0.0
+
+
+def _rr(got, ref):
+    return ((got.double() - ref).square().mean().sqrt() / ref.square().mean().sqrt().clamp_min(1e-30)).item()
+
+
+@pytest.mark.parametrize("dtype", [BF, F32])
+@pytest.mark.parametrize("Tm", [1, 4, 24])
+@pytest.mark.parametrize("D", [256, 1024])
+def test_adaln_modulate_and_gated_residual(dtype, Tm, D):
+    """norm(x)(1 + scale) + shift and x + gate * branch with (B, Tm, D) operands shared by T / Tm tokens, taken in place as
+    chunks of one (B, Tm, 3D) tensor (what the modulation MLP produces), against the fp64 PyTorch expressions: outputs,
+    input gradients and the gradients of shift / scale / gate summed over the tokens that share them."""
+    from flash_pop_b200.layer_ops import AdaLNModulate, GateResidual, row_broadcast_supported
+    if dtype == F32 and D > 512:
+        pytest.skip("fp32 rows are limited to 512 channels")
+    B, T, eps = 3, 24, 1e-6
+    g = torch.Generator().manual_seed(D + Tm)
+    x, br, dy, dz = (torch.randn(B, T, D, generator=g).to(dtype).cuda() for _ in range(4))
+    mod = (torch.randn(B, Tm, 3 * D, generator=g) * 0.5).to(dtype).cuda()
+    leaves = [t.detach().clone().requires_grad_(True) for t in (x, br, mod)]
+    shift, scale, gate = leaves[2].chunk(3, dim=-1)
+    assert row_broadcast_supported(leaves[0], shift, scale)
+    y = AdaLNModulate.apply(leaves[0], shift, scale, eps)
+    z = GateResidual.apply(y, leaves[1], gate)
+    ((y * dy).sum() + (z * dz).sum()).backward()
+    ref = [t.double().detach().clone().requires_grad_(True) for t in (x, br, mod)]
+    rs, rc, rg = (t.repeat_interleave(T // Tm, dim=1) for t in ref[2].chunk(3, dim=-1))
+    yr = F.layer_norm(ref[0], (D,), None, None, eps) * (1 + rc) + rs
+    # the fused chain hands the residual kernel y rounded to `dtype`; do the same in the reference
+    y_in = y.detach().double()
+    zr = y_in + ref[1] * rg
+    ((yr * dy.double()).sum() + (zr * dz.double()).sum()).backward()
+    lim = 4e-3 if dtype == BF else 2e-6
+    assert _rr(y, yr.detach()) < lim and _rr(z, zr.detach()) < lim
+    # d_x of the chain = d_y from the modulate (dy) + the residual's pass-through (dz) through the norm: build the same
+    xr2 = x.double().detach().clone().requires_grad_(True)
+    yr2 = F.layer_norm(xr2, (D,), None, None, eps) * (1 + rc.detach()) + rs.detach()
+    (yr2 * (dy.double() + dz.double())).sum().backward()
+    assert _rr(leaves[0].grad, xr2.grad) < lim
+    assert _rr(leaves[1].grad, ref[1].grad) < lim
+    # modulation gradients: shift <- sum(dy + dz), scale <- sum((dy + dz) n), gate <- sum(dz * branch)
+    n = F.layer_norm(x.double(), (D,), None, None, eps)
+    tot = (dy.double() + dz.double())
+    want = torch.cat([tot.view(B, Tm, T // Tm, D).sum(2), (tot * n).view(B, Tm, T // Tm, D).sum(2),
+                      (dz.double() * br.double()).view(B, Tm, T // Tm, D).sum(2)], dim=-1)
+    assert _rr(leaves[2].grad, want) < (8e-3 if dtype == BF else 2e-6)
+
+
+def test_adaln_modules_on_the_fused_path():
+    """AdaLayerNormZero / AdaLayerNorm on CUDA against the same modules' arithmetic in fp64 (the reference's expression:
+    fp32 LayerNorm, modulate, gate), for the three conditioning shapes."""
+    from flash_pop_b200.modules.adaln import AdaLayerNormZero, gated_residual
+    B, T, D = 2, 12, 256
+    torch.manual_seed(0)
+    m = AdaLayerNormZero(D, device="cuda", dtype=BF)
+    torch.nn.init.normal_(m.modulation[-1].weight, std=0.05)
+    torch.nn.init.normal_(m.modulation[-1].bias, std=0.05)
+    x = torch.randn(B, T, D, device="cuda").to(BF)
+    branch = torch.randn(B, T, D, device="cuda").to(BF)
+    for c in (torch.randn(B, D, device="cuda").to(BF), torch.randn(B, 3, D, device="cuda").to(BF), torch.randn(B, T, D, device="cuda").to(BF)):
+        y, gate_tokens = m(x, c)
+        y2, gate_rows = m.forward_rows(x, c)
+        assert torch.equal(y, y2) and gate_tokens.shape == x.shape
+        out = gated_residual(y, branch, gate_rows)
+        c3 = c.unsqueeze(1) if c.dim() == 2 else c
+        modv = m.modulation(c3).double().repeat_interleave(T // c3.size(1), dim=1)
+        shift, scale, gate = modv.chunk(3, dim=-1)
+        y_ref = F.layer_norm(x.double(), (D,), None, None, m.norm.eps) * (1 + scale) + shift
+        assert _rr(y, y_ref) < 4e-3
+        assert _rr(gate_tokens, gate) < 1e-6
+        assert _rr(out, y.double() + branch.double() * gate) < 4e-3
+
+
+def test_cross_entropy_paths_share_one_definition_and_run_in_place():
+    """Ignored / out-of-range targets: the fused kernel and the PyTorch fallback (taken for unaligned logits) give the
+    same loss - a mean over ALL rows; and the backward may overwrite the logits buffer with the gradient."""
+    import ctypes
+    from flash_pop_b200 import _lib
+    from flash_pop_b200.layer_ops import cross_entropy, cross_entropy_supported
+    rows, V = 64, 1000
+    g = torch.Generator().manual_seed(1)
+    logits = (torch.randn(rows, V, generator=g) * 2).to(BF).cuda()
+    targets = torch.randint(0, V, (rows,), generator=g).cuda()
+    targets[3], targets[10], targets[11] = -100, V + 5, -1
+    assert cross_entropy_supported(logits, targets)
+    unaligned = torch.empty(rows, V + 3, dtype=BF, device="cuda")[:, 1:V + 1]      # rows start off 16-byte boundaries
+    unaligned.copy_(logits)
+    assert not cross_entropy_supported(unaligned, targets)
+    a, b = logits.detach().requires_grad_(True), unaligned.detach().requires_grad_(True)
+    la, lb = cross_entropy(a, targets), cross_entropy(b, targets)
+    la.backward(), lb.backward()
+    assert abs(la.item() - lb.item()) < 2e-4 * max(1.0, abs(lb.item()))
+    assert _rr(a.grad, b.grad.double()) < 5e-3
+    for r in (3, 10, 11):
+        assert float(a.grad[r].abs().max()) == 0.0 and float(b.grad[r].abs().max()) == 0.0
+    # in place through the C ABI: d_logits = the logits buffer
+    loss = torch.empty(rows, device="cuda"); lse = torch.empty(rows, device="cuda")
+    scale = torch.ones(1, device="cuda")
+    buf = logits.clone()
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    st = _lib.stream_ptr(buf.device)
+    _lib.check(_lib.lib().fpb_cross_entropy_fwd(rows, V, _lib.FPB_BF16, p(buf), V, p(targets), p(loss), p(lse), st))
+    _lib.check(_lib.lib().fpb_cross_entropy_bwd(rows, V, _lib.FPB_BF16, p(buf), V, p(targets), p(lse), p(scale), 1.0 / rows, p(buf), V, st))
+    torch.cuda.synchronize()
+    assert torch.equal(buf, a.grad)
