@@ -590,7 +590,9 @@ int64_t fpb_workspace_bytes(const fpb_dims* dims) {
   // what lets the emptiest pass of this shape (one CTA per batch row and head) split as far as it would
   if (!dims || dims->B <= 0 || dims->H <= 0 || dims->T <= 0 || dims->dk <= 0 || dims->dv <= 0) return 0;
   if (dims->dtype != FPB_BF16 || check_device() != FPB_OK) return 0;
-  const Segments sg = choose_segments((long long)dims->B * dims->H, 1, dims->T, 64, (long long)dims->B * dims->H,
+  // (the small state tiles run two CTAs per SM: ask for what that residency can use)
+  const int ctas_per_sm = (dims->dk <= 64 || dims->dv <= 64) ? 2 : 1;
+  const Segments sg = choose_segments((long long)dims->B * dims->H, ctas_per_sm, dims->T, 64, (long long)dims->B * dims->H,
                                       (long long)dims->dk * dims->dv, 0, dims->B);
   return sg.n > 1 ? (int64_t)dims->B * dims->H * sg.n * dims->dk * dims->dv * 4 : 0;
 }

@@ -153,7 +153,7 @@ def test_expanded_upstream_gradients_are_accepted():
     o_ref, _ = orc.retention_chunkwise(*ref, decays, 64)
     ((o_ref.sum(1) * w_t.double()).sum() + (o_ref.sum(2) * w_h.double()).sum()).backward()
     for name, got, want in zip(("dQ", "dK", "dV", "dS0"), leaves, ref):
-        check(name, got.grad, want.grad, torch.bfloat16)
+        check(name, got.grad, want.grad, torch.bfloat16, max_outside=1e-4, plain=name != "dS0")
     # the same with dO itself an expanded tensor, and with an expanded v
     dO = torch.randn(B, 1, H, d, generator=g).to(torch.bfloat16).cuda().expand(B, T, H, d)
     v1 = v[:, :1].cuda().expand(B, T, H, d)
@@ -163,4 +163,5 @@ def test_expanded_upstream_gradients_are_accepted():
     qr, kr = (t.double().requires_grad_(True) for t in (q, k))
     o_ref, _ = orc.retention_chunkwise(qr, kr, v[:, :1].double().expand(B, T, H, d), None, decays, 64)
     o_ref.backward(dO.cpu().double())
-    check("O", o, o_ref, torch.bfloat16), check("dQ", ql.grad, qr.grad, torch.bfloat16), check("dK", kl.grad, kr.grad, torch.bfloat16)
+    check("O", o, o_ref, torch.bfloat16, max_outside=1e-4)
+    check("dQ", ql.grad, qr.grad, torch.bfloat16, max_outside=1e-4), check("dK", kl.grad, kr.grad, torch.bfloat16, max_outside=1e-4)

@@ -5,7 +5,11 @@ import pytest
 import torch
 
 from oracle import retention_oracle as orc
-from tests.util import check, make_inputs
+from tests.util import check as _check, make_inputs
+
+
+def check(name, got, ref, dtype):
+    _check(name, got, ref, dtype, max_outside=1e-4, plain=name != "dS0")
 
 pytestmark = pytest.mark.gpu
 BF = torch.bfloat16
@@ -36,14 +40,14 @@ def test_eight_pieces_with_fp32_state_equal_one_call(d):
     _lib.device_status()
     o_ref, s_ref = orc.retention_chunkwise(q.double(), k.double(), v.double(), None, decays, 64)
     check("O, fp32 hand-off", o32, o_ref, BF)
-    e32 = orc.rel_rms(s32.cpu(), s_ref)
-    e16 = orc.rel_rms(s16.float().cpu(), s_ref)
-    e1 = orc.rel_rms(s1.cpu(), s_ref)
-    # the fp32 hand-off is as accurate as the single call; the bf16 one carries eight bf16 roundings of the state
-    assert e32 < 2 * e1 + 1e-5 and e32 < 5e-4, (e32, e1)
-    assert e16 > 2 * e32, (e16, e32)
-    # and the outputs of the pieces equal the single call's up to the fp32 state's rounding
-    assert orc.rel_rms(o32.float().cpu(), o1.float().cpu().double()) < 1.5e-3
+    # the fp32 hand-off loses nothing: the state crosses the calls exactly as it sits in the registers of a single call
+    assert orc.rel_rms(s32.cpu(), s1.cpu().double()) < 1e-6
+    assert orc.rel_rms(o32.float().cpu(), o1.float().cpu().double()) < 1e-6
+    # the bf16 hand-off rounds the state eight times on the way: further from the single call, still within tolerance
+    d16 = orc.rel_rms(s16.float().cpu(), s1.cpu().double())
+    assert 1e-4 < d16 < 5e-3, d16
+    e32, e16 = orc.rel_rms(s32.cpu(), s_ref), orc.rel_rms(s16.float().cpu(), s_ref)
+    assert e32 < 5e-3 and e16 < 5e-3, (e32, e16)
 
 
 def test_fp32_state_gradients():
