@@ -40,6 +40,8 @@ WORKLOADS = {
     "c4": dict(B=16, H=8, T=5120, dk=64, dv=64, block=80),
     # a quarter of "ns" (still 4 x 67 MB of inputs, larger than L2): the case profiler captures run on
     "small": dict(B=2, H=16, T=8192, dk=128, dv=128, block=0),
+    # one batch row of "c3" (0.8 GB of inputs), for the same purpose
+    "c3s": dict(B=1, H=32, T=16384, dk=128, dv=256, block=0),
 }
 # the full RetNet stack under data parallelism: 12 layers, d_model 1024, global batch 64 x 4096 fixed (strong scaling)
 STACK = dict(layers=12, heads=8, head_dim=128, ffn=4096, vocab=32000, B=64, T=4096, micro_batch=32)
