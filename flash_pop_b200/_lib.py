@@ -30,6 +30,7 @@ NVCC_FLAGS = [
 ]
 
 FPB_BF16, FPB_F32 = 0, 1
+STATIC_SCRATCH_BYTES = 16 << 20      # FPB_STATIC_SCRATCH_BYTES of the header
 PATH_NONE, PATH_SIMT, PATH_TCGEN05 = 0, 1, 2
 FLAG_FORCE_SIMT, FLAG_SKIP_DQ, FLAG_SKIP_DKDV, FLAG_STATE_F32 = 1, 2, 4, 8
 
@@ -96,6 +97,7 @@ _lib: Optional[ctypes.CDLL] = None
 _SEQ_P, _STATE_P, _DIMS_P = ctypes.POINTER(_Seq), ctypes.POINTER(_State), ctypes.POINTER(_Dims)
 _SIGNATURES = {
     "fpb_retention_fwd": [_DIMS_P, _SEQ_P, _SEQ_P, _SEQ_P, _STATE_P, _SEQ_P, _STATE_P, ctypes.c_void_p],
+    "fpb_retention_fwd_static": [_DIMS_P, _SEQ_P, _SEQ_P, _SEQ_P, _STATE_P, _SEQ_P, _STATE_P, ctypes.c_void_p],
     "fpb_retention_bwd": [_DIMS_P, _SEQ_P, _SEQ_P, _SEQ_P, _STATE_P, _SEQ_P, _STATE_P, _SEQ_P, _SEQ_P, _SEQ_P,
                           _STATE_P, ctypes.c_void_p],
     "fpb_pop_retention_fwd": [_DIMS_P, _SEQ_P, _SEQ_P, _SEQ_P, _STATE_P, _SEQ_P, ctypes.c_void_p, ctypes.c_void_p],

@@ -27,7 +27,29 @@ int32_t* device_status_ptr() {
   return p;
 }
 
+// Scratch memory that belongs to the library image itself, for fpb_retention_fwd_static: callers that must not allocate
+// get the T-segment scratch from here.  Every device that loads the library holds these bytes until the process exits.
+// In host code the array's name is only a stand-in for the symbol - not a device address, a kernel must never be given
+// it - so the address is asked for once per device (static_scratch_ptr) and that pointer is what the kernels get.
+static __device__ __align__(256) unsigned char g_static_scratch[FPB_STATIC_SCRATCH_BYTES];
+
 namespace {
+
+// Device address of g_static_scratch on the current device: looked up on the first call per device, with that device
+// current, and kept.  Null if the runtime refuses.
+float* static_scratch_ptr() {
+  static std::atomic<float*> cache[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  float* p = cache[dev].load(std::memory_order_acquire);
+  if (!p) {
+    void* sym = nullptr;
+    if (cudaGetSymbolAddress(&sym, g_static_scratch) != cudaSuccess || !sym) { cudaGetLastError(); return nullptr; }
+    p = (float*)sym;
+    cache[dev].store(p, std::memory_order_release);
+  }
+  return p;
+}
 
 thread_local int tl_last_path = FPB_PATH_NONE;
 thread_local int tl_last_cuda_error = 0;
@@ -218,6 +240,25 @@ int fpb_retention_fwd(const fpb_dims* dims, const fpb_seq* q, const fpb_seq* k, 
   FPB_TRY(check_seq(c, v, c.dv, c.B)); FPB_TRY(check_seq(c, o, c.dv, c.B));
   FPB_TRY(check_state(s0, c)); FPB_TRY(check_state(s_out, c));
   FPB_TRY(check_device());
+  return forward(c, c.B, view(q), view(k), view(v), view(s0), view(o), view(s_out), nullptr, SuffixStates{0, 0, nullptr},
+                 (cudaStream_t)stream);
+}
+
+int fpb_retention_fwd_static(const fpb_dims* dims, const fpb_seq* q, const fpb_seq* k, const fpb_seq* v,
+                             const fpb_state* s0, const fpb_seq* o, const fpb_state* s_out, fpb_stream_t stream) {
+  Call c;
+  FPB_TRY(check_dims(dims, false, &c));
+  if (dims->workspace) return FPB_ERR_BAD_WORKSPACE;      // this entry point brings its own scratch
+  FPB_TRY(check_seq(c, q, c.dk, c.B)); FPB_TRY(check_seq(c, k, c.dk, c.B));
+  FPB_TRY(check_seq(c, v, c.dv, c.B)); FPB_TRY(check_seq(c, o, c.dv, c.B));
+  FPB_TRY(check_state(s0, c)); FPB_TRY(check_state(s_out, c));
+  FPB_TRY(check_device());
+  // a shape whose full split needs more than the built-in scratch holds is refused rather than split less
+  if (fpb_workspace_bytes(dims) > (int64_t)FPB_STATIC_SCRATCH_BYTES) return FPB_ERR_TOO_LARGE;
+  float* scratch = static_scratch_ptr();
+  if (!scratch) { tl_last_cuda_error = (int)cudaErrorInvalidSymbol; return FPB_ERR_LAUNCH; }
+  c.scratch = scratch;
+  c.scratch_bytes = FPB_STATIC_SCRATCH_BYTES;
   return forward(c, c.B, view(q), view(k), view(v), view(s0), view(o), view(s_out), nullptr, SuffixStates{0, 0, nullptr},
                  (cudaStream_t)stream);
 }
@@ -578,7 +619,7 @@ const char* fpb_strerror(int status) {
     case FPB_ERR_LAUNCH: return "CUDA launch failed (see fpb_last_cuda_error)";
     case FPB_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel gave up";
     case FPB_ERR_TENSOR_MAP: return "could not encode a TMA tensor map for a tensor";
-    case FPB_ERR_TOO_LARGE: return "size beyond a fixed limit of this entry point";
+    case FPB_ERR_TOO_LARGE: return "size beyond a fixed limit of this entry point (batch over 65535, or more scratch than the built-in array holds)";
     case FPB_ERR_BAD_WORKSPACE: return "workspace pointer not 16-byte aligned or negative size";
     default: return "unknown status";
   }

@@ -102,6 +102,28 @@ int fpb_retention_fwd(const fpb_dims* dims, const fpb_seq* q, const fpb_seq* k, 
                       const fpb_state* s0, const fpb_seq* o, const fpb_state* s_out, fpb_stream_t stream);
 
 /*
+ * fpb_retention_fwd for callers that cannot allocate device memory.  This entry point has no counterpart in the
+ * reference.  Who needs it: a host that hands the whole GPU to one arena at start-up (an inference server, a process
+ * held to a fixed memory budget) has nothing left for a later cudaMalloc to take, and a plugin running on such a
+ * host's hot path may be forbidden to allocate at all - an allocation can fail there, and cudaMalloc also makes the
+ * whole device wait.  Such a caller still wants an under-filled call (few batch rows x heads) cut into T-segments,
+ * which needs scratch memory; here the scratch is an array built into the library image,
+ * FPB_STATIC_SCRATCH_BYTES of device memory per GPU that loads the library, held until the process exits.
+ *   - Inputs and outputs are the caller's as in fpb_retention_fwd; dims->workspace must be NULL.
+ *   - The call itself allocates nothing and frees nothing (no cudaMalloc / cudaFree, no allocating library routine).
+ *   - A shape whose split would use more scratch than the array holds (fpb_workspace_bytes(dims) >
+ *     FPB_STATIC_SCRATCH_BYTES) is refused with FPB_ERR_TOO_LARGE; shapes that fill the GPU unsplit use no scratch.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress) and keeps it; make that
+ *     first call outside any stream capture.
+ *   - All calls on a device share the one array.  It keeps whatever the last call left; nothing in it has to start at
+ *     zero, since every slot a call reads it has written first.  Two calls that overlap on the GPU (different streams,
+ *     or the same stream from two threads without ordering) race on it: order them.
+ */
+#define FPB_STATIC_SCRATCH_BYTES (16u << 20)
+int fpb_retention_fwd_static(const fpb_dims* dims, const fpb_seq* q, const fpb_seq* k, const fpb_seq* v,
+                             const fpb_state* s0, const fpb_seq* o, const fpb_state* s_out, fpb_stream_t stream);
+
+/*
  * Backward of fused chunked retention: given dO and the gradient d_s_out of the returned state,
  * writes dQ, dK, dV and (if wanted) dS_0.
  * Replaces FusedChunkRetention.backward + fused_retention_bwd_dk_dv_ds + fused_retention_bwd_dq
