@@ -61,8 +61,10 @@ struct BwdParams {
   float log2g[FPB_MAX_HEADS];
 };
 
-enum { B_FULL = 0, B_EMPTY = 3, B_VRDY = 6, B_SCFULL = 9, B_PRDY = 11, B_ACCFULL = 13, B_ACCFREE = 14, B_DSFULL = 15,
-       B_DSFREE = 17, B_SBRDY = 19, B_SBFREE = 20, B_COUNT = 21 };
+constexpr int MAXS = 5;          // most stages a configuration may have
+enum { B_FULL = 0, B_EMPTY = MAXS, B_VRDY = 2 * MAXS, B_SCFULL = 3 * MAXS, B_PRDY = B_SCFULL + 2, B_ACCFULL = B_PRDY + 2,
+       B_ACCFREE = B_ACCFULL + 1, B_DSFULL = B_ACCFREE + 1, B_DSFREE = B_DSFULL + 2, B_SBRDY = B_DSFREE + 2, B_SBFREE = B_SBRDY + 1,
+       B_COUNT = B_SBFREE + 1 };
 constexpr int OFF_TMEM_SLOT = B_COUNT * 8, OFF_ABORT = OFF_TMEM_SLOT + 4, OFF_LIMIT = OFF_ABORT + 4, BAR_PAGE = 256;
 static_assert(OFF_LIMIT % 8 == 0 && OFF_LIMIT + 8 <= BAR_PAGE, "the wait limit sits right after the abort flag");
 
@@ -80,7 +82,11 @@ struct BCfg {
   static constexpr int GB_BYTES = DK * DV * 2;
   static constexpr int FIXED = 2 * NP * P_BYTES + GB_BYTES + C * DV * 2 + C * DK * 2 + BAR_PAGE;
   static constexpr int SMEM_LIMIT = 226 * 1024;
-  static constexpr int STAGES = (FIXED + 3 * STAGE_BYTES <= SMEM_LIMIT) ? 3 : 2;
+  // as many stages as the shared memory of the SM holds (the CTA has it to itself): 3 at d = 128, 5 at d = 64, where a
+  // chunk's few kilobytes leave the walk bound by the number of chunks in flight
+  static constexpr int FIT = (SMEM_LIMIT - FIXED) / STAGE_BYTES;
+  static constexpr int STAGES = FIT < MAXS ? FIT : MAXS;
+  static_assert(STAGES >= 2, "at least two stages");
   static constexpr int OFF_STAGE = 0;
   static constexpr int OFF_P1 = STAGES * STAGE_BYTES;
   static constexpr int OFF_P2 = OFF_P1 + NP * P_BYTES;
@@ -135,7 +141,7 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
   auto tm_dg = [&](int n) { return DK == 128 ? (uint32_t)(G::TM_DG + (n & 1) * DV) : (uint32_t)G::TM_DG + lanes16(n & 1); };
 
   if (tid == 0) {
-    for (int s = 0; s < 3; ++s) { mbar_init(bar(B_FULL + s), 1); mbar_init(bar(B_EMPTY + s), 1); mbar_init(bar(B_VRDY + s), G::N_STATE); }
+    for (int s = 0; s < G::STAGES; ++s) { mbar_init(bar(B_FULL + s), 1); mbar_init(bar(B_EMPTY + s), 1); mbar_init(bar(B_VRDY + s), G::N_STATE); }
     for (int j = 0; j < 2; ++j) {
       mbar_init(bar(B_SCFULL + j), 1); mbar_init(bar(B_PRDY + j), N_SCORE);
       mbar_init(bar(B_DSFULL + j), 1); mbar_init(bar(B_DSFREE + j), G::N_STATE);

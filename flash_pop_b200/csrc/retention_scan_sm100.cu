@@ -95,13 +95,20 @@ struct ScanParams {
   float log2g[FPB_MAX_HEADS];
 };
 
-// barrier slots (8 bytes each) at the start of the barrier page, then two 4-byte words
-enum { B_FULL = 0, B_EMPTY = 3, B_VRDY = 6, B_SCFULL = 9, B_PRDY = 11, B_ACCFULL = 13, B_ACCFREE = 15, B_DSFULL = 17,
-       B_DSFREE = 19, B_SBRDY = 21, B_SBFREE = 22, B_DSPFULL = 23, B_DSPFREE = 24, B_COUNT = 25 };
-constexpr int OFF_TMEM_SLOT = B_COUNT * 8, OFF_ABORT = OFF_TMEM_SLOT + 4, OFF_LIMIT = OFF_ABORT + 4, BAR_PAGE = 256;
+// barrier slots (8 bytes each) at the start of the barrier page - three per stage of the tile ring, then the fixed
+// ones - then two 4-byte words and the wait limit
+constexpr int MAXS = 6;          // most stages a configuration may have
+enum { B_FULL = 0, B_EMPTY = MAXS, B_VRDY = 2 * MAXS, B_SCFULL = 3 * MAXS, B_PRDY = B_SCFULL + 2, B_ACCFULL = B_PRDY + 2,
+       B_ACCFREE = B_ACCFULL + 2, B_DSFULL = B_ACCFREE + 2, B_DSFREE = B_DSFULL + 2, B_SBRDY = B_DSFREE + 2, B_SBFREE = B_SBRDY + 1,
+       B_DSPFULL = B_SBFREE + 1, B_DSPFREE = B_DSPFULL + 1, B_COUNT = B_DSPFREE + 1 };
+constexpr int OFF_TMEM_SLOT = B_COUNT * 8, OFF_ABORT = OFF_TMEM_SLOT + 4, OFF_LIMIT = OFF_ABORT + 4, BAR_PAGE = 512;
 static_assert(OFF_LIMIT % 8 == 0 && OFF_LIMIT + 8 <= BAR_PAGE, "the wait limit sits right after the abort flag");
 
-template <int MODE, int R, int CC>
+// DEEP: a variant of the small-tile configurations for launches of at most one CTA per SM.  The small tiles normally
+// run two CTAs per SM with the three stages each half of the shared memory holds; a lone CTA on its SM is then bound by
+// how many chunks it can have in flight (a chunk holds its stage for about 12 k cycles from the issue of its copies to
+// the completion of its last product), so the lone CTA takes the whole shared memory: six stages, two P' buffers.
+template <int MODE, int R, int CC, bool DEEP = false>
 struct Cfg {
   static constexpr int W1 = MODE == MODE_FWD ? R : CC;       // width of X (and of the Sc contraction)
   static constexpr int NOUT = MODE == MODE_FWD ? CC : R;     // width of the output tile
@@ -110,19 +117,22 @@ struct Cfg {
   static constexpr bool DIRECT_OUT = NOUT == 64;
   // one CTA per SM for the large state tiles (128x128, 64x256), two for the small ones
   static constexpr bool ONE = R * CC >= 128 * 128;
+  static constexpr bool SOLO = ONE || DEEP;                  // one CTA per SM
   static constexpr int STATE_WARPS = ONE ? 8 : 4;
   static constexpr int N_STATE = 32 * STATE_WARPS;
   static constexpr int NTHREADS = STATE_WARP0 * 32 + N_STATE;
-  static constexpr int MIN_CTAS = ONE ? 1 : 2;
-  static constexpr int NP = ONE ? 2 : 1;                     // P' buffers
+  static constexpr int MIN_CTAS = SOLO ? 1 : 2;
+  static constexpr int NP = SOLO ? 2 : 1;                    // P' buffers
   static constexpr int X_BYTES = C * W1 * 2, K_BYTES = C * R * 2, V_BYTES = C * CC * 2;
   static constexpr int STAGE_BYTES = X_BYTES + K_BYTES + V_BYTES;
   static constexpr int P_BYTES = C * C * 2;
   static constexpr int SB_BYTES = R * CC * 2;
   static constexpr int OUT_BYTES = C * NOUT * 2;
   static constexpr int FIXED = NP * P_BYTES + SB_BYTES + OUT_BYTES + BAR_PAGE;
-  static constexpr int SMEM_LIMIT = ONE ? 226 * 1024 : 115712;   // (233472 B per SM) / 2 - 1 KB system reserve
-  static constexpr int STAGES = (FIXED + 3 * STAGE_BYTES <= SMEM_LIMIT) ? 3 : 2;
+  static constexpr int SMEM_LIMIT = SOLO ? 226 * 1024 : 115712;  // (233472 B per SM) / 2 - 1 KB system reserve
+  static constexpr int FIT = (SMEM_LIMIT - FIXED) / STAGE_BYTES;
+  static constexpr int STAGES = DEEP ? (FIT < MAXS ? FIT : MAXS) : (FIT >= 3 ? 3 : 2);
+  static_assert(STAGES >= 2, "at least two stages");
   static constexpr int OFF_STAGE = 0;
   static constexpr int OFF_P = STAGES * STAGE_BYTES;
   static constexpr int OFF_SB = OFF_P + NP * P_BYTES;
@@ -146,7 +156,7 @@ struct Cfg {
   static constexpr int TM_USED = TM_DSP + (EMIT ? CC : 0);
   static constexpr int TM_COLS = TM_USED <= 256 ? 256 : 512;
   static_assert(TM_USED <= 512, "tensor memory budget");
-  static_assert(ONE || TM_COLS == 256, "two CTAs per SM need at most 256 columns each");
+  static_assert(SOLO || TM_COLS == 256, "two CTAs per SM need at most 256 columns each");
   // state registers per state-warp thread; NHALF warps share one tensor-memory sub-partition
   static constexpr int NHALF = STATE_WARPS / 4;
   static constexpr int WCOLS = CC / NHALF;                   // state columns handled by one warp
@@ -156,10 +166,10 @@ struct Cfg {
 // SO ("state only"): the walk computes nothing but the state recurrence from a zero start and leaves its end value, fp32,
 // in p.seg_states - the first pass of a T-segmented call.
 // SF32: the call's state tensors (start / end state, block states and their gradients, suffix start states) are fp32.
-template <int MODE, int REV, int R, int CC, bool SO, bool SF32>
-__global__ void __launch_bounds__(Cfg<MODE, R, CC>::NTHREADS, Cfg<MODE, R, CC>::MIN_CTAS)
+template <int MODE, int REV, int R, int CC, bool SO, bool SF32, bool DEEP = false>
+__global__ void __launch_bounds__(Cfg<MODE, R, CC, DEEP>::NTHREADS, Cfg<MODE, R, CC, DEEP>::MIN_CTAS)
 scan_kernel(const __grid_constant__ ScanParams p) {
-  using G = Cfg<MODE, R, CC>;
+  using G = Cfg<MODE, R, CC, DEEP>;
   extern __shared__ __align__(1024) uint8_t sm[];
   const uint32_t sbase = smem_u32(sm);
   if (sbase & 1023) {                                  // the swizzled tiles need a 1024-byte aligned base
@@ -190,7 +200,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
   auto tm_ds = [&](int n) { return R == 128 ? (uint32_t)(G::TM_DS + (n & 1) * CC) : (uint32_t)(G::TM_DS + ((n & 1) ? (16u << 16) : 0u)); };
 
   if (tid == 0) {
-    for (int s = 0; s < 3; ++s) { mbar_init(bar(B_FULL + s), 1); mbar_init(bar(B_EMPTY + s), 1); mbar_init(bar(B_VRDY + s), G::N_STATE); }
+    for (int s = 0; s < G::STAGES; ++s) { mbar_init(bar(B_FULL + s), 1); mbar_init(bar(B_EMPTY + s), 1); mbar_init(bar(B_VRDY + s), G::N_STATE); }
     for (int j = 0; j < 2; ++j) {
       mbar_init(bar(B_SCFULL + j), 1); mbar_init(bar(B_PRDY + j), N_SCORE);
       mbar_init(bar(B_ACCFULL + j), 1); mbar_init(bar(B_ACCFREE + j), N_SCORE);
@@ -849,20 +859,37 @@ scan_kernel(const __grid_constant__ ScanParams p) {
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tm, G::TM_COLS); }
 }
 
-template <int MODE, int REV, int R, int CC, bool SO, bool SF32>
+template <int MODE, int REV, int R, int CC, bool SO, bool SF32, bool DEEP = false>
 int launch_scan_t(const ScanParams& p, dim3 grid, cudaStream_t stream) {
-  using G = Cfg<MODE, R, CC>;
+  using G = Cfg<MODE, R, CC, DEEP>;
   static std::atomic<bool> configured[64];
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
-    if (cudaFuncSetAttribute(scan_kernel<MODE, REV, R, CC, SO, SF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM) != cudaSuccess)
+    if (cudaFuncSetAttribute(scan_kernel<MODE, REV, R, CC, SO, SF32, DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM) != cudaSuccess)
       return FPB_ERR_LAUNCH;
     if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
   }
-  scan_kernel<MODE, REV, R, CC, SO, SF32><<<grid, G::NTHREADS, G::SMEM, stream>>>(p);
+  scan_kernel<MODE, REV, R, CC, SO, SF32, DEEP><<<grid, G::NTHREADS, G::SMEM, stream>>>(p);
   return FPB_OK;
 }
+int sm_count_cached() {
+  static std::atomic<int> cache[64];
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if ((n = cache[dev].load(std::memory_order_acquire)) == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cache[dev].store(n, std::memory_order_release);
+  }
+  return n;
+}
+
+#ifdef FPB_DIAGNOSTICS
+int g_deep = 1;                  // 1: small tiles take the deep-pipeline variant when the grid has at most one CTA per SM
+#else
+constexpr int g_deep = 1;
+#endif
+
 template <int MODE, int R, int CC>
 int launch_scan(const ScanParams& p, bool rev, bool state_only, dim3 grid, cudaStream_t stream) {
   const bool f32 = p.state_f32 != 0;
@@ -874,6 +901,10 @@ int launch_scan(const ScanParams& p, bool rev, bool state_only, dim3 grid, cudaS
     }
   }
   if (state_only) return FPB_ERR_BAD_SHAPE;
+  if constexpr (R == 64 && CC == 64) {   // at most one CTA per SM: the deep-pipeline variant (forward walks, bf16 states)
+    if (!f32 && !rev && g_deep && (long long)grid.x * grid.y * grid.z <= sm_count_cached())
+      return launch_scan_t<MODE, 0, R, CC, false, false, true>(p, grid, stream);
+  }
   if (f32) return rev ? launch_scan_t<MODE, 1, R, CC, false, true>(p, grid, stream) : launch_scan_t<MODE, 0, R, CC, false, true>(p, grid, stream);
   return rev ? launch_scan_t<MODE, 1, R, CC, false, false>(p, grid, stream) : launch_scan_t<MODE, 0, R, CC, false, false>(p, grid, stream);
 }
@@ -1052,6 +1083,8 @@ extern "C" void fpb_debug_pop_emit(int on) { g_pop_emit = on; }
 extern "C" void fpb_debug_fused_bwd(int on) { g_fused_bwd = on; }
 // 0 never cuts sequences into T-segments.
 extern "C" void fpb_debug_segments(int on) { g_segments = on; }
+// 0 keeps the two-CTAs-per-SM configuration of the small tiles for every grid size.
+extern "C" void fpb_debug_deep(int on) { g_deep = on; }
 // Wait limit in clock ticks (<= 0: the default of about a second), idle suspend hint in ns, early scores on / off, and the
 // chunk the producers withhold (-1: none; makes every role's wait on it run out).
 extern "C" void fpb_debug_tuning(long long wait_cycles, int idle_ns, int sc_early, int withhold_chunk) {
