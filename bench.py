@@ -38,10 +38,10 @@ WORKLOADS = {
     "ns": dict(B=8, H=16, T=8192, dk=128, dv=128, block=0),
     "c3": dict(B=4, H=32, T=16384, dk=128, dv=256, block=0),
     "c4": dict(B=16, H=8, T=5120, dk=64, dv=64, block=80),
-    # a quarter of "ns" (still 4 x 67 MB of inputs, larger than L2): the case profiler captures run on
-    "small": dict(B=2, H=16, T=8192, dk=128, dv=128, block=0),
-    # one batch row of "c3" (0.8 GB of inputs), for the same purpose
-    "c3s": dict(B=1, H=32, T=16384, dk=128, dv=256, block=0),
+    # reduced cases for profiler captures: inputs still larger than L2, launches not under-filled (so the same kernels
+    # run unsplit), at most a few GB on the device
+    "small": dict(B=5, H=16, T=8192, dk=128, dv=128, block=0),
+    "c3s": dict(B=2, H=32, T=16384, dk=128, dv=256, block=0),
 }
 # the full RetNet stack under data parallelism: 12 layers, d_model 1024, global batch 64 x 4096 fixed (strong scaling)
 STACK = dict(layers=12, heads=8, head_dim=128, ffn=4096, vocab=32000, B=64, T=4096, micro_batch=32)
@@ -433,11 +433,24 @@ def run_stack(args):
         dist.destroy_process_group()
 
 
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the kernels captured with ncu, scaled to the
-# full workload by the token-heads processed where the capture ran on a reduced batch; null where there is no capture.
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the kernels as captured with ncu.  "ns" and
+# "c3" were captured on a reduced batch (5 of 8 and 2 of 4 rows: same kernels, launches not under-filled) and are scaled to
+# the full launch by the token-heads processed - traffic grows in proportion, every CTA streams its own sequence once.
+def _traffic(read_b, write_b, scale, what):
+    return {"bytes": (read_b + write_b) * scale, "source": what}
+
+
 NCU_TRAFFIC = {
-    ("ns", "rev"): {"bytes": 1073.8e6 + 506.3e6, "source": "ncu, B=2 capture scaled x4 by token-heads"},
-    ("ns", "fwd"): {"bytes": 1053.0e6, "source": "ncu, B=2 capture scaled x4 by token-heads"},
+    ("ns", "fwd"): _traffic(503386880, 146526464, 8 / 5, "ncu at B=5, scaled x8/5 by token-heads"),
+    ("ns", "dq"): _traffic(503442176, 144563200, 8 / 5, "ncu at B=5, scaled x8/5 by token-heads"),
+    ("ns", "rev"): _traffic(671172864, 305666816, 8 / 5, "ncu at B=5, scaled x8/5 by token-heads"),
+    ("c3", "fwd"): _traffic(1073834240, 507843072, 2, "ncu at B=2, scaled x2 by token-heads"),
+    ("c3", "dq"): _traffic(1343845376, 257063168, 2, "ncu at B=2, scaled x2 by token-heads"),
+    ("c3", "rev"): _traffic(1073828096 + 1343579904, 506655744 + 256747520, 2,
+                            "ncu at B=2 (the dV walk and the dK walk, two launches), scaled x2 by token-heads"),
+    ("c4", "fwd"): _traffic(251724032, 112299008, 1, "ncu at the full workload"),
+    ("c4", "dq"): _traffic(251713280, 60388096, 1, "ncu at the full workload"),
+    ("c4", "rev"): _traffic(335681536, 137153536, 1, "ncu at the full workload"),
 }
 
 

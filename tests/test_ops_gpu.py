@@ -50,7 +50,7 @@ def oracle_fwd_bwd(q, k, v, s, decays, dO, dS, chunk=64):
     return o, s_out, g
 
 
-# ---- BASELINE config 1: fp32, B=2,H=4,T=256,d=64, default decays, compared with the parallel form ----
+# ---- the CPU-runnable reference case: fp32, B=2,H=4,T=256,d=64, default decays, compared with the parallel form ----
 def test_config1_fp32_against_parallel_form():
     B, T, H, d = 2, 256, 4, 64
     decays = orc.head_decays(H)

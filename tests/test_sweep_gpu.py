@@ -8,7 +8,7 @@ from oracle import retention_oracle as orc
 
 pytestmark = pytest.mark.gpu
 BF = torch.bfloat16
-LIMIT = 6e-3      # single head, few tokens: the RMS is taken over far fewer elements than in the other tests
+LIMIT = 5e-3      # the reference's own criterion (tests/test_fused_retention.py:119,131); the worst case measured is 3.4e-3 (dK at T=13, d=64)
 
 
 def _inputs(T, d, seed):
