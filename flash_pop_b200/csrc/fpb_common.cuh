@@ -98,11 +98,12 @@ struct Segments {
 // segment start must be a multiple of; state_floats = dk * dv; scratch holds B*H*n*state_floats floats.
 Segments choose_segments(long long units, int ctas_per_sm, int T, int align, long long batch_heads, long long state_floats,
                          long long scratch_bytes, int B);
-// Start values of the segments from their local end values: in place over `seg` (B, H, n, dk, dv) fp32.
-//   forward : A_0 = start, A_{s+1} = gamma^len_s A_s + E_s ; seg[s] <- A_s ; end <- A_n
-//   reverse : A_{n-1} = start, A_{s-1} = gamma^len_s A_s + E_s ; seg[s] <- A_s ; end <- value carried past segment 0
+// Start values of the segments from the local end values of all but the piece reached last: in place over `seg`
+// (B, H, n, dk, dv) fp32.
+//   forward : A_0 = start, A_{s+1} = gamma^len_s A_s + E_s ; seg[s] <- A_s
+//   reverse : A_{n-1} = start, A_{s-1} = gamma^len_s A_s + E_s ; seg[s] <- A_s
 int launch_segment_combine(float* seg, Segments sg, int B, int T, int H, int dk, int dv, const float* gamma, bool reverse,
-                           StateView start, StateView end, bool state_f32, cudaStream_t stream);
+                           StateView start, bool state_f32, cudaStream_t stream);
 
 // Device status word shared by all kernels: 0 = fine; otherwise (role << 8 | barrier id) of the
 // first bounded wait that gave up.

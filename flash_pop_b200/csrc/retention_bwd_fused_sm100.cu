@@ -435,8 +435,9 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
       return p.sfx_blocks ? at(p.sfx_blocks, (((int64_t)sfx_row * p.sfx_N + (m - 1)) * p.H + h) * state_elems) : nullptr;
     };
     if (p.n_seg > 1) {
-      // T-segments: G after this piece's last token was put into fp32 scratch by the scan, which also wrote dS_0
+      // T-segments: G after this piece's last token was put into fp32 scratch by the scan; the first piece ends in dS_0
       x_start = p.seg_states + (((int64_t)b * p.H + h) * p.n_seg + seg) * state_elems;
+      if (seg == 0 && p.g_end) x_end = at(p.g_end, b * p.ge_sb + h * p.ge_sh);
     } else if (p.sfx_M > 0) {
       if (sfx_g == 1) x_end = sfx_grad(b % groups);    // grouped walks store at every suffix start, inside the loop
     } else {
@@ -703,7 +704,7 @@ int launch_bwd_fused(const UmmaBwdArgs& a, cudaStream_t stream, int* n_launched)
     if ((r = launch_segment_states(a.q, a.dO, true, a.d_block_states, a.gamma, B, T, H, a.dk, a.dv, a.block_size, a.n_blocks,
                                    a.state_f32, sg, a.scratch, stream)) != FPB_OK)
       return r;
-    if ((r = launch_segment_combine(a.scratch, sg, B, T, H, a.dk, a.dv, a.gamma, true, a.d_s_out, a.d_s0, a.state_f32, stream)) != FPB_OK)
+    if ((r = launch_segment_combine(a.scratch, sg, B, T, H, a.dk, a.dv, a.gamma, true, a.d_s_out, a.state_f32, stream)) != FPB_OK)
       return r;
     *n_launched += 2;
   }
@@ -717,7 +718,7 @@ int launch_bwd_fused(const UmmaBwdArgs& a, cudaStream_t stream, int* n_launched)
   p.dv_out = (bf16*)dV.data; p.dv_sb = dV.sb; p.dv_st = dV.st; p.dv_sh = dV.sh;
   const bool split = sg.n > 1;
   p.g_start = split ? nullptr : a.d_s_out.data; p.gs_sb = a.d_s_out.sb; p.gs_sh = a.d_s_out.sh;
-  p.g_end = split ? nullptr : a.d_s0.data; p.ge_sb = a.d_s0.sb; p.ge_sh = a.d_s0.sh;
+  p.g_end = a.d_s0.data; p.ge_sb = a.d_s0.sb; p.ge_sh = a.d_s0.sh;      // split: written by the piece the walk reaches last
   p.block_grads = a.d_block_states;
   p.sfx_blocks = a.sfx_grad.blocks; p.sfx_M = a.sfx_grad.M; p.sfx_N = a.sfx_grad.N; p.sfx_G = G;
   p.T = T; p.H = H; p.dk = a.dk; p.dv = a.dv; p.block_size = block_size; p.n_blocks = a.n_blocks;

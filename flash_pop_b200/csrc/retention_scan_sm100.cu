@@ -181,8 +181,11 @@ scan_kernel(const __grid_constant__ ScanParams p) {
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x, h = blockIdx.y;
-  const int b = p.n_seg > 1 ? (int)blockIdx.z / p.n_seg : (int)blockIdx.z;
-  const int seg = p.n_seg > 1 ? (int)blockIdx.z % p.n_seg : 0;
+  // (a STATE_ONLY pass covers all pieces but the one the walk reaches last - the last one forward, the first one in
+  // reverse - whose end value nobody needs ahead of time: the walk proper produces it)
+  const int nz = SO ? p.n_seg - 1 : p.n_seg;
+  const int b = p.n_seg > 1 ? (int)blockIdx.z / nz : (int)blockIdx.z;
+  const int seg = p.n_seg > 1 ? (int)blockIdx.z % nz + ((SO && REV) ? 1 : 0) : 0;
   // this CTA walks tokens [t0, t_end) of the sequence; chunk positions are absolute (t0 is a chunk and block multiple)
   const int t0 = seg * p.seg_len;
   const int t_end = p.n_seg > 1 ? min(t0 + p.seg_len, p.T) : p.T;
@@ -601,10 +604,13 @@ scan_kernel(const __grid_constant__ ScanParams p) {
     };
     if (SO || p.n_seg > 1) {
       // T-segments: a STATE_ONLY pass leaves the local end value in this segment's scratch slot; the walk proper
-      // starts from the value the scan put there and writes no end state (the scan did)
+      // starts from the value the scan put there, and the piece it reaches last ends in the call's end state
       float* slot = p.seg_states + (((int64_t)b * p.H + h) * p.n_seg + seg) * state_elems;
       if (SO) x_end = slot;
-      else x_start = slot;
+      else {
+        x_start = slot;
+        if (seg == (REV ? 0 : p.n_seg - 1) && p.s_out) x_end = at(p.s_out, b * p.so_sb + h * p.so_sh);
+      }
     } else if (p.sfx_M > 0) {
       const int row = sfx_row, m = sfx_m0;
       void* blk = (m > 0 && p.sfx_blocks) ? at(p.sfx_blocks, (((int64_t)row * p.sfx_N + (m - 1)) * p.H + h) * state_elems) : nullptr;
@@ -1005,9 +1011,9 @@ int launch_one(const PassArgs& a, Segments sg, bool state_only, cudaStream_t str
   if ((r = make_seq_map(&p.map_out, out, Bk, Tk, H, ow, 16)) != FPB_OK) return r;   // one score warp's 16 rows
   p.out = (bf16*)out.data; p.out_sb = out.sb; p.out_st = out.st; p.out_sh = out.sh;
   const bool split = sg.n > 1;
-  // a segmented walk starts from the scratch slots and leaves no end value (the scan wrote it)
+  // a segmented walk starts from the scratch slots; its last piece writes the end value
   p.s0 = split ? nullptr : a.start.data; p.s0_sb = a.start.sb; p.s0_sh = a.start.sh;
-  p.s_out = split ? nullptr : a.end.data; p.so_sb = a.end.sb; p.so_sh = a.end.sh;
+  p.s_out = state_only ? nullptr : a.end.data; p.so_sb = a.end.sb; p.so_sh = a.end.sh;
   p.block_states = state_only ? nullptr : a.block_states;
   p.block_grads = a.block_grads;
   p.sfx_blocks = a.sfx.blocks; p.sfx_M = a.sfx.M; p.sfx_N = a.sfx.N; p.sfx_G = G;
@@ -1026,7 +1032,7 @@ int launch_one(const PassArgs& a, Segments sg, bool state_only, cudaStream_t str
   for (int h = 0; h < H; ++h) p.log2g[h] = (float)std::log2((double)a.gamma[h]);
 
   const Tiling t = tiling_of(mode, dk, dv);
-  const dim3 grid(t.tiles, H, Bk * sg.n);
+  const dim3 grid(t.tiles, H, Bk * (state_only ? sg.n - 1 : sg.n));
 #define FPB_SCAN_CASE(MODE_, R_, CC_) \
   if (mode == MODE_ && t.R == R_ && t.CC == CC_) return launch_scan<MODE_, R_, CC_>(p, a.rev, state_only, grid, stream)
   FPB_SCAN_CASE(MODE_FWD, 128, 128); FPB_SCAN_CASE(MODE_FWD, 128, 64); FPB_SCAN_CASE(MODE_FWD, 64, 64);
@@ -1048,7 +1054,7 @@ int launch_pass(const PassArgs& a, cudaStream_t stream, int* n_launched) {
   int r;
   if (sg.n > 1) {
     if ((r = launch_one(a, sg, true, stream)) != FPB_OK) return r;
-    if ((r = launch_segment_combine(a.scratch, sg, a.B, a.T, a.H, a.dk, a.dv, a.gamma, a.rev, a.start, a.end, a.state_f32, stream)) != FPB_OK)
+    if ((r = launch_segment_combine(a.scratch, sg, a.B, a.T, a.H, a.dk, a.dv, a.gamma, a.rev, a.start, a.state_f32, stream)) != FPB_OK)
       return r;
     *n_launched += 2;
   }

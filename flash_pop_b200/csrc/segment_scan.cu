@@ -5,11 +5,11 @@
 // flash_pop/fused_retention/fused_chunk_fwd.py:119).  The retention recurrence is linear in the state,
 //     S_end = gamma^len S_start + E,   E = the end value of the same piece walked from a zero state,
 // so a sequence can be cut into n pieces that are walked concurrently:
-//   1. every piece computes its local end value E_s from a zero start (state-only instance of the scan kernel: it
-//      reads the two operands of the increment and nothing else) into fp32 scratch memory (B, H, n, dk, dv);
-//   2. this file's kernel scans the pieces of each (batch, head): A_0 = S_0, A_{s+1} = gamma^len_s A_s + E_s, writes
-//      A_s over E_s and the value after the last piece to the call's end state;
-//   3. the walk proper runs one CTA per piece from A_s.
+//   1. every piece but the last computes its local end value E_s from a zero start (state-only instance of the scan
+//      kernel: it reads the two operands of the increment and nothing else) into fp32 scratch memory (B, H, n, dk, dv);
+//   2. this file's kernel scans the pieces of each (batch, head): A_0 = S_0, A_{s+1} = gamma^len_s A_s + E_s, and
+//      writes A_s over E_s;
+//   3. the walk proper runs one CTA per piece from A_s; the last piece ends in the call's end state.
 // Reverse walks (the state gradient) are the mirror image: pieces are scanned from the last to the first.
 // Everything is deterministic; results differ from the unsplit walk by fp32 rounding of the state only.
 #include <atomic>
@@ -23,7 +23,6 @@ namespace {
 struct CombineParams {
   float* seg;
   const void* start; int64_t start_sb, start_sh;
-  void* end; int64_t end_sb, end_sh;
   int32_t n_seg, seg_len, T, H, reverse, state_f32;
   int64_t state_floats;
   float log2g[FPB_MAX_HEADS];
@@ -36,14 +35,6 @@ __device__ __forceinline__ float4 load4(const void* base, int64_t off, bool f32)
   const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
   return make_float4(a.x, a.y, b.x, b.y);
 }
-__device__ __forceinline__ void store4(void* base, int64_t off, bool f32, float4 v) {
-  if (f32) { *reinterpret_cast<float4*>((float*)base + off) = v; return; }
-  __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
-  uint2 raw;
-  raw.x = *reinterpret_cast<uint32_t*>(&lo); raw.y = *reinterpret_cast<uint32_t*>(&hi);
-  *reinterpret_cast<uint2*>((__nv_bfloat16*)base + off) = raw;
-}
-
 // grid (ceil(dk*dv / 4 / 256), H, B); one thread carries four adjacent state elements through the n pieces
 __global__ void __launch_bounds__(256) segment_combine_kernel(const __grid_constant__ CombineParams p) {
   const int64_t e = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 4;
@@ -55,14 +46,14 @@ __global__ void __launch_bounds__(256) segment_combine_kernel(const __grid_const
   if (p.start) a = load4(p.start, b * p.start_sb + h * p.start_sh + e, p.state_f32 != 0);
   for (int i = 0; i < p.n_seg; ++i) {
     const int s = p.reverse ? p.n_seg - 1 - i : i;
+    float4* slot = reinterpret_cast<float4*>(seg + (int64_t)s * p.state_floats);
+    if (i == p.n_seg - 1) { *slot = a; break; }      // the piece reached last has no local value: the walk itself ends it
     const int len = min(p.seg_len, p.T - s * p.seg_len);
     const float g = exp2f((float)len * lg);
-    float4* slot = reinterpret_cast<float4*>(seg + (int64_t)s * p.state_floats);
     const float4 loc = *slot;
     *slot = a;
     a.x = fmaf(g, a.x, loc.x); a.y = fmaf(g, a.y, loc.y); a.z = fmaf(g, a.z, loc.z); a.w = fmaf(g, a.w, loc.w);
   }
-  if (p.end) store4(p.end, b * p.end_sb + h * p.end_sh + e, p.state_f32 != 0, a);
 }
 
 int sm_count() {
@@ -107,11 +98,10 @@ Segments choose_segments(long long units, int ctas_per_sm, int T, int align, lon
 }
 
 int launch_segment_combine(float* seg, Segments sg, int B, int T, int H, int dk, int dv, const float* gamma, bool reverse,
-                           StateView start, StateView end, bool state_f32, cudaStream_t stream) {
+                           StateView start, bool state_f32, cudaStream_t stream) {
   CombineParams p;
   p.seg = seg;
   p.start = start.data; p.start_sb = start.sb; p.start_sh = start.sh;
-  p.end = end.data; p.end_sb = end.sb; p.end_sh = end.sh;
   p.n_seg = sg.n; p.seg_len = sg.seg_len; p.T = T; p.H = H; p.reverse = reverse ? 1 : 0; p.state_f32 = state_f32 ? 1 : 0;
   p.state_floats = (int64_t)dk * dv;
   for (int h = 0; h < H; ++h) p.log2g[h] = (float)std::log2((double)gamma[h]);
