@@ -40,9 +40,11 @@ def test_eight_pieces_with_fp32_state_equal_one_call(d):
     _lib.device_status()
     o_ref, s_ref = orc.retention_chunkwise(q.double(), k.double(), v.double(), None, decays, 64)
     check("O, fp32 hand-off", o32, o_ref, BF)
-    # the fp32 hand-off loses nothing: the state crosses the calls exactly as it sits in the registers of a single call
-    assert orc.rel_rms(s32.cpu(), s1.cpu().double()) < 1e-6
-    assert orc.rel_rms(o32.float().cpu(), o1.float().cpu().double()) < 1e-6
+    # the fp32 hand-off loses nothing: the state crosses the calls as it sits in the registers of a single call; what is
+    # left is the order of the fp32 additions (the calls cut their sequences into different T-segments) and, from that,
+    # a bf16 output here and there that rounds the other way
+    assert orc.rel_rms(s32.cpu(), s1.cpu().double()) < 1e-5
+    assert orc.rel_rms(o32.float().cpu(), o1.float().cpu().double()) < 5e-4
     # the bf16 hand-off rounds the state eight times on the way: further from the single call, still within tolerance
     d16 = orc.rel_rms(s16.float().cpu(), s1.cpu().double())
     assert 1e-4 < d16 < 5e-3, d16
