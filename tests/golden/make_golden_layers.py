@@ -85,6 +85,11 @@ def main(ref_root):
     fill_parameters(pnet)
     py, pst, psfx = pnet.pop_forward(x, RecurrentState([None] * d["layers"], 0), sfx)
     out.update(pop_y=py, pop_state=pst.state, pop_sfx=psfx)
+    # generation scenario (the reference's tests/test_pop_retention.py:161-196): one full block plus a partial one in a
+    # single sequence, and the suffixes that start from S_0 and from the one block state
+    Tg = d["block"] + 7
+    gy, gst, gsfx = pnet.pop_forward(x[:, :Tg], RecurrentState([None] * d["layers"], 0), sfx[:, :2])
+    out.update(popgen_y=gy, popgen_state=gst.state, popgen_sfx=gsfx)
 
     # diffusion stack + final layer
     dcfg = DiffusionRetNetDecoderLayer.Config(use_fused_version=False, chunk_size=16, **common)

@@ -95,6 +95,25 @@ def test_pop_stack_with_suffixes_matches_reference(gold):
     close("pop y without suffixes", y_only, gold["pop_y"])
 
 
+def test_pop_generation_scenario_matches_reference(gold):
+    """One full block plus a partial one in a single sequence and the two suffixes that start from S_0 and from the one
+    block state (the reference's generation scenario, tests/test_pop_retention.py:161-196), through
+    POPRetNetDecoder.pop_forward, against outputs of the reference's own stack."""
+    import flash_pop_b200 as fp
+    from flash_pop_b200 import _lib
+    h = _helpers()
+    d = h.DIMS
+    x, sfx, _ = h.inputs()
+    Tg = d["block"] + 7
+    net = fp.POPRetNetDecoder(fp.POPDecoderLayer.Config(block_size=d["block"], head_decays_range=(5, 12), **_common(h)), d["layers"])
+    h.fill_parameters(net)
+    with torch.no_grad():
+        y, st, out_sfx = net.pop_forward(x[:, :Tg].cuda(), None, sfx[:, :2].cuda())
+    _lib.device_status()
+    close("generation y", y, gold["popgen_y"]), close("generation carried state", st.state, gold["popgen_state"])
+    close("generation suffixes", out_sfx, gold["popgen_sfx"])
+
+
 def test_pop_stack_trains(gold):
     """Gradients reach the weights through both POP operators (stream and suffixes)."""
     import flash_pop_b200 as fp
