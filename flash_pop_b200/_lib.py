@@ -144,6 +144,7 @@ _DIAG_SIGNATURES = {
     "fpb_debug_fused_bwd": [ctypes.c_int],
     "fpb_debug_segments": [ctypes.c_int],
     "fpb_debug_deep": [ctypes.c_int],
+    "fpb_debug_ablate": [ctypes.c_int],
     "fpb_debug_tuning": [ctypes.c_longlong, ctypes.c_int, ctypes.c_int, ctypes.c_int],
 }
 

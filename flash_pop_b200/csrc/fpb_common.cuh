@@ -87,6 +87,7 @@ struct WalkTuning {
   int32_t idle_ns;          // suspend hint (ns) of a polling loop that found nothing to do
   int32_t sc_early;         // walks whose scores do not read the scaled tile issue them as soon as the tiles landed
   int32_t withhold_chunk;   // diagnostics only: the producer never loads this chunk of any sequence (-1 = none)
+  int32_t ablate;           // diagnostics only: bit mask of work to leave out (results are then wrong; timing experiments)
 };
 const WalkTuning& walk_tuning();
 

@@ -73,7 +73,10 @@ struct BCfg {
   static constexpr int DMAX = DK > DV ? DK : DV;
   static constexpr int STATE_WARPS = DK * DV >= 128 * 128 ? 8 : 4;
   static constexpr int N_STATE = 32 * STATE_WARPS;
-  static constexpr int NTHREADS = STATE_WARP0 * 32 + N_STATE;
+  // the 128 x 128 instance issues its seven product groups from two warps (see the MMA issuer); the second is the last warp
+  static constexpr bool SPLIT = DK * DV >= 128 * 128;
+  static constexpr int MMAB_WARP = STATE_WARP0 + STATE_WARPS;
+  static constexpr int NTHREADS = STATE_WARP0 * 32 + N_STATE + (SPLIT ? 32 : 0);
   static constexpr int Q_BYTES = C * DK * 2, V_BYTES = C * DV * 2;           // Q and K tiles; V and dO tiles
   static constexpr int STAGE_BYTES = 2 * Q_BYTES + 2 * V_BYTES;
   static constexpr int OFF_Q = 0, OFF_K = Q_BYTES, OFF_V = 2 * Q_BYTES, OFF_DO = 2 * Q_BYTES + V_BYTES;   // inside a stage
@@ -141,7 +144,7 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
   auto tm_dg = [&](int n) { return DK == 128 ? (uint32_t)(G::TM_DG + (n & 1) * DV) : (uint32_t)G::TM_DG + lanes16(n & 1); };
 
   if (tid == 0) {
-    for (int s = 0; s < G::STAGES; ++s) { mbar_init(bar(B_FULL + s), 1); mbar_init(bar(B_EMPTY + s), 1); mbar_init(bar(B_VRDY + s), G::N_STATE); }
+    for (int s = 0; s < G::STAGES; ++s) { mbar_init(bar(B_FULL + s), 1); mbar_init(bar(B_EMPTY + s), G::SPLIT ? 2 : 1); mbar_init(bar(B_VRDY + s), G::N_STATE); }
     for (int j = 0; j < 2; ++j) {
       mbar_init(bar(B_SCFULL + j), 1); mbar_init(bar(B_PRDY + j), N_SCORE);
       mbar_init(bar(B_DSFULL + j), 1); mbar_init(bar(B_DSFREE + j), G::N_STATE);
@@ -195,7 +198,11 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
         }
       }
     }
-  } else if (warp == 1) {                            // ---------------- MMA issuer (warp-uniform, one elected lane)
+  } else if (warp == 1 || (G::SPLIT && warp == G::MMAB_WARP)) {   // ---------------- MMA issuer(s) (warp-uniform, one elected lane)
+    // The issuing thread is the walk's pacemaker (seven product groups, each with its barrier tests, descriptor
+    // arithmetic and commit), so the 128 x 128 instance splits them over two warps along the line that needs no ordering
+    // between them: warp A issues what depends on the tiles alone (both score products, the increment), warp B the
+    // accumulator products (state terms, then intra-chunk terms).  A stage is released when both have committed.
     if (NC > 0) {
       const bool leader = elect_one();
       constexpr uint32_t ID_SC = idesc_bf16(64, 64, 0, 0);
@@ -215,15 +222,28 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
       auto kstep = [](int ks, uint32_t cb_stride) { return (uint64_t)((ks >> 2) * (cb_stride >> 4) + (ks & 3) * 2); };
       auto mstep = [](int ks) { return (uint64_t)(ks * 128); };
       auto ready = [&](int slot, uint32_t parity) { return __all_sync(0xffffffffu, mbar_test_wait(bar(slot), parity)) != 0; };
-      int n_sc = 0, n_ds = 0, n_qs = 0, n_pv = 0, n_rel = 0, n_data = 0;
+      auto issue_loop = [&](auto do_a, auto do_b) {
+      constexpr bool DO_A = decltype(do_a)::value, DO_B = decltype(do_b)::value;
+      int n_sc = 0, n_ds = 0, n_qs = 0, n_pv = 0, n_rel = 0, n_data = 0, n_pdone = 0;
       auto data_ready = [&](int n) {     // "dO scaled" implies "tiles landed"; each phase is tested until seen once
         if (n < n_data) return true;
         if (!ready(B_VRDY + stage_of(n_data), stage_ph(n_data))) return false;
         ++n_data;
         return n < n_data;
       };
+      // score buffers n & 1 are free once P1/P2 of chunk n - 2 were taken out: the warp that issues the intra terms knows it
+      // from its own counter; warp A alone tests the P' barrier (two P' buffers, so the phase is unambiguous)
+      auto score_tiles_free = [&](int n) {
+        if constexpr (DO_A && DO_B) return n < n_pv + 2;
+        else {
+          if (n < 2 || n - 2 < n_pdone) return true;
+          if (!ready(B_PRDY + (n_pdone & 1), (n_pdone >> 1) & 1)) return false;
+          ++n_pdone;
+          return n - 2 < n_pdone;
+        }
+      };
       auto release = [&]() {
-        while (n_rel < n_pv && n_rel < n_ds && n_rel < n_sc) {
+        while ((!DO_B || n_rel < n_pv) && (!DO_A || (n_rel < n_ds && n_rel < n_sc))) {
           if (leader) { umma_commit(bar(B_EMPTY + stage_of(n_rel))); FPB_TRACE(5, n_rel); }
           ++n_rel;
         }
@@ -232,7 +252,7 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
       while (n_rel < NC) {
         bool progress = false;
         // scores of chunk n into buffers n & 1; free once P1/P2 of chunk n-2 were taken out (seen by its intra terms)
-        if (n_sc < NC && n_sc < n_pv + 2 && data_ready(n_sc)) {
+        if (DO_A && n_sc < NC && score_tiles_free(n_sc) && data_ready(n_sc)) {
           const uint64_t so = (uint64_t)(stage_of(n_sc) * STAGE16);
           tc_fence_after();
           if (leader) {
@@ -246,7 +266,7 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
           ++n_sc; progress = true;
         }
         // increment dG = Q^T dOz into buffer n & 1
-        if (n_ds < NC && data_ready(n_ds) && (n_ds < 2 || ready(B_DSFREE + (n_ds & 1), ((n_ds >> 1) & 1) ^ 1))) {
+        if (DO_A && n_ds < NC && data_ready(n_ds) && (n_ds < 2 || ready(B_DSFREE + (n_ds & 1), ((n_ds >> 1) & 1) ^ 1))) {
           const uint64_t so = (uint64_t)(stage_of(n_ds) * STAGE16);
           tc_fence_after();
           if (leader) {
@@ -259,7 +279,7 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
           release();
         }
         // state terms ACCV = K Gb, ACCK = V Gb^T (one accumulator pair: wait until the previous epilogue has read it)
-        if (n_qs < NC && data_ready(n_qs) && (n_qs == 0 || ready(B_ACCFREE, (n_qs & 1) ^ 1)) && ready(B_SBRDY, n_qs & 1)) {
+        if (DO_B && n_qs < NC && data_ready(n_qs) && (n_qs == 0 || ready(B_ACCFREE, (n_qs & 1) ^ 1)) && ready(B_SBRDY, n_qs & 1)) {
           const uint64_t so = (uint64_t)(stage_of(n_qs) * STAGE16);
           tc_fence_after();
           if (leader) {
@@ -273,7 +293,7 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
           ++n_qs; progress = true;
         }
         // intra-chunk terms ACCV += P1 dOz, ACCK += P2 Q
-        if (n_pv < n_qs && ready(B_PRDY + (n_pv & 1), (n_pv >> 1) & 1)) {
+        if (DO_B && n_pv < n_qs && ready(B_PRDY + (n_pv & 1), (n_pv >> 1) & 1)) {
           const uint64_t so = (uint64_t)(stage_of(n_pv) * STAGE16);
           const uint64_t po = (uint64_t)((n_pv & 1) * (G::P_BYTES >> 4));
           tc_fence_after();
@@ -288,9 +308,17 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
           ++n_pv; progress = true;
           release();
         }
+        release();      // (warp A may issue the scores of a chunk after its increment: nothing else would release then)
         if (progress) patience.progress();
-        else if (__any_sync(0xffffffffu, patience.exhausted(abort_flag))) { if (leader) FPB_GIVE_UP(0x200 | (n_pv & 0xff)); break; }
+        else if (__any_sync(0xffffffffu, patience.exhausted(abort_flag))) {
+          if (leader) FPB_GIVE_UP((DO_A ? 0x200 : 0x500) | ((DO_A ? n_ds : n_pv) & 0xff));
+          break;
+        }
       }
+      };
+      if (!G::SPLIT) issue_loop(std::true_type{}, std::true_type{});
+      else if (warp == 1) issue_loop(std::true_type{}, std::false_type{});
+      else issue_loop(std::false_type{}, std::true_type{});
     }
   } else if (warp < STATE_WARP0) {                   // ---------------- score warps
     const int t = tid - SCORE_WARP0 * 32;            // 0..127
@@ -402,7 +430,7 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
       }
       if (t == 0) tma_store_wait_all0();
     }
-  } else {                                           // ---------------- state warps
+  } else if (warp < STATE_WARP0 + G::STATE_WARPS) {  // ---------------- state warps
     const int t = tid - STATE_WARP0 * 32;
     const int q4 = warp & 3;
     const int half = (warp - STATE_WARP0) >> 2;

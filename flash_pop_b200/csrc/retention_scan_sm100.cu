@@ -68,6 +68,13 @@ using namespace ptx;
 using namespace scan;
 typedef __nv_bfloat16 bf16;
 
+// The tcgen05.mma issue loops (4-8 k-steps each) are fully unrolled unless an experiment build says otherwise.
+#ifdef FPB_EXP_SMALL_MMA
+#define FPB_UNROLL_MMA _Pragma("unroll 1")
+#else
+#define FPB_UNROLL_MMA _Pragma("unroll")
+#endif
+
 constexpr int MODE_FWD = 0, MODE_DQ = 1;
 constexpr int SCORE_WARP0 = 2, STATE_WARP0 = 6;
 constexpr int N_SCORE = 128;
@@ -99,8 +106,8 @@ struct ScanParams {
 // ones - then two 4-byte words and the wait limit
 constexpr int MAXS = 6;          // most stages a configuration may have
 enum { B_FULL = 0, B_EMPTY = MAXS, B_VRDY = 2 * MAXS, B_SCFULL = 3 * MAXS, B_PRDY = B_SCFULL + 2, B_ACCFULL = B_PRDY + 2,
-       B_ACCFREE = B_ACCFULL + 2, B_DSFULL = B_ACCFREE + 2, B_DSFREE = B_DSFULL + 2, B_SBRDY = B_DSFREE + 2, B_SBFREE = B_SBRDY + 1,
-       B_DSPFULL = B_SBFREE + 1, B_DSPFREE = B_DSPFULL + 1, B_COUNT = B_DSPFREE + 1 };
+       B_ACCFREE = B_ACCFULL + 2, B_DSFULL = B_ACCFREE + 2, B_DSFREE = B_DSFULL + 2, B_SBRDY = B_DSFREE + 2, B_SBFREE = B_SBRDY + 2,
+       B_DSPFULL = B_SBFREE + 2, B_DSPFREE = B_DSPFULL + 1, B_COUNT = B_DSPFREE + 1 };
 constexpr int OFF_TMEM_SLOT = B_COUNT * 8, OFF_ABORT = OFF_TMEM_SLOT + 4, OFF_LIMIT = OFF_ABORT + 4, BAR_PAGE = 512;
 static_assert(OFF_LIMIT % 8 == 0 && OFF_LIMIT + 8 <= BAR_PAGE, "the wait limit sits right after the abort flag");
 
@@ -120,15 +127,22 @@ struct Cfg {
   static constexpr bool SOLO = ONE || DEEP;                  // one CTA per SM
   static constexpr int STATE_WARPS = ONE ? 8 : 4;
   static constexpr int N_STATE = 32 * STATE_WARPS;
-  static constexpr int NTHREADS = STATE_WARP0 * 32 + N_STATE;
+  // one-CTA-per-SM configurations issue their products from two warps (see the MMA issuer in the kernel); the second
+  // one is the CTA's last warp
+  static constexpr bool SPLIT = ONE;      // (the deep 64 x 64 variant lost 7 % with it)
+  static constexpr int MMAB_WARP = STATE_WARP0 + STATE_WARPS;
+  static constexpr int NTHREADS = STATE_WARP0 * 32 + N_STATE + (SPLIT ? 32 : 0);
   static constexpr int MIN_CTAS = SOLO ? 1 : 2;
   static constexpr int NP = SOLO ? 2 : 1;                    // P' buffers
   static constexpr int X_BYTES = C * W1 * 2, K_BYTES = C * R * 2, V_BYTES = C * CC * 2;
   static constexpr int STAGE_BYTES = X_BYTES + K_BYTES + V_BYTES;
   static constexpr int P_BYTES = C * C * 2;
   static constexpr int SB_BYTES = R * CC * 2;
+  // bf16 copies of the state.  Two (so that the copy for chunk n + 1 need not wait for the state-term product of chunk
+  // n to finish reading) fit only next to the small tiles, where they measured no gain: one.
+  static constexpr int NSB = 1;
   static constexpr int OUT_BYTES = C * NOUT * 2;
-  static constexpr int FIXED = NP * P_BYTES + SB_BYTES + OUT_BYTES + BAR_PAGE;
+  static constexpr int FIXED = NP * P_BYTES + NSB * SB_BYTES + OUT_BYTES + BAR_PAGE;
   static constexpr int SMEM_LIMIT = SOLO ? 226 * 1024 : 115712;  // (233472 B per SM) / 2 - 1 KB system reserve
   static constexpr int FIT = (SMEM_LIMIT - FIXED) / STAGE_BYTES;
   static constexpr int STAGES = DEEP ? (FIT < MAXS ? FIT : MAXS) : (FIT >= 3 ? 3 : 2);
@@ -136,7 +150,7 @@ struct Cfg {
   static constexpr int OFF_STAGE = 0;
   static constexpr int OFF_P = STAGES * STAGE_BYTES;
   static constexpr int OFF_SB = OFF_P + NP * P_BYTES;
-  static constexpr int OFF_OUT = OFF_SB + SB_BYTES;
+  static constexpr int OFF_OUT = OFF_SB + NSB * SB_BYTES;
   static constexpr int OFF_BAR = OFF_OUT + OUT_BYTES;
   static constexpr int SMEM = OFF_BAR + BAR_PAGE;
   static_assert(SMEM <= SMEM_LIMIT, "shared memory budget");
@@ -195,6 +209,9 @@ scan_kernel(const __grid_constant__ ScanParams p) {
   const float rs = rsqrtf((float)p.dk);
   const int NC = chunk_count(t_end - t0, p.sched_bs);
   auto bar = [&](int slot) { return sbase + G::OFF_BAR + slot * 8; };
+  constexpr int ARR_SCORE = N_SCORE, ARR_STATE = G::N_STATE;   // every thread of a role arrives (one elected lane per warp
+                                                                // after a warp sync was measured: no faster)
+  auto warp_arrive = [&](uint32_t b_) { mbar_arrive(b_); };
   auto stage_of = [&](int n) { return n % G::STAGES; };
   auto stage_ph = [&](int n) { return (uint32_t)((n / G::STAGES) & 1); };
   // tensor-memory address (lane offset in the upper half-word) of buffer n & 1 of each accumulator kind
@@ -203,14 +220,16 @@ scan_kernel(const __grid_constant__ ScanParams p) {
   auto tm_ds = [&](int n) { return R == 128 ? (uint32_t)(G::TM_DS + (n & 1) * CC) : (uint32_t)(G::TM_DS + ((n & 1) ? (16u << 16) : 0u)); };
 
   if (tid == 0) {
-    for (int s = 0; s < G::STAGES; ++s) { mbar_init(bar(B_FULL + s), 1); mbar_init(bar(B_EMPTY + s), 1); mbar_init(bar(B_VRDY + s), G::N_STATE); }
-    for (int j = 0; j < 2; ++j) {
-      mbar_init(bar(B_SCFULL + j), 1); mbar_init(bar(B_PRDY + j), N_SCORE);
-      mbar_init(bar(B_ACCFULL + j), 1); mbar_init(bar(B_ACCFREE + j), N_SCORE);
+    for (int s = 0; s < G::STAGES; ++s) {
+      mbar_init(bar(B_FULL + s), 1); mbar_init(bar(B_EMPTY + s), (G::SPLIT && !SO) ? 2 : 1); mbar_init(bar(B_VRDY + s), ARR_STATE);
     }
-    for (int j = 0; j < 2; ++j) { mbar_init(bar(B_DSFULL + j), 1); mbar_init(bar(B_DSFREE + j), G::N_STATE); }
-    mbar_init(bar(B_SBRDY), G::N_STATE); mbar_init(bar(B_SBFREE), 1);
-    mbar_init(bar(B_DSPFULL), 1); mbar_init(bar(B_DSPFREE), G::N_STATE);
+    for (int j = 0; j < 2; ++j) {
+      mbar_init(bar(B_SCFULL + j), 1); mbar_init(bar(B_PRDY + j), ARR_SCORE);
+      mbar_init(bar(B_ACCFULL + j), 1); mbar_init(bar(B_ACCFREE + j), ARR_SCORE);
+    }
+    for (int j = 0; j < 2; ++j) { mbar_init(bar(B_DSFULL + j), 1); mbar_init(bar(B_DSFREE + j), ARR_STATE); }
+    for (int j = 0; j < 2; ++j) { mbar_init(bar(B_SBRDY + j), ARR_STATE); mbar_init(bar(B_SBFREE + j), 1); }
+    mbar_init(bar(B_DSPFULL), 1); mbar_init(bar(B_DSPFREE), ARR_STATE);
     fence_mbar_init();
     *abort_flag = 0;
     *reinterpret_cast<volatile long long*>(sm + G::OFF_BAR + OFF_LIMIT) = p.tune.wait_cycles;
@@ -265,10 +284,18 @@ scan_kernel(const __grid_constant__ ScanParams p) {
         }
       }
     }
-  } else if (warp == 1) {                            // ---------------- MMA issuer
+  } else if (warp == 1 || (G::SPLIT && warp == G::MMAB_WARP)) {   // ---------------- MMA issuer(s)
     // The whole warp runs this loop with warp-uniform control flow and data (barrier tests are made uniform by a
     // vote), so that descriptors and counters stay in the uniform datapath; one elected lane issues.
-    if (NC > 0) {
+    //
+    // A chunk is four product groups - scores, increment, state term, intra-chunk term - and the thread that issues them
+    // is the walk's pacemaker: about 3000 cycles of barrier tests, descriptor arithmetic, tcgen05.mma and commits per
+    // chunk, more than the chunk's HBM time.  The one-CTA-per-SM configurations therefore split the issue over TWO
+    // warps along the only line that needs no ordering between them: warp A issues the products that depend on the
+    // tiles alone (scores, increment), warp B the two accumulator products (state term, then intra-chunk term, in that
+    // order on the same accumulator).  A stage goes back to the producer when both have committed their last product
+    // of its chunk.
+    if (NC > 0 && !(SO && warp != 1)) {
       const bool leader = elect_one();
       constexpr uint32_t ID_SC = idesc_bf16(64, 64, 0, 0);
       constexpr uint32_t ID_STATE = MODE == MODE_FWD ? idesc_bf16(64, CC, 0, 1) : idesc_bf16(64, R, 0, 0);
@@ -289,129 +316,171 @@ scan_kernel(const __grid_constant__ ScanParams p) {
       const uint64_t d_p = smem_desc(sbase + G::OFF_P, 16, 1024);                                       // P', K-major
       auto kstep = [](int ks, uint32_t cb_stride) { return (uint64_t)((ks >> 2) * (cb_stride >> 4) + (ks & 3) * 2); };
       auto mstep = [](int ks) { return (uint64_t)(ks * 128); };
-      auto ready = [&](int slot, uint32_t parity) { return __all_sync(0xffffffffu, mbar_test_wait(bar(slot), parity)) != 0; };
-      // Next chunk to issue for each of the four products, and the next stage to hand back to the producer.
-      // Each product of chunk n is issued when its inputs are there; the tensor pipe runs them in issue order.
-      int n_sc = 0, n_ds = 0, n_qs = 0, n_pv = 0, n_rel = 0;
-      int n_dsp = (emit && !SO) ? 0 : 0x7fffffff, m_dsp = 0;   // chunks whose partial increment is settled; partials issued
-      // a stage goes back to the producer as soon as all four products of its chunk have been issued (issuing
-      // blocks while the tensor pipe is busy, so this is checked after every group, not once per round)
-      auto release = [&]() {
-        while ((SO || (n_rel < n_pv && n_rel < n_sc)) && n_rel < n_ds && n_rel < n_dsp) {
-          if (leader) { umma_commit(bar(B_EMPTY + stage_of(n_rel))); FPB_TRACE(5, n_rel); }
-          ++n_rel;
-        }
+      FPB_PROF_DECL();
+      auto ready = [&](int slot, uint32_t parity) {
+        FPB_PROF_BEGIN();
+        const bool ok = __all_sync(0xffffffffu, mbar_test_wait(bar(slot), parity)) != 0;
+        FPB_PROF_END(0);
+        return ok;
       };
-      // A barrier test costs this thread on the order of a hundred cycles while the tensor pipe is streaming
-      // operands out of shared memory, so each barrier phase is tested until it has been seen complete once and
-      // never again.  "V scaled" implies "tiles landed" (the state warps waited for them), so the products wait
-      // for that one barrier only.
-      int n_data = 0, n_full = 0;
-      auto data_ready = [&](int n) {
-        if (n < n_data) return true;
-        if (!ready(B_VRDY + stage_of(n_data), stage_ph(n_data))) return false;
-        ++n_data;
-        return n < n_data;
-      };
-      // The scores of a MODE_FWD walk read X and K only, not the tile the state warps rescale in place: they may go
-      // as soon as the copies have landed, so that the chain scores -> P' -> intra-chunk term starts a rescaling early.
-      auto scores_ready = [&](int n) {
-        if (MODE != MODE_FWD || !p.tune.sc_early) return data_ready(n);
-        if (n < n_data || n < n_full) return true;
-        if (n_full < n_data) n_full = n_data;
-        if (!ready(B_FULL + stage_of(n_full), stage_ph(n_full))) return false;
-        ++n_full;
-        return n < n_full;
-      };
-      Patience patience{0, 0};
-      while (n_rel < NC) {             // until every product of every chunk has been issued
-        bool progress = false;
-        // Order of the tests = priority: the products that feed the longest chains first (scores -> P' -> intra term;
-        // increment -> state -> next chunk's state term).
-        // scores Sc = X K^T (FWD) | X Veta^T (DQ); its buffer is free once P' of chunk n - NSC has been taken out,
-        // which the intra-chunk term of that chunk has waited for
-        if (!SO && n_sc < NC && n_sc < n_pv + G::NSC && scores_ready(n_sc)) {
-          const uint64_t so = (uint64_t)(stage_of(n_sc) * STAGE16);
-          tc_fence_after();
-          const uint32_t d = tm + tm_sc(n_sc);
-          const uint64_t bk = (MODE == MODE_FWD ? d_kk : d_vk) + so;
-          if (leader) {
-#pragma unroll
-            for (int ks = 0; ks < G::W1 / 16; ++ks) umma_bf16(d, d_x + so + kstep(ks, 8192), bk + kstep(ks, 8192), ID_SC, ks > 0);
-            umma_commit(bar(B_SCFULL + n_sc % G::NSC));
-            FPB_TRACE(0, n_sc);
+      // DO_A: this warp issues scores and increment (and the POP partial increments); DO_B: state and intra-chunk terms
+      auto issue_loop = [&](auto do_a, auto do_b) {
+        constexpr bool DO_A = decltype(do_a)::value, DO_B = decltype(do_b)::value;
+        constexpr bool BOTH = DO_A && DO_B;
+        // Next chunk to issue for each of the four products, and the next stage to hand back to the producer.
+        // Each product of chunk n is issued when its inputs are there; the tensor pipe runs them in issue order.
+        int n_sc = 0, n_ds = 0, n_qs = 0, n_pv = 0, n_rel = 0;
+        int n_dsp = (emit && !SO) ? 0 : 0x7fffffff, m_dsp = 0;   // chunks whose partial increment is settled; partials issued
+        // a stage goes back to the producer as soon as this warp's products of its chunk have been issued (issuing
+        // blocks while the tensor pipe is busy, so this is checked after every group, not once per round)
+        auto release = [&]() {
+          while ((!DO_B || SO || n_rel < n_pv) && (!DO_A || ((SO || n_rel < n_sc) && n_rel < n_ds && n_rel < n_dsp))) {
+            if (leader) { { FPB_PROF_BEGIN(); umma_commit(bar(B_EMPTY + stage_of(n_rel))); FPB_PROF_END(1); } FPB_TRACE(5, n_rel); }
+            ++n_rel;
           }
-          ++n_sc; progress = true;
-        }
-        // state increment dS = K^T Veta: depends on no other product and feeds the only chunk-to-chunk dependency
-        if (n_ds < NC && data_ready(n_ds) && (n_ds < 2 || ready(B_DSFREE + (n_ds & 1), ((n_ds >> 1) & 1) ^ 1))) {
-          const uint64_t so = (uint64_t)(stage_of(n_ds) * STAGE16);
-          tc_fence_after();
-          if (leader) {
-#pragma unroll
-            for (int ks = 0; ks < C / 16; ++ks) umma_bf16(tm + tm_ds(n_ds), d_km + so + mstep(ks), d_vm + so + mstep(ks), ID_DS, ks > 0);
-            umma_commit(bar(B_DSFULL + (n_ds & 1)));
-            FPB_TRACE(4, n_ds);
+        };
+        // A barrier test costs this thread on the order of a hundred cycles while the tensor pipe is streaming
+        // operands out of shared memory, so each barrier phase is tested until it has been seen complete once and
+        // never again.  "V scaled" implies "tiles landed" (the state warps waited for them), so the products wait
+        // for that one barrier only.
+        int n_data = 0, n_full = 0, n_pdone = 0;
+        auto data_ready = [&](int n) {
+          if (n < n_data) return true;
+          if (!ready(B_VRDY + stage_of(n_data), stage_ph(n_data))) return false;
+          ++n_data;
+          return n < n_data;
+        };
+        // The scores of a MODE_FWD walk read X and K only, not the tile the state warps rescale in place: they may go
+        // as soon as the copies have landed, so that the chain scores -> P' -> intra-chunk term starts a rescaling early.
+        auto scores_ready = [&](int n) {
+          if (MODE != MODE_FWD || !p.tune.sc_early) return data_ready(n);
+          if (n < n_data || n < n_full) return true;
+          if (n_full < n_data) n_full = n_data;
+          if (!ready(B_FULL + stage_of(n_full), stage_ph(n_full))) return false;
+          ++n_full;
+          return n < n_full;
+        };
+        // The score tile of chunk n may be overwritten once P' of chunk n - NSC has been taken out of it.  The warp that
+        // also issues the intra-chunk terms knows that from its own counter (that term waited for P'); warp A alone
+        // tests the P' barrier itself (NP == NSC in the split configurations, so the phase is unambiguous).
+        auto score_tile_free = [&](int n) {
+          if constexpr (BOTH) return n < n_pv + G::NSC;
+          else {
+            if (n < G::NSC || n - G::NSC < n_pdone) return true;
+            if (!ready(B_PRDY + n_pdone % G::NP, (n_pdone / G::NP) & 1)) return false;
+            ++n_pdone;
+            return n - G::NSC < n_pdone;
           }
-          ++n_ds; progress = true;
-          release();
-        }
-        // EMIT: partial increment of the chunk whose full increment has just been issued (same operands, first k-steps)
-        if (G::EMIT && !SO && n_dsp < n_ds) {
-          const int pmid = mid_end(n_dsp);
-          if (pmid == 0) { ++n_dsp; progress = true; release(); }
-          else if (m_dsp == 0 || ready(B_DSPFREE, (m_dsp - 1) & 1)) {
-            const uint64_t so = (uint64_t)(stage_of(n_dsp) * STAGE16);
-            tc_fence_after();
+        };
+        Patience patience{0, 0};
+        while (n_rel < NC) {             // until every product of this warp for every chunk has been issued
+          bool progress = false;
+          // Order of the tests = priority: the products that feed the longest chains first (scores -> P' -> intra term;
+          // increment -> state -> next chunk's state term).
+          // scores Sc = X K^T (FWD) | X Veta^T (DQ)
+          if (DO_A && !SO && n_sc < NC && score_tile_free(n_sc) && scores_ready(n_sc)) {
+            const uint64_t so = (uint64_t)(stage_of(n_sc) * STAGE16);
+            { FPB_PROF_BEGIN(); tc_fence_after(); FPB_PROF_END(3); }
+            const uint32_t d = tm + tm_sc(n_sc);
+            const uint64_t bk = (MODE == MODE_FWD ? d_kk : d_vk) + so;
             if (leader) {
-              for (int ks = 0; ks < pmid / 16; ++ks) umma_bf16(tm + G::TM_DSP, d_km + so + mstep(ks), d_vm + so + mstep(ks), ID_DS, ks > 0);
-              umma_commit(bar(B_DSPFULL));
+              FPB_PROF_BEGIN();
+FPB_UNROLL_MMA
+              for (int ks = 0; ks < (FPB_ABL(32) ? 1 : G::W1 / 16); ++ks) umma_bf16(d, d_x + so + kstep(ks, 8192), bk + kstep(ks, 8192), ID_SC, ks > 0);
+              FPB_PROF_END(2);
+              { FPB_PROF_BEGIN(); umma_commit(bar(B_SCFULL + n_sc % G::NSC)); FPB_PROF_END(1); }
+              FPB_TRACE(0, n_sc);
             }
-            ++m_dsp; ++n_dsp; progress = true;
+            ++n_sc; progress = true;
+          }
+          // state increment dS = K^T Veta: depends on no other product and feeds the only chunk-to-chunk dependency
+          if (DO_A && n_ds < NC && data_ready(n_ds) && (n_ds < 2 || ready(B_DSFREE + (n_ds & 1), ((n_ds >> 1) & 1) ^ 1))) {
+            const uint64_t so = (uint64_t)(stage_of(n_ds) * STAGE16);
+            { FPB_PROF_BEGIN(); tc_fence_after(); FPB_PROF_END(3); }
+            if (leader) {
+              FPB_PROF_BEGIN();
+FPB_UNROLL_MMA
+              for (int ks = 0; ks < (FPB_ABL(32) ? 1 : C / 16); ++ks) umma_bf16(tm + tm_ds(n_ds), d_km + so + mstep(ks), d_vm + so + mstep(ks), ID_DS, ks > 0);
+              FPB_PROF_END(2);
+              { FPB_PROF_BEGIN(); umma_commit(bar(B_DSFULL + (n_ds & 1))); FPB_PROF_END(1); }
+              FPB_TRACE(4, n_ds);
+            }
+            ++n_ds; progress = true;
             release();
           }
-        }
-        // state term: ACC = X Sb (FWD) | X Sb^T (DQ)
-        if (!SO && n_qs < NC && data_ready(n_qs) && (n_qs < G::NACC || ready(B_ACCFREE + n_qs % G::NACC, ((n_qs / G::NACC) & 1) ^ 1)) &&
-            ready(B_SBRDY, n_qs & 1)) {
-          const uint64_t so = (uint64_t)(stage_of(n_qs) * STAGE16);
-          if (leader) FPB_TRACE(2, n_qs);
-          tc_fence_after();
-          const uint32_t acc = tm + tm_acc(n_qs);
-          if (leader) {
-            if (MODE == MODE_FWD) {
-#pragma unroll
-              for (int ks = 0; ks < R / 16; ++ks) umma_bf16(acc, d_x + so + kstep(ks, 8192), d_sb + mstep(ks), ID_STATE, ks > 0);
-            } else {
-#pragma unroll
-              for (int ks = 0; ks < CC / 16; ++ks) umma_bf16(acc, d_x + so + kstep(ks, 8192), d_sb + kstep(ks, R * 128), ID_STATE, ks > 0);
+          // EMIT: partial increment of the chunk whose full increment has just been issued (same operands, first k-steps)
+          if (DO_A && G::EMIT && !SO && n_dsp < n_ds) {
+            const int pmid = mid_end(n_dsp);
+            if (pmid == 0) { ++n_dsp; progress = true; release(); }
+            else if (m_dsp == 0 || ready(B_DSPFREE, (m_dsp - 1) & 1)) {
+              const uint64_t so = (uint64_t)(stage_of(n_dsp) * STAGE16);
+              { FPB_PROF_BEGIN(); tc_fence_after(); FPB_PROF_END(3); }
+              if (leader) {
+                FPB_PROF_BEGIN();
+                for (int ks = 0; ks < pmid / 16; ++ks) umma_bf16(tm + G::TM_DSP, d_km + so + mstep(ks), d_vm + so + mstep(ks), ID_DS, ks > 0);
+                FPB_PROF_END(2);
+                { FPB_PROF_BEGIN(); umma_commit(bar(B_DSPFULL)); FPB_PROF_END(1); }
+              }
+              ++m_dsp; ++n_dsp; progress = true;
+              release();
             }
-            umma_commit(bar(B_SBFREE));    // Sb may be overwritten with the next state once this has run
-            FPB_TRACE(1, n_qs);
           }
-          ++n_qs; progress = true;
-        }
-        // intra-chunk term: ACC += P' Veta (FWD) | P' K (DQ); needs the state term of the same chunk issued before
-        if (!SO && n_pv < n_qs && ready(B_PRDY + n_pv % G::NP, (n_pv / G::NP) & 1)) {   // the state term has seen the data
-          const uint64_t so = (uint64_t)(stage_of(n_pv) * STAGE16);
-          if (leader) FPB_TRACE(15, n_pv);
-          tc_fence_after();
-          const uint32_t acc = tm + tm_acc(n_pv);
-          const uint64_t a = d_p + (uint64_t)((n_pv % G::NP) * (G::P_BYTES >> 4));
-          const uint64_t bm = (MODE == MODE_FWD ? d_vm : d_km) + so;
-          if (leader) {
-#pragma unroll
-            for (int ks = 0; ks < C / 16; ++ks) umma_bf16(acc, a + kstep(ks, 0), bm + mstep(ks), ID_INTRA, 1);
-            umma_commit(bar(B_ACCFULL + n_pv % G::NACC));
-            FPB_TRACE(3, n_pv);
+          // state term: ACC = X Sb (FWD) | X Sb^T (DQ)
+          if (DO_B && !SO && n_qs < NC && data_ready(n_qs) && (n_qs < G::NACC || ready(B_ACCFREE + n_qs % G::NACC, ((n_qs / G::NACC) & 1) ^ 1)) &&
+              ready(B_SBRDY + n_qs % G::NSB, (n_qs / G::NSB) & 1)) {
+            const uint64_t so = (uint64_t)(stage_of(n_qs) * STAGE16);
+            if (leader) FPB_TRACE(2, n_qs);
+            { FPB_PROF_BEGIN(); tc_fence_after(); FPB_PROF_END(3); }
+            const uint32_t acc = tm + tm_acc(n_qs);
+            const uint64_t sbo = (uint64_t)((n_qs % G::NSB) * (G::SB_BYTES >> 4));      // which copy of the state
+            if (leader) {
+              if (MODE == MODE_FWD) {
+                FPB_PROF_BEGIN();
+FPB_UNROLL_MMA
+                for (int ks = 0; ks < (FPB_ABL(32) ? 1 : R / 16); ++ks) umma_bf16(acc, d_x + so + kstep(ks, 8192), d_sb + sbo + mstep(ks), ID_STATE, ks > 0);
+                FPB_PROF_END(2);
+              } else {
+                FPB_PROF_BEGIN();
+FPB_UNROLL_MMA
+                for (int ks = 0; ks < (FPB_ABL(32) ? 1 : CC / 16); ++ks) umma_bf16(acc, d_x + so + kstep(ks, 8192), d_sb + sbo + kstep(ks, R * 128), ID_STATE, ks > 0);
+                FPB_PROF_END(2);
+              }
+              { FPB_PROF_BEGIN(); umma_commit(bar(B_SBFREE + n_qs % G::NSB)); FPB_PROF_END(1); }    // that copy may be overwritten once this has run
+              FPB_TRACE(1, n_qs);
+            }
+            ++n_qs; progress = true;
           }
-          ++n_pv; progress = true;
+          // intra-chunk term: ACC += P' Veta (FWD) | P' K (DQ); needs the state term of the same chunk issued before
+          if (DO_B && !SO && n_pv < n_qs && ready(B_PRDY + n_pv % G::NP, (n_pv / G::NP) & 1)) {   // the state term has seen the data
+            const uint64_t so = (uint64_t)(stage_of(n_pv) * STAGE16);
+            if (leader) FPB_TRACE(15, n_pv);
+            { FPB_PROF_BEGIN(); tc_fence_after(); FPB_PROF_END(3); }
+            const uint32_t acc = tm + tm_acc(n_pv);
+            const uint64_t a = d_p + (uint64_t)((n_pv % G::NP) * (G::P_BYTES >> 4));
+            const uint64_t bm = (MODE == MODE_FWD ? d_vm : d_km) + so;
+            if (leader) {
+              FPB_PROF_BEGIN();
+FPB_UNROLL_MMA
+              for (int ks = 0; ks < (FPB_ABL(32) ? 1 : C / 16); ++ks) umma_bf16(acc, a + kstep(ks, 0), bm + mstep(ks), ID_INTRA, 1);
+              FPB_PROF_END(2);
+              { FPB_PROF_BEGIN(); umma_commit(bar(B_ACCFULL + n_pv % G::NACC)); FPB_PROF_END(1); }
+              FPB_TRACE(3, n_pv);
+            }
+            ++n_pv; progress = true;
+            release();
+          }
           release();
+          if (progress) patience.progress();
+          else if (__any_sync(0xffffffffu, patience.exhausted(abort_flag))) {
+            if (leader) FPB_GIVE_UP((DO_A ? 0x200 : 0x500) | ((DO_A ? n_ds : n_pv) & 0xff));
+            break;
+          }
         }
-        release();
-        if (progress) patience.progress();
-        else if (__any_sync(0xffffffffu, patience.exhausted(abort_flag))) { if (leader) FPB_GIVE_UP(0x200 | (n_pv & 0xff)); break; }
-      }
+      };
+      if (!G::SPLIT || SO) issue_loop(std::true_type{}, std::true_type{});
+      else if (warp == 1) issue_loop(std::true_type{}, std::false_type{});
+      else issue_loop(std::false_type{}, std::true_type{});
+      if (warp == 1) FPB_PROF_STORE();
     }
   } else if (warp < STATE_WARP0) {                   // ---------------- score warps
     const int t = tid - SCORE_WARP0 * 32;            // 0..127
@@ -423,6 +492,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
     // P'(n): causal side of Sc times gamma^-L (and rs in forward walks), bf16, swizzled K-major tile
     auto make_p = [&](int n, int L) {
       tc_fence_after();
+      if (FPB_ABL(4)) { tc_fence_before(); if (!FPB_ABL(64)) fence_async_smem(); warp_arrive(bar(B_PRDY + n % G::NP)); return; }
       uint32_t r[32];
       tmem_ld_16x256b_x8(tm + lane_base + tm_sc(n), r);
       tmem_wait_ld();
@@ -440,8 +510,8 @@ scan_kernel(const __grid_constant__ ScanParams p) {
         *reinterpret_cast<uint32_t*>(pt + r_lo * 128 + ((g ^ (r_lo & 7)) << 4) + cpair * 2) = pack_bf16(a0, a1);
         *reinterpret_cast<uint32_t*>(pt + (r_lo + 8) * 128 + ((g ^ ((r_lo + 8) & 7)) << 4) + cpair * 2) = pack_bf16(b0, b1);
       }
-      fence_async_smem();
-      mbar_arrive(bar(B_PRDY + n % G::NP));
+      if (!FPB_ABL(64)) fence_async_smem();
+      warp_arrive(bar(B_PRDY + n % G::NP));
       if (t == 0) FPB_TRACE(7, n);
     };
 
@@ -455,6 +525,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
       __syncwarp();
       if (t == 0) FPB_TRACE(9, n);
       tc_fence_after();
+      if (FPB_ABL(8)) { tc_fence_before(); warp_arrive(bar(B_ACCFREE + n % G::NACC)); return; }
       // row scale: zeta_i (forward walks) or eta_j * rs (reverse walks)
       const float z_lo = REV ? exp2f((float)(ck.L - 1 - r_lo) * lg) * rs : exp2f((float)(r_lo + 1) * lg);
       const float z_hi = REV ? exp2f((float)(ck.L - 9 - r_lo) * lg) * rs : exp2f((float)(r_lo + 9) * lg);
@@ -464,7 +535,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
         uint32_t r[32];
         tmem_ld_16x256b_x8(tm + lane_base + tm_acc(n) + half * 64, r);
         tmem_wait_ld();
-        if (half == G::NOUT / 64 - 1) { tc_fence_before(); mbar_arrive(bar(B_ACCFREE + n % G::NACC)); }
+        if (half == G::NOUT / 64 - 1) { tc_fence_before(); warp_arrive(bar(B_ACCFREE + n % G::NACC)); }
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
           const uint32_t lo = pack_bf16(__uint_as_float(r[4 * g]) * z_lo, __uint_as_float(r[4 * g + 1]) * z_lo);
@@ -477,7 +548,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
       const int wrow0 = q4 * 16;                                // this warp's rows [wrow0, wrow0 + 16)
       const int ocol0 = MODE == MODE_FWD ? col0 : row0;
       if (whole_box) {
-        fence_async_smem();
+        if (!FPB_ABL(64)) fence_async_smem();
         __syncwarp();
         if (lane == 0 && ck.a + wrow0 < p.T) {
 #pragma unroll
@@ -505,6 +576,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
     // thread waits for another, rows >= L are simply not stored, and the shared-memory port is left to the MMAs.
     auto epilogue_direct = [&](int n, Chunk ck) {
       tc_fence_after();
+      if (FPB_ABL(8)) { tc_fence_before(); warp_arrive(bar(B_ACCFREE + n % G::NACC)); return; }
       const int row = q4 * 16 + (lane & 15);
       const bool mine = (lane >> 4) == (n & 1) && row < ck.L;
       const float z = REV ? exp2f((float)(ck.L - 1 - row) * lg) * rs : exp2f((float)(row + 1) * lg);
@@ -515,7 +587,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(tm + lane_base + G::TM_ACC + c0, r);
         tmem_wait_ld();
-        if (c0 + 32 == G::NOUT) { tc_fence_before(); mbar_arrive(bar(B_ACCFREE + n % G::NACC)); }
+        if (c0 + 32 == G::NOUT) { tc_fence_before(); warp_arrive(bar(B_ACCFREE + n % G::NACC)); }
         if (mine) {
 #pragma unroll
           for (int v4 = 0; v4 < 4; ++v4) {
@@ -568,7 +640,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
       }
       if (!G::DIRECT_OUT && lane == 0) tma_store_wait_all0();
     }
-  } else {                                           // ---------------- state warps
+  } else if (warp < STATE_WARP0 + G::STATE_WARPS) {  // ---------------- state warps
     const int t = tid - STATE_WARP0 * 32;            // 0..N_STATE-1
     const int q4 = warp & 3;
     const int half = (warp - STATE_WARP0) >> 2;      // which slice of the CC state columns
@@ -704,8 +776,9 @@ scan_kernel(const __grid_constant__ ScanParams p) {
     };
     // bf16 copy of the state in shared memory: [CC/64 column blocks][R rows][128 bytes], 16-byte
     // pieces XOR-swizzled by (row & 7) — an MN-major B operand (FWD) or a K-major B operand (DQ).
-    auto publish_sb = [&]() {
-      uint8_t* sb = sm + G::OFF_SB;
+    auto publish_sb = [&](int n) {
+      uint8_t* sb = sm + G::OFF_SB + (n % G::NSB) * G::SB_BYTES;
+      if (FPB_ABL(2)) { if (!FPB_ABL(64)) fence_async_smem(); warp_arrive(bar(B_SBRDY + n % G::NSB)); return; }
       if (R == 128) {
         const int row = row_of(0);
 #pragma unroll
@@ -724,15 +797,15 @@ scan_kernel(const __grid_constant__ ScanParams p) {
               pack_bf16(S[i], S[i + 1]);
         }
       }
-      fence_async_smem();
-      mbar_arrive(bar(B_SBRDY));
+      if (!FPB_ABL(64)) fence_async_smem();
+      warp_arrive(bar(B_SBRDY + n % G::NSB));
     };
     // in-place row scale of the V tile of chunk n: eta_j = gamma^(L-1-j) (forward walks) or
     // zeta_i = gamma^(i+1) (reverse walks, the tile holds dO); rows >= L are zeroed
     auto scale_v = [&](int n, int L) {
       const int s = stage_of(n);
       uint8_t* vt = sm + G::OFF_STAGE + s * G::STAGE_BYTES + G::X_BYTES + G::K_BYTES;
-      for (int idx = t; idx < C * CC / 8; idx += G::N_STATE) {
+      for (int idx = t; idx < (FPB_ABL(1) ? 0 : C * CC / 8); idx += G::N_STATE) {
         const int row = (idx >> 3) & 63;
         uint4* ptr = reinterpret_cast<uint4*>(vt + idx * 16);
         uint4 val = make_uint4(0u, 0u, 0u, 0u);
@@ -748,8 +821,8 @@ scan_kernel(const __grid_constant__ ScanParams p) {
         }
         *ptr = val;
       }
-      fence_async_smem();
-      mbar_arrive(bar(B_VRDY + s));
+      if (!FPB_ABL(64)) fence_async_smem();
+      warp_arrive(bar(B_VRDY + s));
     };
 
     if (x_start) {
@@ -781,8 +854,9 @@ scan_kernel(const __grid_constant__ ScanParams p) {
           progress = true;
         }
         if (publish_due) {
-          if (n_u == 0 || mbar_test_wait(bar(B_SBFREE), (n_u - 1) & 1)) {
-            publish_sb();
+          // copy n_u goes into buffer n_u % NSB, which the state term of chunk n_u - NSB was the last to read
+          if (n_u < G::NSB || mbar_test_wait(bar(B_SBFREE + n_u % G::NSB), (n_u / G::NSB - 1) & 1)) {
+            publish_sb(n_u);
             if (t == 0) FPB_TRACE(13, n_u);
             publish_due = false; progress = true;
           }
@@ -806,7 +880,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
               }
             }
             tc_fence_before();
-            mbar_arrive(bar(B_DSPFREE));
+            warp_arrive(bar(B_DSPFREE));
             ++m_part; partial_due = false; progress = true;
           }
         } else if (mbar_test_wait(bar(B_DSFULL + (n_u & 1)), (n_u >> 1) & 1)) {
@@ -815,7 +889,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
           const float gl = exp2f((float)ck_u.L * lg);
           // 16 registers at a time keeps the state warps inside the register budget
 #pragma unroll
-          for (int i0 = 0; i0 < G::NS; i0 += 16) {
+          for (int i0 = 0; i0 < (FPB_ABL(16) ? 0 : G::NS); i0 += 16) {
             uint32_t r[16];
             if (R == 128) tmem_ld_32x32b_x16(tm + lane_base + tm_ds(n_u) + wcol0 + i0, r);
             else tmem_ld_16x256b_x4(tm + lane_base + tm_ds(n_u) + wcol0 + i0 * 2, r);
@@ -824,7 +898,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
             for (int i = 0; i < 16; ++i) S[i0 + i] = fmaf(gl, S[i0 + i], ds_scale * __uint_as_float(r[i]));
           }
           tc_fence_before();
-          mbar_arrive(bar(B_DSFREE + (n_u & 1)));   // the increment has been read: the one after next may overwrite it
+          warp_arrive(bar(B_DSFREE + (n_u & 1)));   // the increment has been read: the one after next may overwrite it
           const int end = ck_u.a + ck_u.L;
           if (!REV && !SO && p.block_size > 0 && p.block_states && end % p.block_size == 0 && end / p.block_size - 1 < p.n_blocks)
             store_global(at(p.block_states, (((int64_t)b * p.n_blocks + (end / p.block_size - 1)) * p.H + h) * state_elems), state_t);
@@ -848,7 +922,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
         }
         if (progress) patience.progress();
         else if (patience.exhausted(abort_flag)) { FPB_GIVE_UP(0x400 | (n_u & 0xff)); break; }
-        else if (publish_due) mbar_try_wait_hint(bar(B_SBFREE), (n_u - 1) & 1, p.tune.idle_ns);   // idle: sleep on the likely next
+        else if (publish_due) mbar_try_wait_hint(bar(B_SBFREE + n_u % G::NSB), (n_u / G::NSB - 1) & 1, p.tune.idle_ns);   // idle: sleep on the likely next
         else if (G::EMIT && partial_due) mbar_try_wait_hint(bar(B_DSPFULL), m_part & 1, p.tune.idle_ns);
         else mbar_try_wait_hint(bar(B_DSFULL + (n_u & 1)), (n_u >> 1) & 1, p.tune.idle_ns);
       }
@@ -930,10 +1004,10 @@ FPB_KNOB g_fused_bwd = 1;            // 1: dK, dV, dS_0 in one fused reverse wal
 FPB_KNOB g_segments = 1;             // 1: under-filled launches are cut into T-segments when the caller gave scratch memory
 #ifdef FPB_DIAGNOSTICS
 long long* g_trace = nullptr;        // set by fpb_debug_trace
-WalkTuning g_tuning{kWaitCycles, 200, 1, -1};
+WalkTuning g_tuning{kWaitCycles, 200, 1, -1, 0};
 #else
 constexpr long long* g_trace = nullptr;
-constexpr WalkTuning g_tuning{kWaitCycles, 200, 1, -1};
+constexpr WalkTuning g_tuning{kWaitCycles, 200, 1, -1, 0};
 #endif
 
 bool aligned_state(const StateView& s, bool f32) {
@@ -1093,6 +1167,7 @@ extern "C" void fpb_debug_segments(int on) { g_segments = on; }
 extern "C" void fpb_debug_deep(int on) { g_deep = on; }
 // Wait limit in clock ticks (<= 0: the default of about a second), idle suspend hint in ns, early scores on / off, and the
 // chunk the producers withhold (-1: none; makes every role's wait on it run out).
+extern "C" void fpb_debug_ablate(int mask) { g_tuning.ablate = mask; }
 extern "C" void fpb_debug_tuning(long long wait_cycles, int idle_ns, int sc_early, int withhold_chunk) {
   g_tuning.wait_cycles = wait_cycles > 0 ? wait_cycles : kWaitCycles;
   g_tuning.idle_ns = idle_ns > 0 ? idle_ns : 200;

@@ -60,6 +60,32 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 #define FPB_TRACE(slot, c) do { } while (0)
 #endif
 
+// diagnostics build: "leave this piece of work out" switches for timing experiments (the hand-offs stay, the results
+// are wrong).  1 tile rescaling, 2 state copy, 4 P', 8 epilogue, 16 state update, 32 one k-step per product, 64 proxy fences
+#ifdef FPB_DIAGNOSTICS
+#define FPB_ABL(bit) ((p.tune.ablate & (bit)) != 0)
+#else
+#define FPB_ABL(bit) false
+#endif
+
+// diagnostics build: cycles the MMA-issuing thread spends in barrier tests (0), commits (1), tcgen05.mma issue (2) and
+// tcgen05 fences (3), with their counts in slots 4-7; written to row 63 of the trace buffer by CTA (0,0,0)
+#ifdef FPB_DIAGNOSTICS
+#define FPB_PROF_DECL() long long prof_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long prof_t_ = 0
+#define FPB_PROF_BEGIN() (prof_t_ = clock64())
+#define FPB_PROF_END(i) (prof_[i] += clock64() - prof_t_, ++prof_[(i) + 4])
+#define FPB_PROF_STORE()                                                                       \
+  do {                                                                                         \
+    if (p.trace && leader && (blockIdx.x | blockIdx.y | blockIdx.z) == 0)                      \
+      for (int i_ = 0; i_ < 8; ++i_) p.trace[63 * 16 + i_] = prof_[i_];                        \
+  } while (0)
+#else
+#define FPB_PROF_DECL() do { } while (0)
+#define FPB_PROF_BEGIN() do { } while (0)
+#define FPB_PROF_END(i) do { } while (0)
+#define FPB_PROF_STORE() do { } while (0)
+#endif
+
 // A polling loop that made no progress: true when it should give up (another thread did, or the CTA's wait limit,
 // kept in shared memory right after the abort flag, has passed since the last progress).
 struct Patience {

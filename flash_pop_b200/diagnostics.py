@@ -5,8 +5,9 @@
 
 prints, for the first CTA of a forward (or dQ) walk, the events of a few chunks in order - copies issued, tile rescaled,
 each product issued, scores / accumulator seen by the score warps, state copy published - in SM clock cycles, and the mean
-period of each event over 40 chunks.  A chunk's period is what bounds the walk; the lag of an event behind the issue of
-the chunk's copies shows which hand-off the chunk waits on."""
+period of each event over 40 chunks, and what the MMA-issuing thread spends per chunk in barrier tests, commits, tcgen05.mma
+issue and fences.  A chunk's period is what bounds the walk; the lag of an event behind the issue of the chunk's copies
+shows which hand-off the chunk waits on."""
 from __future__ import annotations
 
 import ctypes
@@ -54,6 +55,12 @@ def chunk_timeline(B: int = 8, H: int = 16, T: int = 8192, d: int = 128, walk: s
         col = t[lo:hi, i]
         if hi - lo > 2 and (col > 0).all():
             lines.append(f"{EVENTS[i]:38s} period {np.diff(col).mean():7.0f}   lag behind the copies' issue {np.mean(col - t[lo:hi, 14]):7.0f}")
+    acct = t[63][:8]
+    chunks = (T + 63) // 64
+    if acct[4:].any():
+        names = ("barrier tests", "commits", "tcgen05.mma issue", "tcgen05 fences")
+        lines.append(f"MMA-issuing thread, whole walk ({chunks} chunks): " + "; ".join(
+            f"{names[i]} {acct[i] / chunks:.0f} cycles per chunk in {acct[4 + i] / chunks:.1f} calls" for i in range(4)))
     return "\n".join(lines)
 
 
