@@ -441,16 +441,16 @@ def _traffic(read_b, write_b, scale, what):
 
 
 NCU_TRAFFIC = {
-    ("ns", "fwd"): _traffic(503386880, 146526464, 8 / 5, "ncu at B=5, scaled x8/5 by token-heads"),
-    ("ns", "dq"): _traffic(503442176, 144563200, 8 / 5, "ncu at B=5, scaled x8/5 by token-heads"),
-    ("ns", "rev"): _traffic(671172864, 305666816, 8 / 5, "ncu at B=5, scaled x8/5 by token-heads"),
-    ("c3", "fwd"): _traffic(1073834240, 507843072, 2, "ncu at B=2, scaled x2 by token-heads"),
-    ("c3", "dq"): _traffic(1343845376, 257063168, 2, "ncu at B=2, scaled x2 by token-heads"),
-    ("c3", "rev"): _traffic(1073828096 + 1343579904, 506655744 + 256747520, 2,
+    ("ns", "fwd"): _traffic(503387136, 145907200, 8 / 5, "ncu at B=5, scaled x8/5 by token-heads"),
+    ("ns", "dq"): _traffic(503387392, 145740800, 8 / 5, "ncu at B=5, scaled x8/5 by token-heads"),
+    ("ns", "rev"): _traffic(671177984, 304712448, 8 / 5, "ncu at B=5, scaled x8/5 by token-heads"),
+    ("c3", "fwd"): _traffic(1073822208, 507802368, 2, "ncu at B=2, scaled x2 by token-heads"),
+    ("c3", "dq"): _traffic(1343727360, 257168384, 2, "ncu at B=2, scaled x2 by token-heads"),
+    ("c3", "rev"): _traffic(1073847552 + 1343894784, 506097152 + 257013248, 2,
                             "ncu at B=2 (the dV walk and the dK walk, two launches), scaled x2 by token-heads"),
-    ("c4", "fwd"): _traffic(251724032, 112299008, 1, "ncu at the full workload"),
-    ("c4", "dq"): _traffic(251713280, 60388096, 1, "ncu at the full workload"),
-    ("c4", "rev"): _traffic(335681536, 137153536, 1, "ncu at the full workload"),
+    ("c4", "fwd"): _traffic(251724800, 112073728, 1, "ncu at the full workload"),
+    ("c4", "dq"): _traffic(251713280, 59949824, 1, "ncu at the full workload"),
+    ("c4", "rev"): _traffic(335681792, 137124096, 1, "ncu at the full workload"),
 }
 
 

@@ -68,12 +68,8 @@ using namespace ptx;
 using namespace scan;
 typedef __nv_bfloat16 bf16;
 
-// The tcgen05.mma issue loops (4-8 k-steps each) are fully unrolled unless an experiment build says otherwise.
-#ifdef FPB_EXP_SMALL_MMA
-#define FPB_UNROLL_MMA _Pragma("unroll 1")
-#else
+// The tcgen05.mma issue loops (4-8 k-steps each) are fully unrolled: rolled loops measured slower at d = 128.
 #define FPB_UNROLL_MMA _Pragma("unroll")
-#endif
 
 constexpr int MODE_FWD = 0, MODE_DQ = 1;
 constexpr int SCORE_WARP0 = 2, STATE_WARP0 = 6;
@@ -129,7 +125,7 @@ struct Cfg {
   static constexpr int N_STATE = 32 * STATE_WARPS;
   // one-CTA-per-SM configurations issue their products from two warps (see the MMA issuer in the kernel); the second
   // one is the CTA's last warp
-  static constexpr bool SPLIT = ONE;      // (the deep 64 x 64 variant lost 7 % with it)
+  static constexpr bool SPLIT = ONE;      // (the deep 64 x 64 variant lost 7 % with it; 64 x 256 is indifferent)
   static constexpr int MMAB_WARP = STATE_WARP0 + STATE_WARPS;
   static constexpr int NTHREADS = STATE_WARP0 * 32 + N_STATE + (SPLIT ? 32 : 0);
   static constexpr int MIN_CTAS = SOLO ? 1 : 2;
@@ -139,7 +135,8 @@ struct Cfg {
   static constexpr int P_BYTES = C * C * 2;
   static constexpr int SB_BYTES = R * CC * 2;
   // bf16 copies of the state.  Two (so that the copy for chunk n + 1 need not wait for the state-term product of chunk
-  // n to finish reading) fit only next to the small tiles, where they measured no gain: one.
+  // n to finish reading) measured no gain next to the small tiles, and next to the 128 x 128 tile - where the second
+  // copy takes the place of the output staging tile - a loss of 3 % on top of the 8 % the direct epilogue costs: one.
   static constexpr int NSB = 1;
   static constexpr int OUT_BYTES = C * NOUT * 2;
   static constexpr int FIXED = NP * P_BYTES + NSB * SB_BYTES + OUT_BYTES + BAR_PAGE;
@@ -847,12 +844,8 @@ FPB_UNROLL_MMA
       Patience patience{0, 0};
       while (n_u < NC) {
         bool progress = false;
-        if (n_v < NC && mbar_test_wait(bar(B_FULL + stage_of(n_v)), stage_ph(n_v))) {
-          scale_v(n_v, ck_v.L);
-          if (t == 0) FPB_TRACE(11, n_v);
-          ++n_v; advance<REV>(ck_v, t_end, p.sched_bs);
-          progress = true;
-        }
+        // the state copy and the state update come first: they sit on the chunk-to-chunk chain (copy -> state term ->
+        // copy of the next chunk), the tile rescaling only has to stay ahead of the products (2 % on the 128-wide walks)
         if (publish_due) {
           // copy n_u goes into buffer n_u % NSB, which the state term of chunk n_u - NSB was the last to read
           if (n_u < G::NSB || mbar_test_wait(bar(B_SBFREE + n_u % G::NSB), (n_u / G::NSB - 1) & 1)) {
@@ -918,6 +911,12 @@ FPB_UNROLL_MMA
             publish_due = !SO;
             partial_due = emit && !SO && mid_end(n_u) > 0;
           }
+          progress = true;
+        }
+        if (n_v < NC && mbar_test_wait(bar(B_FULL + stage_of(n_v)), stage_ph(n_v))) {
+          scale_v(n_v, ck_v.L);
+          if (t == 0) FPB_TRACE(11, n_v);
+          ++n_v; advance<REV>(ck_v, t_end, p.sched_bs);
           progress = true;
         }
         if (progress) patience.progress();
