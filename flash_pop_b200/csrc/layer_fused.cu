@@ -430,32 +430,21 @@ template <int V> __device__ __forceinline__ void load_params(const float* base, 
   }
 }
 
-template <typename T, int NPASS, bool BWD>
-__global__ void __launch_bounds__(BWD ? 128 : 256) layernorm_kernel(const __grid_constant__ NormParams p) {
+template <typename T, int NPASS>
+__global__ void __launch_bounds__(256) layernorm_kernel(const __grid_constant__ NormParams p) {
   constexpr int V = 16 / sizeof(T);
-  extern __shared__ float sh_grad[];             // backward: d floats of weight gradient, d of bias gradient
   const int lane = threadIdx.x & 31;
   const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
   const float inv_n = 1.0f / (float)p.d;
-  float gw[BWD ? NPASS : 1][V], gb[BWD ? NPASS : 1][V];
-  if constexpr (BWD) {
-#pragma unroll
-    for (int i = 0; i < NPASS; ++i)
-#pragma unroll
-      for (int e = 0; e < V; ++e) gw[i][e] = gb[i][e] = 0.0f;
-    for (int i = threadIdx.x; i < 2 * p.d; i += blockDim.x) sh_grad[i] = 0.0f;
-    __syncthreads();
-  }
   for (int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < p.rows; row += warps) {
     const T* x = (const T*)p.x + row * p.x_stride;
-    float xv[NPASS][V], dv[BWD ? NPASS : 1][V];
+    float xv[NPASS][V];
     float sum = 0.0f;
 #pragma unroll
     for (int i = 0; i < NPASS; ++i) {
       const int c = V * (lane + 32 * i);
       if (c < p.d) {
         load16v<T, V>(x + c, xv[i]);
-        if constexpr (BWD) load16v<T, V>((const T*)p.dy + row * p.y_stride + c, dv[i]);
 #pragma unroll
         for (int e = 0; e < V; ++e) sum += xv[i][e];
       }
@@ -470,21 +459,211 @@ __global__ void __launch_bounds__(BWD ? 128 : 256) layernorm_kernel(const __grid
       }
     }
     const float rstd = rsqrtf(warp_sum(sq) * inv_n + p.eps);
-    if constexpr (!BWD) {
-      T* y = (T*)p.y + row * p.y_stride;
+    T* y = (T*)p.y + row * p.y_stride;
 #pragma unroll
-      for (int i = 0; i < NPASS; ++i) {
-        const int c = V * (lane + 32 * i);
-        if (c < p.d) {
-          float res[V], w[V], b[V];
-          load_params<V>(p.w, c, 1.0f, w);
-          load_params<V>(p.b, c, 0.0f, b);
+    for (int i = 0; i < NPASS; ++i) {
+      const int c = V * (lane + 32 * i);
+      if (c < p.d) {
+        float res[V], w[V], b[V];
+        load_params<V>(p.w, c, 1.0f, w);
+        load_params<V>(p.b, c, 0.0f, b);
 #pragma unroll
-          for (int e = 0; e < V; ++e) res[e] = xv[i][e] * rstd * w[e] + b[e];
-          store16v<T, V>(y + c, res);
-        }
+        for (int e = 0; e < V; ++e) res[e] = xv[i][e] * rstd * w[e] + b[e];
+        store16v<T, V>(y + c, res);
       }
-    } else {
+    }
+  }
+}
+
+// Sums of N values over the CTA (every thread gets them): a shuffle reduction per warp, then the warps' partial sums
+// through `buf` ([warps][N]).  The caller rotates three buffers, so a buffer is rewritten two barriers after its last read.
+template <int N> __device__ __forceinline__ void cta_sums(float (&v)[N], float* buf, int warp, int lane, int n_warps) {
+#pragma unroll
+  for (int k = 0; k < N; ++k) v[k] = warp_sum(v[k]);
+  if (n_warps == 1) return;
+  if (lane == 0) {
+#pragma unroll
+    for (int k = 0; k < N; ++k) buf[warp * N + k] = v[k];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < N; ++k) {
+    float acc = 0.0f;
+    for (int w = 0; w < n_warps; ++w) acc += buf[w * N + k];
+    v[k] = acc;
+  }
+}
+
+// 16 raw bytes -> V floats
+template <typename T, int V> __device__ __forceinline__ void unpack16v(const uint4& raw, float (&f)[V]) {
+  if constexpr (sizeof(T) == 2) {
+    const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 a = __bfloat1622float2(e[i]); f[2 * i] = a.x; f[2 * i + 1] = a.y; }
+  } else {
+    f[0] = __uint_as_float(raw.x); f[1] = __uint_as_float(raw.y); f[2] = __uint_as_float(raw.z); f[3] = __uint_as_float(raw.w);
+  }
+}
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// LayerNorm backward with the whole CTA across a row: thread t owns channels [V t, V t + V) of every row the CTA walks
+// (ceil(d / V) threads rounded up to whole warps, at most 128), R rows per step.  A thread's share of the weight and
+// bias gradients is then 2 V registers - with one warp per row it was 2 d / 32, which left a quarter of the warps
+// resident.  What bounds the pass is the number of bytes in flight, so every thread keeps a ring of LN_DEPTH steps of
+// its own 16-byte pieces of x and dy in shared memory, filled by asynchronous copies that it alone waits for and reads
+// (no barrier belongs to the ring), while the three CTA-wide reductions of a step (mean; variance; the two sums of the
+// input gradient) run.  The gradient sums go out as 16-byte atomic adds at the end (atomic adds into one 32-byte
+// sector serialise at a few nanoseconds each, so their number matters: one wave of CTAs, four floats per add).
+//   n = (x - mean) rstd, y = n w + b:  dn = dy w;  dx = rstd (dn - mean(dn) - n mean(dn n));  dw += dy n;  db += dy
+constexpr int LN_DEPTH = 4;
+template <typename T, int R>
+__global__ void __launch_bounds__(128) layernorm_bwd_kernel(const __grid_constant__ NormParams p) {
+  constexpr int V = 16 / sizeof(T);
+  extern __shared__ __align__(16) uint4 ln_ring[];          // [LN_DEPTH][2 R][blockDim.x]
+  __shared__ float red[3][4 * 2 * R];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  const int c = V * threadIdx.x;
+  const bool active = c < p.d;
+  const float inv_n = 1.0f / (float)p.d;
+  float gw[V], gb[V], w[V];
+#pragma unroll
+  for (int e = 0; e < V; ++e) gw[e] = gb[e] = 0.0f;
+  load_params<V>(active ? p.w : nullptr, c, 1.0f, w);
+  auto slot = [&](int step, int j) { return ln_ring + ((step % LN_DEPTH) * 2 * R + j) * blockDim.x + threadIdx.x; };
+  auto fetch = [&](int step, int64_t base) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (active && base + r < p.rows) {
+        cp_async_16(slot(step, 2 * r), (const T*)p.x + (base + r) * p.x_stride + c);
+        cp_async_16(slot(step, 2 * r + 1), (const T*)p.dy + (base + r) * p.y_stride + c);
+      }
+    }
+    cp_async_commit();
+  };
+  const int64_t stride = (int64_t)gridDim.x * R, base0 = (int64_t)blockIdx.x * R;
+#pragma unroll
+  for (int k = 0; k < LN_DEPTH - 1; ++k) fetch(k, base0 + k * stride);
+  int step = 0;
+  for (int64_t base = base0; base < p.rows; base += stride, ++step) {
+    fetch(step + LN_DEPTH - 1, base + (LN_DEPTH - 1) * stride);
+    cp_async_wait<LN_DEPTH - 1>();                          // this step's pieces have landed
+    float xv[R][V], dv[R][V];
+    float a[R], s[2 * R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      uint4 rx = make_uint4(0u, 0u, 0u, 0u), ry = rx;
+      if (active && base + r < p.rows) { rx = *slot(step, 2 * r); ry = *slot(step, 2 * r + 1); }
+      unpack16v<T, V>(rx, xv[r]);
+      unpack16v<T, V>(ry, dv[r]);
+      a[r] = 0.0f;
+#pragma unroll
+      for (int e = 0; e < V; ++e) a[r] += xv[r][e];
+    }
+    cta_sums<R>(a, red[0], warp, lane, n_warps);
+    float mean[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      mean[r] = a[r] * inv_n;
+      a[r] = 0.0f;
+      if (active) {
+#pragma unroll
+        for (int e = 0; e < V; ++e) { xv[r][e] -= mean[r]; a[r] += xv[r][e] * xv[r][e]; }
+      }
+    }
+    cta_sums<R>(a, red[1], warp, lane, n_warps);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const float rstd = rsqrtf(a[r] * inv_n + p.eps);
+      a[r] = rstd;
+      s[2 * r] = s[2 * r + 1] = 0.0f;
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        const float n = xv[r][e] * rstd, g = dv[r][e];
+        gw[e] += g * n;
+        gb[e] += g;
+        const float dn = g * w[e];
+        xv[r][e] = n; dv[r][e] = dn;
+        s[2 * r] += dn;
+        s[2 * r + 1] += dn * n;
+      }
+    }
+    cta_sums<2 * R>(s, red[2], warp, lane, n_warps);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (active && base + r < p.rows) {
+        const float m1 = s[2 * r] * inv_n, m2 = s[2 * r + 1] * inv_n;
+        float res[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) res[e] = a[r] * (dv[r][e] - m1 - xv[r][e] * m2);
+        store16v<T, V>((T*)p.dx + (base + r) * p.x_stride + c, res);
+      }
+    }
+  }
+  cp_async_wait<0>();
+  if (active) {
+    auto add_out = [&](float* dst, const float (&g)[V]) {
+      if (!dst) return;
+      if (((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+        for (int e = 0; e < V; e += 4) atomicAdd(reinterpret_cast<float4*>(dst + c + e), make_float4(g[e], g[e + 1], g[e + 2], g[e + 3]));
+      } else {
+#pragma unroll
+        for (int e = 0; e < V; ++e) atomicAdd(dst + c + e, g[e]);
+      }
+    };
+    add_out(p.dw, gw);
+    add_out(p.db, gb);
+  }
+}
+
+// LayerNorm backward, one warp per row (rows of at most 2 passes of 32 lanes x 16 bytes: the weight / bias gradient sums
+// are then at most 32 registers of a lane).  The CTA's sums meet in shared memory and go out as 16-byte atomic adds.
+template <typename T, int NPASS>
+__global__ void __launch_bounds__(128) layernorm_bwd_warp_kernel(const __grid_constant__ NormParams p) {
+  constexpr int V = 16 / sizeof(T);
+  extern __shared__ float sh_grad[];             // backward: d floats of weight gradient, d of bias gradient
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const float inv_n = 1.0f / (float)p.d;
+  float gw[NPASS][V], gb[NPASS][V];
+  {
+#pragma unroll
+    for (int i = 0; i < NPASS; ++i)
+#pragma unroll
+      for (int e = 0; e < V; ++e) gw[i][e] = gb[i][e] = 0.0f;
+    for (int i = threadIdx.x; i < 2 * p.d; i += blockDim.x) sh_grad[i] = 0.0f;
+    __syncthreads();
+  }
+  for (int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < p.rows; row += warps) {
+    const T* x = (const T*)p.x + row * p.x_stride;
+    float xv[NPASS][V], dv[NPASS][V];
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NPASS; ++i) {
+      const int c = V * (lane + 32 * i);
+      if (c < p.d) {
+        load16v<T, V>(x + c, xv[i]);
+        load16v<T, V>((const T*)p.dy + row * p.y_stride + c, dv[i]);
+#pragma unroll
+        for (int e = 0; e < V; ++e) sum += xv[i][e];
+      }
+    }
+    const float mean = warp_sum(sum) * inv_n;
+    float sq = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NPASS; ++i) {
+      if (V * (lane + 32 * i) < p.d) {
+#pragma unroll
+        for (int e = 0; e < V; ++e) { xv[i][e] -= mean; sq += xv[i][e] * xv[i][e]; }
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(sq) * inv_n + p.eps);
+    {
       // n = (x - mean) rstd, y = n w + b:  dn = dy w;  dx = rstd (dn - mean(dn) - n mean(dn n));  dw += dy n;  db += dy
       float s1 = 0.0f, s2 = 0.0f;
 #pragma unroll
@@ -519,7 +698,7 @@ __global__ void __launch_bounds__(BWD ? 128 : 256) layernorm_kernel(const __grid
       }
     }
   }
-  if constexpr (BWD) {
+  {
     if (p.dw || p.db) {
 #pragma unroll
       for (int i = 0; i < NPASS; ++i) {
@@ -533,10 +712,17 @@ __global__ void __launch_bounds__(BWD ? 128 : 256) layernorm_kernel(const __grid
         }
       }
       __syncthreads();
-      for (int i = threadIdx.x; i < p.d; i += blockDim.x) {
-        if (p.dw) atomicAdd(p.dw + i, sh_grad[i]);
-        if (p.db) atomicAdd(p.db + i, sh_grad[p.d + i]);
-      }
+      auto add_out = [&](float* dst, const float* src) {
+        if (!dst) return;
+        if (((uintptr_t)dst & 15) == 0 && p.d % 4 == 0) {
+          for (int i = 4 * threadIdx.x; i < p.d; i += 4 * blockDim.x)
+            atomicAdd(reinterpret_cast<float4*>(dst + i), make_float4(src[i], src[i + 1], src[i + 2], src[i + 3]));
+        } else {
+          for (int i = threadIdx.x; i < p.d; i += blockDim.x) atomicAdd(dst + i, src[i]);
+        }
+      };
+      add_out(p.dw, sh_grad);
+      add_out(p.db, sh_grad + p.d);
     }
   }
 }
@@ -573,27 +759,39 @@ int launch_layernorm(int dtype, bool backward, int64_t rows, int d, float eps, c
   p.rows = rows; p.x_stride = x_stride; p.y_stride = y_stride; p.d = d; p.eps = eps;
   const int V = dtype == FPB_F32 ? 4 : 8;
   const int npass = (d + 32 * V - 1) / (32 * V);
-  const int wpb = backward ? 4 : 8;
-  // backward: every CTA ends with 2d atomic adds, so no more CTAs than keep the SMs full
-  const int64_t blocks = (rows + wpb - 1) / wpb;
-  const size_t smem = backward ? 2 * (size_t)d * sizeof(float) : 0;
+  if (backward) {
+    // one wave of resident CTAs, each walking its share of the rows: a second, partial wave would cost as much as a
+    // full one, and every CTA ends with atomic adds into the 2 d gradient sums
+    int sms = 148, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    auto launch = [&](auto kernel, int threads, size_t smem, int64_t blocks) {
+      int per_sm = 0;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) != cudaSuccess || per_sm < 1) per_sm = 1;
+      const int64_t cap = (int64_t)per_sm * sms;
+      kernel<<<(int)(blocks < 1 ? 1 : (blocks < cap ? blocks : cap)), threads, smem, stream>>>(p);
+    };
+    auto go = [&](auto tag) {
+      using T = decltype(tag);
+      if (npass <= 2) {         // narrow rows: a warp per row (measured faster up to 512 bf16 / 256 fp32 channels)
+        const size_t smem = 2 * (size_t)d * sizeof(float);
+        if (npass == 1) launch(layernorm_bwd_warp_kernel<T, 1>, 128, smem, (rows + 3) / 4);
+        else launch(layernorm_bwd_warp_kernel<T, 2>, 128, smem, (rows + 3) / 4);
+      } else {                  // wide rows: the CTA across a row, two rows per step
+        constexpr int R = 2;
+        const int threads = ((d + V - 1) / V + 31) / 32 * 32;
+        launch(layernorm_bwd_kernel<T, R>, threads, (size_t)LN_DEPTH * 2 * R * threads * 16, (rows + R - 1) / R);
+      }
+    };
+    if (dtype == FPB_BF16) go(__nv_bfloat16{}); else go(float{});
+    return FPB_OK;
+  }
+  const int64_t blocks = (rows + 7) / 8;
   auto go = [&](auto tag, auto passes) {
     using T = decltype(tag);
     constexpr int NP = decltype(passes)::value;
-    if (backward) {
-      // one wave of resident CTAs, each walking its share of the rows: a second, partial wave would cost as much
-      // as a full one, and every CTA ends with 2d atomic adds
-      int per_sm = 0, sms = 148, dev = 0;
-      cudaGetDevice(&dev);
-      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, layernorm_kernel<T, NP, true>, 128, smem) != cudaSuccess || per_sm < 1)
-        per_sm = 1;
-      const int64_t cap = (int64_t)per_sm * sms;
-      layernorm_kernel<T, NP, true><<<(int)(blocks < 1 ? 1 : (blocks < cap ? blocks : cap)), 128, smem, stream>>>(p);
-    } else {
-      const int64_t cap = 148 * 16;
-      layernorm_kernel<T, NP, false><<<(int)(blocks < 1 ? 1 : (blocks < cap ? blocks : cap)), 256, 0, stream>>>(p);
-    }
+    const int64_t cap = 148 * 16;
+    layernorm_kernel<T, NP><<<(int)(blocks < 1 ? 1 : (blocks < cap ? blocks : cap)), 256, 0, stream>>>(p);
   };
   auto by_passes = [&](auto tag) {
     if (npass == 1) go(tag, std::integral_constant<int, 1>{});
