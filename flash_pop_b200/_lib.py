@@ -143,6 +143,7 @@ _DIAG_SIGNATURES = {
     "fpb_debug_pop_emit": [ctypes.c_int],
     "fpb_debug_fused_bwd": [ctypes.c_int],
     "fpb_debug_segments": [ctypes.c_int],
+    "fpb_debug_col_split": [ctypes.c_int],
     "fpb_debug_deep": [ctypes.c_int],
     "fpb_debug_ablate": [ctypes.c_int],
     "fpb_debug_tuning": [ctypes.c_longlong, ctypes.c_int, ctypes.c_int, ctypes.c_int],

@@ -125,6 +125,10 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h = blockIdx.y;
+  // dv = 2 DV: blockIdx.x is the half of dv this CTA takes.  dV and the G columns of the half are complete; dK is a
+  // partial sum over the half's columns, which TMA adds to the (zeroed) output.
+  const int vcol = (int)blockIdx.x * DV;
+  const bool dv_split = gridDim.x > 1;
   const int b = p.n_seg > 1 ? (int)blockIdx.z / p.n_seg : (int)blockIdx.z;
   const int seg = p.n_seg > 1 ? (int)blockIdx.z % p.n_seg : 0;
   // this CTA walks tokens [t0, t_end) of the sequence; chunk positions are absolute (t0 is a chunk and block multiple)
@@ -180,8 +184,8 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
         mbar_arrive_expect_tx(bar(B_FULL + s), G::STAGE_BYTES);
 #pragma unroll
         for (int cb = 0; cb < DV / 64; ++cb) {      // dO first: it has to be scaled before anything can use it
-          tma_load_4d(st + G::OFF_DO + cb * 8192, &p.map_do, bar(B_FULL + s), cb * 64, ck.a, h, b);
-          tma_load_4d(st + G::OFF_V + cb * 8192, &p.map_v, bar(B_FULL + s), cb * 64, ck.a, h, b);
+          tma_load_4d(st + G::OFF_DO + cb * 8192, &p.map_do, bar(B_FULL + s), vcol + cb * 64, ck.a, h, b);
+          tma_load_4d(st + G::OFF_V + cb * 8192, &p.map_v, bar(B_FULL + s), vcol + cb * 64, ck.a, h, b);
         }
 #pragma unroll
         for (int cb = 0; cb < DK / 64; ++cb) {
@@ -390,9 +394,14 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
       if (whole_box) {
         if (t == 0) {
 #pragma unroll
-          for (int cb = 0; cb < DV / 64; ++cb) tma_store_4d(&p.map_dv, sbase + G::OFF_OUTV + cb * 8192, cb * 64, ck.a, h, b);
+          for (int cb = 0; cb < DV / 64; ++cb) tma_store_4d(&p.map_dv, sbase + G::OFF_OUTV + cb * 8192, vcol + cb * 64, ck.a, h, b);
+          if (dv_split) {
 #pragma unroll
-          for (int cb = 0; cb < DK / 64; ++cb) tma_store_4d(&p.map_dk, sbase + G::OFF_OUTK + cb * 8192, cb * 64, ck.a, h, b);
+            for (int cb = 0; cb < DK / 64; ++cb) tma_reduce_add_4d(&p.map_dk, sbase + G::OFF_OUTK + cb * 8192, cb * 64, ck.a, h, b);
+          } else {
+#pragma unroll
+            for (int cb = 0; cb < DK / 64; ++cb) tma_store_4d(&p.map_dk, sbase + G::OFF_OUTK + cb * 8192, cb * 64, ck.a, h, b);
+          }
           tma_store_commit();
         }
       } else {   // chunk cut short by a block end: rows >= L belong to another chunk
@@ -440,7 +449,7 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
     auto row_of = [&](int i) { return DK == 128 ? q4 * 32 + lane : q4 * 16 + (lane >> 2) + 8 * ((i >> 1) & 1); };
     auto col_of = [&](int i) { return DK == 128 ? wcol0 + i : wcol0 + 8 * (i >> 2) + 2 * (lane & 3) + (i & 1); };
 
-    const int64_t state_elems = (int64_t)(DK * DV);
+    const int64_t state_elems = (int64_t)DK * p.dv;   // p.dv = DV, or 2 DV when two CTAs share a head
     // start: gradient of the returned state (none for suffix calls, whose end states are dropped);
     // end: dS_0, or for suffix m > 0 of a row the gradient of block state m-1
     const void* x_start = nullptr;
@@ -474,7 +483,7 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
     }
     auto load_global = [&](const void* src_, auto f32, bool accumulate) {
       if constexpr (decltype(f32)::value) {
-        const float* src = (const float*)src_;
+        const float* src = (const float*)src_ + vcol;
         if (DK == 128) {
           const float* rowp = src + (int64_t)row_of(0) * p.dv + wcol0;
 #pragma unroll
@@ -492,7 +501,7 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
           }
         }
       } else {
-      const bf16* src = (const bf16*)src_;
+      const bf16* src = (const bf16*)src_ + vcol;
       if (DK == 128) {
         const bf16* rowp = src + (int64_t)row_of(0) * p.dv + wcol0;
 #pragma unroll
@@ -523,7 +532,7 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
     };
     auto store_global = [&](void* dst_) {
       if constexpr (SF32) {
-        float* dst = (float*)dst_;
+        float* dst = (float*)dst_ + vcol;
         if (DK == 128) {
           float* rowp = dst + (int64_t)row_of(0) * p.dv + wcol0;
 #pragma unroll
@@ -534,7 +543,7 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
             *reinterpret_cast<float2*>(dst + (int64_t)row_of(i) * p.dv + col_of(i)) = make_float2(S[i], S[i + 1]);
         }
       } else {
-      bf16* dst = (bf16*)dst_;
+      bf16* dst = (bf16*)dst_ + vcol;
       if (DK == 128) {
         bf16* rowp = dst + (int64_t)row_of(0) * p.dv + wcol0;
 #pragma unroll
@@ -697,7 +706,11 @@ int gcd_int(int a, int b) { while (b) { const int t = a % b; a = b; b = t; } ret
 
 // dK, dV and dS_0 in one reverse walk.  FPB_UMMA_NOT_APPLICABLE when the shape is not one the kernel is built for.
 int launch_bwd_fused(const UmmaBwdArgs& a, cudaStream_t stream, int* n_launched) {
-  const bool dims_ok = (a.dk == 64 || a.dk == 128) && (a.dv == 64 || a.dv == 128);
+  // dv = 256 next to dk = 128: two CTAs per head, one per half of dv, on the 128 x 128 instance.  Each writes its half
+  // of dV and of dS_0; dK is the sum of the two CTAs' partial results, which TMA adds to the zeroed tensor in L2.  Only
+  // where every chunk is stored as a whole tile (no POP blocks, no suffixes).
+  const bool dv_halves = a.dk == 128 && a.dv == 256 && a.block_size == 0 && a.sfx_grad.M == 0 && col_split_enabled();
+  const bool dims_ok = ((a.dk == 64 || a.dk == 128) && (a.dv == 64 || a.dv == 128)) || dv_halves;
   if (!dims_ok || a.dtype != FPB_BF16 || a.T <= 0 || a.B > 65535 || a.H > 65535) return FPB_UMMA_NOT_APPLICABLE;
   if (!tma_addressable(a.q, 2) || !tma_addressable(a.k, 2) || !tma_addressable(a.v, 2) || !tma_addressable(a.dO, 2) ||
       !tma_addressable(a.dK, 2) || !tma_addressable(a.dV, 2))
@@ -726,7 +739,7 @@ int launch_bwd_fused(const UmmaBwdArgs& a, cudaStream_t stream, int* n_launched)
   Segments sg{1, 0};
   if (segments_enabled() && a.scratch && a.sfx_grad.M == 0) {
     const int align = a.block_size > 0 ? C / gcd_int(C, a.block_size) * a.block_size : C;
-    sg = choose_segments((long long)H * B, 1, T, align, (long long)B * H, (long long)a.dk * a.dv, a.scratch_bytes, B);
+    sg = choose_segments((long long)H * B * (dv_halves ? 2 : 1), 1, T, align, (long long)B * H, (long long)a.dk * a.dv, a.scratch_bytes, B);
   }
   if (sg.n > 1) {
     if ((r = launch_segment_states(a.q, a.dO, true, a.d_block_states, a.gamma, B, T, H, a.dk, a.dv, a.block_size, a.n_blocks,
@@ -757,9 +770,14 @@ int launch_bwd_fused(const UmmaBwdArgs& a, cudaStream_t stream, int* n_launched)
   p.trace = debug_trace_ptr();
   if (!p.status) return FPB_ERR_LAUNCH;
   for (int h = 0; h < H; ++h) p.log2g[h] = (float)std::log2((double)a.gamma[h]);
-  const dim3 grid(1, H, B * sg.n);
+  const dim3 grid(dv_halves ? 2 : 1, H, B * sg.n);
+  if (dv_halves) {
+    launch_zero_seq(dK, B, T, H, a.dk, stream);
+    ++*n_launched;
+  }
+  const int tile_dv = dv_halves ? 128 : a.dv;
 #define FPB_FUSED_CASE(DK_, DV_) \
-  if (a.dk == DK_ && a.dv == DV_) r = a.state_f32 ? launch_fused_t<DK_, DV_, true>(p, grid, stream) : launch_fused_t<DK_, DV_, false>(p, grid, stream)
+  if (a.dk == DK_ && tile_dv == DV_) r = a.state_f32 ? launch_fused_t<DK_, DV_, true>(p, grid, stream) : launch_fused_t<DK_, DV_, false>(p, grid, stream)
   r = FPB_ERR_BAD_SHAPE;
   FPB_FUSED_CASE(128, 128); FPB_FUSED_CASE(64, 64); FPB_FUSED_CASE(64, 128); FPB_FUSED_CASE(128, 64);
 #undef FPB_FUSED_CASE

@@ -90,6 +90,8 @@ struct ScanParams {
   int32_t sched_bs;              // block size the chunk schedule is cut at: block_size, or 0 when block states are
                                  // emitted from inside full chunks (forward walk, 64 x 64 tiles, see EMIT below)
   int32_t state_f32;             // element type of s0, s_out, block states / gradients and suffix start states
+  int32_t col_split;             // MODE_DQ walks only: the tiles cut dv (columns of the state) instead of dk, so each CTA's
+                                 // output tile is a partial sum over its dv columns; TMA adds it to `out` (zeroed before)
   int32_t n_seg, seg_len;        // T-segments: blockIdx.z = batch * n_seg + segment, segment s covers tokens [s * seg_len, ...)
   float* seg_states;             // fp32 (B, H, n_seg, dk, dv): start values of the segments (local end values in a STATE_ONLY pass)
   WalkTuning tune;
@@ -200,8 +202,9 @@ scan_kernel(const __grid_constant__ ScanParams p) {
   // this CTA walks tokens [t0, t_end) of the sequence; chunk positions are absolute (t0 is a chunk and block multiple)
   const int t0 = seg * p.seg_len;
   const int t_end = p.n_seg > 1 ? min(t0 + p.seg_len, p.T) : p.T;
-  const int row0 = MODE == MODE_FWD ? 0 : tile * R;     // state rows [row0, row0+R) of dk
-  const int col0 = MODE == MODE_FWD ? tile * CC : 0;    // state cols [col0, col0+CC) of dv
+  const bool by_cols = MODE == MODE_FWD || p.col_split != 0;
+  const int row0 = by_cols ? 0 : tile * R;              // state rows [row0, row0+R) of dk
+  const int col0 = by_cols ? tile * CC : 0;             // state cols [col0, col0+CC) of dv
   const float lg = p.log2g[h];
   const float rs = rsqrtf((float)p.dk);
   const int NC = chunk_count(t_end - t0, p.sched_bs);
@@ -548,9 +551,15 @@ FPB_UNROLL_MMA
         if (!FPB_ABL(64)) fence_async_smem();
         __syncwarp();
         if (lane == 0 && ck.a + wrow0 < p.T) {
+          if (MODE == MODE_DQ && p.col_split) {
 #pragma unroll
-          for (int cb = 0; cb < G::NOUT / 64; ++cb)
-            tma_store_4d(&p.map_out, sbase + G::OFF_OUT + cb * 8192 + wrow0 * 128, ocol0 + cb * 64, ck.a + wrow0, h, b);
+            for (int cb = 0; cb < G::NOUT / 64; ++cb)
+              tma_reduce_add_4d(&p.map_out, sbase + G::OFF_OUT + cb * 8192 + wrow0 * 128, ocol0 + cb * 64, ck.a + wrow0, h, b);
+          } else {
+#pragma unroll
+            for (int cb = 0; cb < G::NOUT / 64; ++cb)
+              tma_store_4d(&p.map_out, sbase + G::OFF_OUT + cb * 8192 + wrow0 * 128, ocol0 + cb * 64, ck.a + wrow0, h, b);
+          }
           tma_store_commit();
         }
       } else {   // chunk cut short by a block end: rows >= L belong to another chunk, store rows < L only
@@ -844,8 +853,18 @@ FPB_UNROLL_MMA
       Patience patience{0, 0};
       while (n_u < NC) {
         bool progress = false;
-        // the state copy and the state update come first: they sit on the chunk-to-chunk chain (copy -> state term ->
-        // copy of the next chunk), the tile rescaling only has to stay ahead of the products (2 % on the 128-wide walks)
+        auto try_scale = [&]() {
+          if (n_v < NC && mbar_test_wait(bar(B_FULL + stage_of(n_v)), stage_ph(n_v))) {
+            scale_v(n_v, ck_v.L);
+            if (t == 0) FPB_TRACE(11, n_v);
+            ++n_v; advance<REV>(ck_v, t_end, p.sched_bs);
+            progress = true;
+          }
+        };
+        // 128-wide walks: the state copy and the state update come first - they sit on the chunk-to-chunk chain (copy ->
+        // state term -> copy of the next chunk), the tile rescaling only has to stay ahead of the products (2 %).  The
+        // small tiles, whose products are short, want the rescaling first (the other order cost the 64 x 64 dQ walk 30 %).
+        if constexpr (!G::ONE) try_scale();
         if (publish_due) {
           // copy n_u goes into buffer n_u % NSB, which the state term of chunk n_u - NSB was the last to read
           if (n_u < G::NSB || mbar_test_wait(bar(B_SBFREE + n_u % G::NSB), (n_u / G::NSB - 1) & 1)) {
@@ -913,12 +932,7 @@ FPB_UNROLL_MMA
           }
           progress = true;
         }
-        if (n_v < NC && mbar_test_wait(bar(B_FULL + stage_of(n_v)), stage_ph(n_v))) {
-          scale_v(n_v, ck_v.L);
-          if (t == 0) FPB_TRACE(11, n_v);
-          ++n_v; advance<REV>(ck_v, t_end, p.sched_bs);
-          progress = true;
-        }
+        if constexpr (G::ONE) try_scale();
         if (progress) patience.progress();
         else if (patience.exhausted(abort_flag)) { FPB_GIVE_UP(0x400 | (n_u & 0xff)); break; }
         else if (publish_due) mbar_try_wait_hint(bar(B_SBFREE + n_u % G::NSB), (n_u / G::NSB - 1) & 1, p.tune.idle_ns);   // idle: sleep on the likely next
@@ -1001,6 +1015,7 @@ FPB_KNOB g_sfx_min_ctas = 3 * 296;   // ... as long as that many CTAs remain (th
 FPB_KNOB g_pop_emit = 1;             // 1: POP forward walks over full chunks where block states can come from partial increments
 FPB_KNOB g_fused_bwd = 1;            // 1: dK, dV, dS_0 in one fused reverse walk where it applies; 0: two separate walks
 FPB_KNOB g_segments = 1;             // 1: under-filled launches are cut into T-segments when the caller gave scratch memory
+FPB_KNOB g_col_split = 1;            // 1: dv = 256 gradient walks cut dv into 128 x 128 tiles and add their partial results
 #ifdef FPB_DIAGNOSTICS
 long long* g_trace = nullptr;        // set by fpb_debug_trace
 WalkTuning g_tuning{kWaitCycles, 200, 1, -1, 0};
@@ -1041,17 +1056,37 @@ bool pass_applicable(const PassArgs& a) {
 }
 
 // state tile and CTAs per SM of the instance a pass runs on
-struct Tiling { int R, CC, tiles, ctas_per_sm; };
-Tiling tiling_of(int mode, int dk, int dv) {
+struct Tiling { int R, CC, tiles, ctas_per_sm; bool col_split; };
+// split_ok: a MODE_DQ walk may cut dv instead of dk.  Its output tile is then a partial sum over the CTA's dv columns,
+// which TMA adds to the (zeroed) output in L2 - two addends per element when dv = 256, so the result does not depend on
+// their order.  For dv = 256 that replaces the 64 x 256 tiles (M = 64 products over 256 columns, 5400 cycles per chunk)
+// by the 128 x 128 instance.  Only walks whose chunks are all stored as whole tiles qualify (no POP blocks, no suffixes).
+Tiling tiling_of(int mode, int dk, int dv, bool split_ok) {
   if (mode == MODE_FWD) {         // state tile: all dk rows x CC columns of dv
-    if (dk == 128 && dv % 128 == 0 && g_tile_pref) return {128, 128, dv / 128, 1};
-    if (dk == 128) return {128, 64, dv / 64, 2};
-    return {64, 64, dv / 64, 2};
+    if (dk == 128 && dv % 128 == 0 && g_tile_pref) return {128, 128, dv / 128, 1, false};
+    if (dk == 128) return {128, 64, dv / 64, 2, false};
+    return {64, 64, dv / 64, 2, false};
   }                               // state tile: R rows of dk x all dv columns
-  if (dv == 128 && dk % 128 == 0 && g_tile_pref) return {128, 128, dk / 128, 1};
-  if (dv == 64) return {64, 64, dk / 64, 2};
-  if (dv == 128) return {64, 128, dk / 64, 2};
-  return {64, 256, dk / 64, 1};
+  if (dv == 128 && dk % 128 == 0 && g_tile_pref) return {128, 128, dk / 128, 1, false};
+  if (dv == 64) return {64, 64, dk / 64, 2, false};
+  if (dv == 128) return {64, 128, dk / 64, 2, false};
+  if (dk == 128 && split_ok && g_col_split && g_tile_pref) return {128, 128, dv / 128, 1, true};
+  return {64, 256, dk / 64, 1, false};
+}
+bool col_split_ok(int mode, int block_size, const SuffixStates& sfx) { return mode == MODE_DQ && block_size == 0 && sfx.M == 0; }
+
+// 16 bytes of zeros per thread over the (B, T, H, d) elements of a strided view, d a multiple of 8
+__global__ void zero_seq_kernel(bf16* base, int64_t sb, int64_t st, int64_t sh, int64_t rows, int T, int H, int d8) {
+  const int64_t total = rows * d8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / d8;
+    const int c = (int)(i - row * d8);
+    const int h = (int)(row % H);
+    const int64_t bt = row / H;
+    const int t = (int)(bt % T);
+    const int64_t b = bt / T;
+    *reinterpret_cast<uint4*>(base + b * sb + t * st + h * sh + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+  }
 }
 
 int gcd_int(int a, int b) { while (b) { const int t = a % b; a = b; b = t; } return a; }
@@ -1104,7 +1139,8 @@ int launch_one(const PassArgs& a, Segments sg, bool state_only, cudaStream_t str
   if (!p.status) return FPB_ERR_LAUNCH;
   for (int h = 0; h < H; ++h) p.log2g[h] = (float)std::log2((double)a.gamma[h]);
 
-  const Tiling t = tiling_of(mode, dk, dv);
+  const Tiling t = tiling_of(mode, dk, dv, col_split_ok(mode, a.block_size, a.sfx));
+  p.col_split = t.col_split ? 1 : 0;
   const dim3 grid(t.tiles, H, Bk * (state_only ? sg.n - 1 : sg.n));
 #define FPB_SCAN_CASE(MODE_, R_, CC_) \
   if (mode == MODE_ && t.R == R_ && t.CC == CC_) return launch_scan<MODE_, R_, CC_>(p, a.rev, state_only, grid, stream)
@@ -1119,7 +1155,7 @@ int launch_one(const PassArgs& a, Segments sg, bool state_only, cudaStream_t str
 int launch_pass(const PassArgs& a, cudaStream_t stream, int* n_launched) {
   Segments sg{1, 0};
   if (g_segments && a.scratch && a.sfx.M == 0 && a.B * 16 <= 65535) {
-    const Tiling t = tiling_of(a.mode, a.dk, a.dv);
+    const Tiling t = tiling_of(a.mode, a.dk, a.dv, col_split_ok(a.mode, a.block_size, a.sfx));
     const int align = a.block_size > 0 ? C / gcd_int(C, a.block_size) * a.block_size : C;   // segment starts: chunk and block multiples
     sg = choose_segments((long long)t.tiles * a.H * a.B, t.ctas_per_sm, a.T, align, (long long)a.B * a.H, (long long)a.dk * a.dv,
                          a.scratch_bytes, a.B);
@@ -1131,6 +1167,10 @@ int launch_pass(const PassArgs& a, cudaStream_t stream, int* n_launched) {
       return r;
     *n_launched += 2;
   }
+  if (tiling_of(a.mode, a.dk, a.dv, col_split_ok(a.mode, a.block_size, a.sfx)).col_split) {
+    launch_zero_seq(a.out, a.B, a.T, a.H, a.mode == MODE_FWD ? a.dv : a.dk, stream);   // the tiles' partial results are added to it
+    ++*n_launched;
+  }
   if ((r = launch_one(a, sg, false, stream)) != FPB_OK) return r;
   ++*n_launched;
   return FPB_OK;
@@ -1141,6 +1181,13 @@ int launch_pass(const PassArgs& a, cudaStream_t stream, int* n_launched) {
 long long* debug_trace_ptr() { return g_trace; }
 const WalkTuning& walk_tuning() { return g_tuning; }
 bool segments_enabled() { return g_segments != 0; }
+bool col_split_enabled() { return g_col_split != 0 && g_tile_pref != 0; }
+void launch_zero_seq(const SeqView& v, int B, int T, int H, int d, cudaStream_t stream) {
+  const int64_t rows = (int64_t)B * T * H, total = rows * (d / 8);
+  const int64_t blocks = (total + 255) / 256;
+  zero_seq_kernel<<<(int)(blocks < 148 * 16 ? (blocks < 1 ? 1 : blocks) : 148 * 16), 256, 0, stream>>>((bf16*)v.data, v.sb, v.st, v.sh, rows, T, H, d / 8);
+}
+
 
 int choose_suffix_group(int M, long long units) {
   for (int cand = g_sfx_group; cand > 1; --cand)
@@ -1162,6 +1209,8 @@ extern "C" void fpb_debug_pop_emit(int on) { g_pop_emit = on; }
 extern "C" void fpb_debug_fused_bwd(int on) { g_fused_bwd = on; }
 // 0 never cuts sequences into T-segments.
 extern "C" void fpb_debug_segments(int on) { g_segments = on; }
+// 0 keeps the dk-tiled 64 x 256 instances (and the two separate reverse walks) for dv = 256.
+extern "C" void fpb_debug_col_split(int on) { g_col_split = on; }
 // 0 keeps the two-CTAs-per-SM configuration of the small tiles for every grid size.
 extern "C" void fpb_debug_deep(int on) { g_deep = on; }
 // Wait limit in clock ticks (<= 0: the default of about a second), idle suspend hint in ns, early scores on / off, and the

@@ -41,6 +41,10 @@ int launch_bwd_fused(const UmmaBwdArgs& a, cudaStream_t stream, int* n_launched)
 int launch_segment_states(SeqView k, SeqView v, bool rev, const void* block_grads, const float* gamma, int B, int T, int H, int dk,
                           int dv, int block_size, int n_blocks, bool state_f32, Segments sg, float* scratch, cudaStream_t stream);
 bool segments_enabled();
+// dv = 256: the gradient walks cut dv into 128-wide tiles whose partial results TMA adds to a zeroed output
+bool col_split_enabled();
+// zeros over the (B, T, H, d) bf16 elements of a strided view (d a multiple of 8, 16-byte aligned rows)
+void launch_zero_seq(const SeqView& v, int B, int T, int H, int d, cudaStream_t stream);
 // How many consecutive suffixes of a row one CTA walks as one sequence: the largest divisor of M (up to a limit)
 // that leaves enough CTAs to fill the GPU a few times over; `units` = CTAs per suffix index (rows x heads x tiles).
 int choose_suffix_group(int M, long long units);

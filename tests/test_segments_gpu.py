@@ -42,7 +42,7 @@ def _fwd_bwd(q, k, v, s, decays, dO, dS):
     (2, 2048, 2, 64, 64, True),
     (1, 3000, 2, 64, 128, True),
     (1, 2048, 2, 128, 64, False),
-    (1, 4096, 2, 128, 256, True),       # dv = 256: the backward runs as separate reverse walks
+    (1, 4096, 2, 128, 256, True),       # dv = 256: two CTAs per head (dv halves) in the dQ walk and the fused reverse walk
 ])
 def test_split_walks_equal_unsplit(B, T, H, dk, dv, state):
     from flash_pop_b200 import _lib
