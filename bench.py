@@ -444,10 +444,11 @@ NCU_TRAFFIC = {
     ("ns", "fwd"): _traffic(503387136, 145907200, 8 / 5, "ncu at B=5, scaled x8/5 by token-heads"),
     ("ns", "dq"): _traffic(503387392, 145740800, 8 / 5, "ncu at B=5, scaled x8/5 by token-heads"),
     ("ns", "rev"): _traffic(671177984, 304712448, 8 / 5, "ncu at B=5, scaled x8/5 by token-heads"),
-    ("c3", "fwd"): _traffic(1073822208, 507802368, 2, "ncu at B=2, scaled x2 by token-heads"),
-    ("c3", "dq"): _traffic(1343727360, 257168384, 2, "ncu at B=2, scaled x2 by token-heads"),
-    ("c3", "rev"): _traffic(1073847552 + 1343894784, 506097152 + 257013248, 2,
-                            "ncu at B=2 (the dV walk and the dK walk, two launches), scaled x2 by token-heads"),
+    ("c3", "fwd"): _traffic(1073861888, 506872064, 2, "ncu at B=2, scaled x2 by token-heads"),
+    ("c3", "dq"): _traffic(20992 + 1610695168, 211433984 + 253492736, 2,
+                           "ncu at B=2 (zero fill of dQ and the dQ walk over the two halves of dv), scaled x2 by token-heads"),
+    ("c3", "rev"): _traffic(21248 + 1914728704, 211275776 + 790550272, 2,
+                            "ncu at B=2 (zero fill of dK and the fused reverse walk over the two halves of dv), scaled x2 by token-heads"),
     ("c4", "fwd"): _traffic(251724800, 112073728, 1, "ncu at the full workload"),
     ("c4", "dq"): _traffic(251713280, 59949824, 1, "ncu at the full workload"),
     ("c4", "rev"): _traffic(335681792, 137124096, 1, "ncu at the full workload"),

@@ -1075,17 +1075,18 @@ Tiling tiling_of(int mode, int dk, int dv, bool split_ok) {
 }
 bool col_split_ok(int mode, int block_size, const SuffixStates& sfx) { return mode == MODE_DQ && block_size == 0 && sfx.M == 0; }
 
-// 16 bytes of zeros per thread over the (B, T, H, d) elements of a strided view, d a multiple of 8
-__global__ void zero_seq_kernel(bf16* base, int64_t sb, int64_t st, int64_t sh, int64_t rows, int T, int H, int d8) {
-  const int64_t total = rows * d8;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t row = i / d8;
-    const int c = (int)(i - row * d8);
-    const int h = (int)(row % H);
-    const int64_t bt = row / H;
-    const int t = (int)(bt % T);
-    const int64_t b = bt / T;
-    *reinterpret_cast<uint4*>(base + b * sb + t * st + h * sh + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+// Zeros over the (B, T, H, d) elements of a strided bf16 view, d a multiple of 8: a CTA takes ZERO_TOKENS tokens of a
+// batch row and writes their H * d / 8 16-byte pieces each (32-bit index arithmetic: a 64-bit division per piece made
+// the fill issue-bound at half the HBM write rate).
+constexpr int ZERO_TOKENS = 16;
+__global__ void __launch_bounds__(256) zero_seq_kernel(bf16* base, int64_t sb, int64_t st, int64_t sh, int T, int H, int d8) {
+  const int t0 = blockIdx.x * ZERO_TOKENS, nt = min(ZERO_TOKENS, T - t0);
+  bf16* row = base + (int64_t)blockIdx.y * sb + (int64_t)t0 * st;
+  const uint32_t per_token = (uint32_t)(H * d8), total = (uint32_t)nt * per_token;
+  for (uint32_t i = threadIdx.x; i < total; i += blockDim.x) {
+    const uint32_t t = i / per_token, r = i - t * per_token;
+    const uint32_t h = r / (uint32_t)d8, c = r - h * (uint32_t)d8;
+    *reinterpret_cast<uint4*>(row + (int64_t)t * st + (int64_t)h * sh + c * 8) = make_uint4(0u, 0u, 0u, 0u);
   }
 }
 
@@ -1183,9 +1184,8 @@ const WalkTuning& walk_tuning() { return g_tuning; }
 bool segments_enabled() { return g_segments != 0; }
 bool col_split_enabled() { return g_col_split != 0 && g_tile_pref != 0; }
 void launch_zero_seq(const SeqView& v, int B, int T, int H, int d, cudaStream_t stream) {
-  const int64_t rows = (int64_t)B * T * H, total = rows * (d / 8);
-  const int64_t blocks = (total + 255) / 256;
-  zero_seq_kernel<<<(int)(blocks < 148 * 16 ? (blocks < 1 ? 1 : blocks) : 148 * 16), 256, 0, stream>>>((bf16*)v.data, v.sb, v.st, v.sh, rows, T, H, d / 8);
+  if (B <= 0 || T <= 0) return;
+  zero_seq_kernel<<<dim3((T + ZERO_TOKENS - 1) / ZERO_TOKENS, B), 256, 0, stream>>>((bf16*)v.data, v.sb, v.st, v.sh, T, H, d / 8);
 }
 
 
