@@ -125,11 +125,15 @@ struct Cfg {
   static constexpr bool SOLO = ONE || DEEP;                  // one CTA per SM
   static constexpr int STATE_WARPS = ONE ? 8 : 4;
   static constexpr int N_STATE = 32 * STATE_WARPS;
-  // one-CTA-per-SM configurations issue their products from two warps (see the MMA issuer in the kernel); the second
-  // one is the CTA's last warp
-  static constexpr bool SPLIT = ONE;      // (the deep 64 x 64 variant lost 7 % with it; 64 x 256 is indifferent)
+  // The 128-wide one-CTA-per-SM configurations issue their products from THREE warps, one per chain of products, each a
+  // plain loop over the chunks that blocks on the barriers of its next product: scores | increment | state term, then
+  // intra-chunk term (same accumulator, in that order).  One warp polling for whichever product is ready - about 3000
+  // cycles of barrier tests, descriptor arithmetic, tcgen05.mma and commits per chunk - was the walk's pacemaker; two
+  // polling warps gained 5-6 %, three blocking ones another 2-3 %.  (The deep 64 x 64 variant gains nothing from either.)
+  static constexpr int NMMA = ONE ? 3 : 1;
   static constexpr int MMAB_WARP = STATE_WARP0 + STATE_WARPS;
-  static constexpr int NTHREADS = STATE_WARP0 * 32 + N_STATE + (SPLIT ? 32 : 0);
+  static constexpr int MMAC_WARP = MMAB_WARP + 1;
+  static constexpr int NTHREADS = STATE_WARP0 * 32 + N_STATE + (NMMA - 1) * 32;
   static constexpr int MIN_CTAS = SOLO ? 1 : 2;
   static constexpr int NP = SOLO ? 2 : 1;                    // P' buffers
   static constexpr int X_BYTES = C * W1 * 2, K_BYTES = C * R * 2, V_BYTES = C * CC * 2;
@@ -221,7 +225,7 @@ scan_kernel(const __grid_constant__ ScanParams p) {
 
   if (tid == 0) {
     for (int s = 0; s < G::STAGES; ++s) {
-      mbar_init(bar(B_FULL + s), 1); mbar_init(bar(B_EMPTY + s), (G::SPLIT && !SO) ? 2 : 1); mbar_init(bar(B_VRDY + s), ARR_STATE);
+      mbar_init(bar(B_FULL + s), 1); mbar_init(bar(B_EMPTY + s), SO ? 1 : G::NMMA); mbar_init(bar(B_VRDY + s), ARR_STATE);
     }
     for (int j = 0; j < 2; ++j) {
       mbar_init(bar(B_SCFULL + j), 1); mbar_init(bar(B_PRDY + j), ARR_SCORE);
@@ -284,17 +288,14 @@ scan_kernel(const __grid_constant__ ScanParams p) {
         }
       }
     }
-  } else if (warp == 1 || (G::SPLIT && warp == G::MMAB_WARP)) {   // ---------------- MMA issuer(s)
+  } else if (warp == 1 || (G::NMMA >= 2 && warp == G::MMAB_WARP) || (G::NMMA == 3 && warp == G::MMAC_WARP)) {   // ---------------- MMA issuer(s)
     // The whole warp runs this loop with warp-uniform control flow and data (barrier tests are made uniform by a
     // vote), so that descriptors and counters stay in the uniform datapath; one elected lane issues.
     //
-    // A chunk is four product groups - scores, increment, state term, intra-chunk term - and the thread that issues them
-    // is the walk's pacemaker: about 3000 cycles of barrier tests, descriptor arithmetic, tcgen05.mma and commits per
-    // chunk, more than the chunk's HBM time.  The one-CTA-per-SM configurations therefore split the issue over TWO
-    // warps along the only line that needs no ordering between them: warp A issues the products that depend on the
-    // tiles alone (scores, increment), warp B the two accumulator products (state term, then intra-chunk term, in that
-    // order on the same accumulator).  A stage goes back to the producer when both have committed their last product
-    // of its chunk.
+    // A chunk is four product groups - scores, increment, state term, intra-chunk term.  Two ways of issuing them:
+    // one warp that polls for whichever product has its inputs (`issue_loop`: the small tiles, and every state-only
+    // pass), or three warps with one blocking loop each (the 128-wide tiles, see Cfg::NMMA).  A stage goes back to the
+    // producer when every issuing warp has committed its last product of the stage's chunk.
     if (NC > 0 && !(SO && warp != 1)) {
       const bool leader = elect_one();
       constexpr uint32_t ID_SC = idesc_bf16(64, 64, 0, 0);
@@ -323,7 +324,8 @@ scan_kernel(const __grid_constant__ ScanParams p) {
         FPB_PROF_END(0);
         return ok;
       };
-      // DO_A: this warp issues scores and increment (and the POP partial increments); DO_B: state and intra-chunk terms
+      // one polling warp for all four products (DO_A: scores, increment, POP partial increments; DO_B: state and
+      // intra-chunk terms - both set wherever this loop is used)
       auto issue_loop = [&](auto do_a, auto do_b) {
         constexpr bool DO_A = decltype(do_a)::value, DO_B = decltype(do_b)::value;
         constexpr bool BOTH = DO_A && DO_B;
@@ -477,9 +479,105 @@ FPB_UNROLL_MMA
           }
         }
       };
-      if (!G::SPLIT || SO) issue_loop(std::true_type{}, std::true_type{});
-      else if (warp == 1) issue_loop(std::true_type{}, std::false_type{});
-      else issue_loop(std::false_type{}, std::true_type{});
+      // ---- three blocking issue loops (NMMA == 3), one warp each
+      auto wait_or_quit = [&](int slot, uint32_t parity, int code) {
+        if (mbar_wait(bar(slot), parity, abort_flag)) return true;
+        if (leader) FPB_GIVE_UP(code);
+        return false;
+      };
+      auto scores_loop = [&]() {                        // warp 1: Sc(n) = X K^T | X Veta^T
+        const bool early = MODE == MODE_FWD && p.tune.sc_early;
+        for (int n = 0; n < NC; ++n) {
+          // the score tile of chunk n - NSC must have been read out (P' of that chunk written)
+          if (n >= G::NSC && !wait_or_quit(B_PRDY + (n - G::NSC) % G::NP, ((n - G::NSC) / G::NP) & 1, 0x200 | (n & 0xff))) return;
+          if (!wait_or_quit((early ? B_FULL : B_VRDY) + stage_of(n), stage_ph(n), 0x200 | (n & 0xff))) return;
+          tc_fence_after();
+          const uint64_t so = (uint64_t)(stage_of(n) * STAGE16);
+          const uint32_t d = tm + tm_sc(n);
+          const uint64_t bk = (MODE == MODE_FWD ? d_kk : d_vk) + so;
+          if (leader) {
+FPB_UNROLL_MMA
+            for (int ks = 0; ks < G::W1 / 16; ++ks) umma_bf16(d, d_x + so + kstep(ks, 8192), bk + kstep(ks, 8192), ID_SC, ks > 0);
+            umma_commit(bar(B_SCFULL + n % G::NSC));
+            umma_commit(bar(B_EMPTY + stage_of(n)));
+            FPB_TRACE(0, n);
+          }
+          __syncwarp();
+        }
+      };
+      auto increment_loop = [&]() {                     // warp C: dS(n) = K^T Veta, and the POP partial increments
+        int m_dsp = 0;
+        for (int n = 0; n < NC; ++n) {
+          if (!wait_or_quit(B_VRDY + stage_of(n), stage_ph(n), 0x600 | (n & 0xff))) return;
+          if (n >= 2 && !wait_or_quit(B_DSFREE + (n & 1), ((n >> 1) & 1) ^ 1, 0x600 | (n & 0xff))) return;
+          tc_fence_after();
+          const uint64_t so = (uint64_t)(stage_of(n) * STAGE16);
+          if (leader) {
+FPB_UNROLL_MMA
+            for (int ks = 0; ks < C / 16; ++ks) umma_bf16(tm + tm_ds(n), d_km + so + mstep(ks), d_vm + so + mstep(ks), ID_DS, ks > 0);
+            umma_commit(bar(B_DSFULL + (n & 1)));
+            FPB_TRACE(4, n);
+          }
+          if (G::EMIT && emit) {
+            const int pmid = mid_end(n);
+            if (pmid > 0) {
+              if (m_dsp > 0 && !wait_or_quit(B_DSPFREE, (m_dsp - 1) & 1, 0x600 | (n & 0xff))) return;
+              tc_fence_after();
+              if (leader) {
+                for (int ks = 0; ks < pmid / 16; ++ks) umma_bf16(tm + G::TM_DSP, d_km + so + mstep(ks), d_vm + so + mstep(ks), ID_DS, ks > 0);
+                umma_commit(bar(B_DSPFULL));
+              }
+              ++m_dsp;
+            }
+          }
+          if (leader) { umma_commit(bar(B_EMPTY + stage_of(n))); FPB_TRACE(5, n); }
+          __syncwarp();
+        }
+      };
+      auto accumulator_loop = [&]() {                   // warp B: ACC(n) = X Sb, then += P' Veta (same accumulator, in order)
+        for (int n = 0; n < NC; ++n) {
+          if (!wait_or_quit(B_VRDY + stage_of(n), stage_ph(n), 0x500 | (n & 0xff))) return;
+          if (n >= G::NACC && !wait_or_quit(B_ACCFREE + n % G::NACC, ((n / G::NACC) & 1) ^ 1, 0x500 | (n & 0xff))) return;
+          if (!wait_or_quit(B_SBRDY + n % G::NSB, (n / G::NSB) & 1, 0x500 | (n & 0xff))) return;
+          tc_fence_after();
+          const uint64_t so = (uint64_t)(stage_of(n) * STAGE16);
+          const uint32_t acc = tm + tm_acc(n);
+          const uint64_t sbo = (uint64_t)((n % G::NSB) * (G::SB_BYTES >> 4));
+          if (leader) {
+            FPB_TRACE(2, n);
+            if (MODE == MODE_FWD) {
+FPB_UNROLL_MMA
+              for (int ks = 0; ks < R / 16; ++ks) umma_bf16(acc, d_x + so + kstep(ks, 8192), d_sb + sbo + mstep(ks), ID_STATE, ks > 0);
+            } else {
+FPB_UNROLL_MMA
+              for (int ks = 0; ks < CC / 16; ++ks) umma_bf16(acc, d_x + so + kstep(ks, 8192), d_sb + sbo + kstep(ks, R * 128), ID_STATE, ks > 0);
+            }
+            umma_commit(bar(B_SBFREE + n % G::NSB));
+            FPB_TRACE(1, n);
+          }
+          if (!wait_or_quit(B_PRDY + n % G::NP, (n / G::NP) & 1, 0x500 | (n & 0xff))) return;
+          tc_fence_after();
+          const uint64_t a = d_p + (uint64_t)((n % G::NP) * (G::P_BYTES >> 4));
+          const uint64_t bm = (MODE == MODE_FWD ? d_vm : d_km) + so;
+          if (leader) {
+            FPB_TRACE(15, n);
+FPB_UNROLL_MMA
+            for (int ks = 0; ks < C / 16; ++ks) umma_bf16(acc, a + kstep(ks, 0), bm + mstep(ks), ID_INTRA, 1);
+            umma_commit(bar(B_ACCFULL + n % G::NACC));
+            umma_commit(bar(B_EMPTY + stage_of(n)));
+            FPB_TRACE(3, n);
+          }
+          __syncwarp();
+        }
+      };
+      if constexpr (G::NMMA == 3 && !SO) {
+        static_assert(G::NP == G::NSC, "the scores warp reads the P' barrier as 'score tile free'");
+        if (warp == 1) scores_loop();
+        else if (warp == G::MMAB_WARP) accumulator_loop();
+        else increment_loop();
+      } else {
+        issue_loop(std::true_type{}, std::true_type{});
+      }
       if (warp == 1) FPB_PROF_STORE();
     }
   } else if (warp < STATE_WARP0) {                   // ---------------- score warps
@@ -850,6 +948,66 @@ FPB_UNROLL_MMA
       bool publish_due = !SO, partial_due = emit && !SO && mid_end(0) > 0;   // partial_due: chunk n_u has a block end inside
       Chunk ck_v = first, ck_u = first;
       inject(first.a + first.L);
+      // block state from the partial increment of chunk n_u (its barrier has completed)
+      auto emit_block_state = [&]() {
+        tc_fence_after();
+        const int pmid = mid_end(n_u);
+        const float gp = exp2f((float)pmid * lg), up = exp2f(-(float)(ck_u.L - pmid) * lg) * rs;
+        void* dst_ = at(p.block_states, (((int64_t)b * p.n_blocks + ((ck_u.a + pmid) / p.block_size - 1)) * p.H + h) * state_elems);
+#pragma unroll
+        for (int i0 = 0; i0 < G::NS; i0 += 16) {
+          uint32_t r[16];
+          tmem_ld_16x256b_x4(tm + lane_base + G::TM_DSP + wcol0 + i0 * 2, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; i += 2) {
+            const float lo = fmaf(gp, S[i0 + i], up * __uint_as_float(r[i])), hi = fmaf(gp, S[i0 + i + 1], up * __uint_as_float(r[i + 1]));
+            const int64_t off = (int64_t)(row0 + row_of(i0 + i)) * p.dv + col0 + col_of(i0 + i);
+            if (SF32) *reinterpret_cast<float2*>((float*)dst_ + off) = make_float2(lo, hi);
+            else *reinterpret_cast<uint32_t*>((bf16*)dst_ + off) = pack_bf16(lo, hi);
+          }
+        }
+        tc_fence_before();
+        warp_arrive(bar(B_DSPFREE));
+        ++m_part; partial_due = false;
+      };
+      // U(n_u): S <- gamma^L S + dS(n_u) (its barrier has completed), and what follows a chunk's end
+      auto update_state = [&]() {
+        if (t == 0) FPB_TRACE(12, n_u);
+        tc_fence_after();
+        const float gl = exp2f((float)ck_u.L * lg);
+        // 16 registers at a time keeps the state warps inside the register budget
+#pragma unroll
+        for (int i0 = 0; i0 < (FPB_ABL(16) ? 0 : G::NS); i0 += 16) {
+          uint32_t r[16];
+          if (R == 128) tmem_ld_32x32b_x16(tm + lane_base + tm_ds(n_u) + wcol0 + i0, r);
+          else tmem_ld_16x256b_x4(tm + lane_base + tm_ds(n_u) + wcol0 + i0 * 2, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) S[i0 + i] = fmaf(gl, S[i0 + i], ds_scale * __uint_as_float(r[i]));
+        }
+        tc_fence_before();
+        warp_arrive(bar(B_DSFREE + (n_u & 1)));   // the increment has been read: the one after next may overwrite it
+        const int end = ck_u.a + ck_u.L;
+        if (!REV && !SO && p.block_size > 0 && p.block_states && end % p.block_size == 0 && end / p.block_size - 1 < p.n_blocks)
+          store_global(at(p.block_states, (((int64_t)b * p.n_blocks + (end / p.block_size - 1)) * p.H + h) * state_elems), state_t);
+        ++n_u;
+        if (n_u < NC) {
+          advance<REV>(ck_u, t_end, p.sched_bs);
+          if (!REV && !SO && p.sfx_G > 1 && ck_u.a % p.block_size == 0) {
+            // grouped suffixes: the next chunk opens the next suffix, which starts from its own state
+            const void* src = sfx_start(sfx_m0 + ck_u.a / p.block_size);
+            if (src) load_global(src, state_t, false);
+            else {
+#pragma unroll
+              for (int i = 0; i < G::NS; ++i) S[i] = 0.f;
+            }
+          }
+          inject(ck_u.a + ck_u.L);
+          publish_due = !SO;
+          partial_due = emit && !SO && mid_end(n_u) > 0;
+        }
+      };
       Patience patience{0, 0};
       while (n_u < NC) {
         bool progress = false;
@@ -874,62 +1032,11 @@ FPB_UNROLL_MMA
           }
         } else if (G::EMIT && partial_due) {
           if (mbar_test_wait(bar(B_DSPFULL), m_part & 1)) {
-            tc_fence_after();
-            const int pmid = mid_end(n_u);
-            const float gp = exp2f((float)pmid * lg), up = exp2f(-(float)(ck_u.L - pmid) * lg) * rs;
-            void* dst_ = at(p.block_states, (((int64_t)b * p.n_blocks + ((ck_u.a + pmid) / p.block_size - 1)) * p.H + h) * state_elems);
-#pragma unroll
-            for (int i0 = 0; i0 < G::NS; i0 += 16) {
-              uint32_t r[16];
-              tmem_ld_16x256b_x4(tm + lane_base + G::TM_DSP + wcol0 + i0 * 2, r);
-              tmem_wait_ld();
-#pragma unroll
-              for (int i = 0; i < 16; i += 2) {
-                const float lo = fmaf(gp, S[i0 + i], up * __uint_as_float(r[i])), hi = fmaf(gp, S[i0 + i + 1], up * __uint_as_float(r[i + 1]));
-                const int64_t off = (int64_t)(row0 + row_of(i0 + i)) * p.dv + col0 + col_of(i0 + i);
-                if (SF32) *reinterpret_cast<float2*>((float*)dst_ + off) = make_float2(lo, hi);
-                else *reinterpret_cast<uint32_t*>((bf16*)dst_ + off) = pack_bf16(lo, hi);
-              }
-            }
-            tc_fence_before();
-            warp_arrive(bar(B_DSPFREE));
-            ++m_part; partial_due = false; progress = true;
+            emit_block_state();
+            progress = true;
           }
         } else if (mbar_test_wait(bar(B_DSFULL + (n_u & 1)), (n_u >> 1) & 1)) {
-          if (t == 0) FPB_TRACE(12, n_u);
-          tc_fence_after();
-          const float gl = exp2f((float)ck_u.L * lg);
-          // 16 registers at a time keeps the state warps inside the register budget
-#pragma unroll
-          for (int i0 = 0; i0 < (FPB_ABL(16) ? 0 : G::NS); i0 += 16) {
-            uint32_t r[16];
-            if (R == 128) tmem_ld_32x32b_x16(tm + lane_base + tm_ds(n_u) + wcol0 + i0, r);
-            else tmem_ld_16x256b_x4(tm + lane_base + tm_ds(n_u) + wcol0 + i0 * 2, r);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 16; ++i) S[i0 + i] = fmaf(gl, S[i0 + i], ds_scale * __uint_as_float(r[i]));
-          }
-          tc_fence_before();
-          warp_arrive(bar(B_DSFREE + (n_u & 1)));   // the increment has been read: the one after next may overwrite it
-          const int end = ck_u.a + ck_u.L;
-          if (!REV && !SO && p.block_size > 0 && p.block_states && end % p.block_size == 0 && end / p.block_size - 1 < p.n_blocks)
-            store_global(at(p.block_states, (((int64_t)b * p.n_blocks + (end / p.block_size - 1)) * p.H + h) * state_elems), state_t);
-          ++n_u;
-          if (n_u < NC) {
-            advance<REV>(ck_u, t_end, p.sched_bs);
-            if (!REV && !SO && p.sfx_G > 1 && ck_u.a % p.block_size == 0) {
-              // grouped suffixes: the next chunk opens the next suffix, which starts from its own state
-              const void* src = sfx_start(sfx_m0 + ck_u.a / p.block_size);
-              if (src) load_global(src, state_t, false);
-              else {
-#pragma unroll
-                for (int i = 0; i < G::NS; ++i) S[i] = 0.f;
-              }
-            }
-            inject(ck_u.a + ck_u.L);
-            publish_due = !SO;
-            partial_due = emit && !SO && mid_end(n_u) > 0;
-          }
+          update_state();
           progress = true;
         }
         if constexpr (G::ONE) try_scale();
