@@ -441,9 +441,9 @@ def _traffic(read_b, write_b, scale, what):
 
 
 NCU_TRAFFIC = {
-    ("ns", "fwd"): _traffic(503387136, 145907200, 8 / 5, "ncu at B=5, scaled x8/5 by token-heads"),
-    ("ns", "dq"): _traffic(503387392, 145740800, 8 / 5, "ncu at B=5, scaled x8/5 by token-heads"),
-    ("ns", "rev"): _traffic(671177984, 304712448, 8 / 5, "ncu at B=5, scaled x8/5 by token-heads"),
+    ("ns", "fwd"): _traffic(503399936, 145707776, 8 / 5, "ncu at B=5, scaled x8/5 by token-heads"),
+    ("ns", "dq"): _traffic(503390720, 146074624, 8 / 5, "ncu at B=5, scaled x8/5 by token-heads"),
+    ("ns", "rev"): _traffic(671247104, 304547328, 8 / 5, "ncu at B=5, scaled x8/5 by token-heads"),
     ("c3", "fwd"): _traffic(1073861888, 506872064, 2, "ncu at B=2, scaled x2 by token-heads"),
     ("c3", "dq"): _traffic(20992 + 1610695168, 211433984 + 253492736, 2,
                            "ncu at B=2 (zero fill of dQ and the dQ walk over the two halves of dv), scaled x2 by token-heads"),
