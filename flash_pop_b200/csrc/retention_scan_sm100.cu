@@ -28,14 +28,15 @@
 // the column scale already folded into Veta, so no [C,C] mask table is needed.
 //
 // Warp roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 "score" warps (P', output epilogue),
-// warps 6.. "state" warps (in-place row scaling of V, state update, bf16 state copy).  All hand-offs
-// are mbarriers; every wait is bounded and reports through the status word instead of hanging.
+// warps 6.. "state" warps (in-place row scaling of V, state update, bf16 state copy), and in the 128-wide tiles two
+// more MMA-issuing warps after them (Cfg::NMMA).  All hand-offs are mbarriers; every wait is bounded and reports
+// through the status word instead of hanging.
 //
 // Scheduling.  Per chunk the work is a feed-forward chain (TMA -> V scaling -> Sc, dS -> P', state update
 // -> X Sb, P' V -> epilogue) whose every hand-off costs a few hundred cycles; only the fp32 state
 // recurrence in the state warps' registers is truly serial.  So no role walks the chunks in lock step:
-// the MMA issuer, the state warps and the score warps each POLL their input barriers and run whichever of
-// their tasks is ready (scores of chunk n+1 before the products of chunk n if that is what has arrived),
+// the state warps and the score warps (and the MMA issuer where it is one warp) each POLL their input barriers and run
+// whichever of their tasks is ready (scores of chunk n+1 before the products of chunk n if that is what has arrived),
 // with the score tile, P' and the accumulator double-buffered where tensor/shared memory allows, so that
 // several chunks are in flight per SM and the chain latency is hidden.
 //
@@ -51,6 +52,10 @@
 // Suffix calls (thousands of sequences of a few chunks, each starting from its own state and dropping its end
 // state) may be regrouped by the launcher: G consecutive suffixes of a row as one sequence of G*T tokens with block
 // size T, the state replaced at every suffix start - same results, one CTA set-up per G suffixes.
+//
+// dv = 256 beside dk = 128.  A MODE_DQ walk may cut dv instead of dk (ScanParams::col_split): two CTAs per head on the
+// 128 x 128 instance, each with its half of the state columns; its output tile is then a partial sum, which the TMA
+// unit adds to the zeroed output (cp.reduce.async.bulk.tensor, performed in L2).
 #include <atomic>
 #include <cmath>
 #include <type_traits>
