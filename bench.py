@@ -449,9 +449,9 @@ NCU_TRAFFIC = {
                            "ncu at B=2 (zero fill of dQ and the dQ walk over the two halves of dv), scaled x2 by token-heads"),
     ("c3", "rev"): _traffic(21248 + 1914728704, 211275776 + 790550272, 2,
                             "ncu at B=2 (zero fill of dK and the fused reverse walk over the two halves of dv), scaled x2 by token-heads"),
-    ("c4", "fwd"): _traffic(251724800, 112073728, 1, "ncu at the full workload"),
-    ("c4", "dq"): _traffic(251713280, 59949824, 1, "ncu at the full workload"),
-    ("c4", "rev"): _traffic(335681792, 137124096, 1, "ncu at the full workload"),
+    ("c4", "fwd"): _traffic(251720960, 112434176, 1, "ncu at the full workload"),
+    ("c4", "dq"): _traffic(251710208, 60016384, 1, "ncu at the full workload"),
+    ("c4", "rev"): _traffic(335696896, 136674560, 1, "ncu at the full workload"),
 }
 
 

@@ -128,7 +128,9 @@ struct Cfg {
   // one CTA per SM for the large state tiles (128x128, 64x256), two for the small ones
   static constexpr bool ONE = R * CC >= 128 * 128;
   static constexpr bool SOLO = ONE || DEEP;                  // one CTA per SM
-  static constexpr int STATE_WARPS = ONE ? 8 : 4;
+  // state warps: their three tasks per chunk are latency, not instructions, so a CTA that has its SM to itself spreads
+  // the state over eight warps (the deep 64 x 64 variant: forward -8 %, dQ walk -13 % against four; sixteen: +4 %)
+  static constexpr int STATE_WARPS = (ONE || DEEP) ? 8 : 4;
   static constexpr int N_STATE = 32 * STATE_WARPS;
   // The 128-wide one-CTA-per-SM configurations issue their products from THREE warps, one per chain of products, each a
   // plain loop over the chunks that blocks on the barriers of its next product: scores | increment | state term, then
@@ -953,6 +955,8 @@ FPB_UNROLL_MMA
       bool publish_due = !SO, partial_due = emit && !SO && mid_end(0) > 0;   // partial_due: chunk n_u has a block end inside
       Chunk ck_v = first, ck_u = first;
       inject(first.a + first.L);
+      constexpr int TSTEP = 16;                            // state registers per tensor-memory load
+      static_assert(G::NS % TSTEP == 0, "a state-warp thread holds whole loads of its slice");
       // block state from the partial increment of chunk n_u (its barrier has completed)
       auto emit_block_state = [&]() {
         tc_fence_after();
@@ -960,12 +964,12 @@ FPB_UNROLL_MMA
         const float gp = exp2f((float)pmid * lg), up = exp2f(-(float)(ck_u.L - pmid) * lg) * rs;
         void* dst_ = at(p.block_states, (((int64_t)b * p.n_blocks + ((ck_u.a + pmid) / p.block_size - 1)) * p.H + h) * state_elems);
 #pragma unroll
-        for (int i0 = 0; i0 < G::NS; i0 += 16) {
-          uint32_t r[16];
+        for (int i0 = 0; i0 < G::NS; i0 += TSTEP) {
+          uint32_t r[TSTEP];
           tmem_ld_16x256b_x4(tm + lane_base + G::TM_DSP + wcol0 + i0 * 2, r);
           tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 16; i += 2) {
+          for (int i = 0; i < TSTEP; i += 2) {
             const float lo = fmaf(gp, S[i0 + i], up * __uint_as_float(r[i])), hi = fmaf(gp, S[i0 + i + 1], up * __uint_as_float(r[i + 1]));
             const int64_t off = (int64_t)(row0 + row_of(i0 + i)) * p.dv + col0 + col_of(i0 + i);
             if (SF32) *reinterpret_cast<float2*>((float*)dst_ + off) = make_float2(lo, hi);
@@ -983,13 +987,13 @@ FPB_UNROLL_MMA
         const float gl = exp2f((float)ck_u.L * lg);
         // 16 registers at a time keeps the state warps inside the register budget
 #pragma unroll
-        for (int i0 = 0; i0 < (FPB_ABL(16) ? 0 : G::NS); i0 += 16) {
-          uint32_t r[16];
-          if (R == 128) tmem_ld_32x32b_x16(tm + lane_base + tm_ds(n_u) + wcol0 + i0, r);
+        for (int i0 = 0; i0 < (FPB_ABL(16) ? 0 : G::NS); i0 += TSTEP) {
+          uint32_t r[TSTEP];
+          if constexpr (R == 128) tmem_ld_32x32b_x16(tm + lane_base + tm_ds(n_u) + wcol0 + i0, r);
           else tmem_ld_16x256b_x4(tm + lane_base + tm_ds(n_u) + wcol0 + i0 * 2, r);
           tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) S[i0 + i] = fmaf(gl, S[i0 + i], ds_scale * __uint_as_float(r[i]));
+          for (int i = 0; i < TSTEP; ++i) S[i0 + i] = fmaf(gl, S[i0 + i], ds_scale * __uint_as_float(r[i]));
         }
         tc_fence_before();
         warp_arrive(bar(B_DSFREE + (n_u & 1)));   // the increment has been read: the one after next may overwrite it
