@@ -15,15 +15,16 @@ pytestmark = pytest.mark.gpu
 BF = torch.bfloat16
 
 
-@pytest.mark.parametrize("d,backward", [(64, False), (128, False), (128, True), (64, True)])
-def test_wait_limit_runs_out_and_the_context_survives(d, backward):
+@pytest.mark.parametrize("d,dv,backward", [(64, 64, False), (128, 128, False), (128, 128, True), (64, 64, True),
+                                          (128, 256, True)])      # dv = 256: the score warps of the dQ walk meet at named barriers
+def test_wait_limit_runs_out_and_the_context_survives(d, dv, backward):
     import ctypes
     import flash_pop_b200 as fp
     from flash_pop_b200 import _lib
     B, T, H = 1, 128, 2
     decays = orc.head_decays(H, (5, 12))
-    q, k, v, s, g = make_inputs(3, B, T, H, d, d, BF)
-    dO = torch.randn(B, T, H, d, generator=g).to(BF)
+    q, k, v, s, g = make_inputs(3, B, T, H, d, dv, BF)
+    dO = torch.randn(B, T, H, dv, generator=g).to(BF)
     dev = [t.cuda() for t in (q, k, v, s, dO)]
 
     def step():
