@@ -44,15 +44,21 @@ __global__ void __launch_bounds__(256) segment_combine_kernel(const __grid_const
   float* seg = p.seg + ((int64_t)b * p.H + h) * p.n_seg * p.state_floats + e;
   float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
   if (p.start) a = load4(p.start, b * p.start_sb + h * p.start_sh + e, p.state_f32 != 0);
+  // The local values do not depend on the running value, so the next one is fetched before the current slot is
+  // overwritten: the n loads overlap instead of queueing behind one another's stores (the chain of n dependent
+  // round trips made this scan the longest of a split call's three launches).
+  auto slot_of = [&](int i) { return reinterpret_cast<float4*>(seg + (int64_t)(p.reverse ? p.n_seg - 1 - i : i) * p.state_floats); };
+  float4 loc = p.n_seg > 1 ? *slot_of(0) : make_float4(0.f, 0.f, 0.f, 0.f);
   for (int i = 0; i < p.n_seg; ++i) {
     const int s = p.reverse ? p.n_seg - 1 - i : i;
-    float4* slot = reinterpret_cast<float4*>(seg + (int64_t)s * p.state_floats);
+    float4* slot = slot_of(i);
     if (i == p.n_seg - 1) { *slot = a; break; }      // the piece reached last has no local value: the walk itself ends it
+    const float4 next = i + 2 < p.n_seg ? *slot_of(i + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
     const int len = min(p.seg_len, p.T - s * p.seg_len);
     const float g = exp2f((float)len * lg);
-    const float4 loc = *slot;
     *slot = a;
     a.x = fmaf(g, a.x, loc.x); a.y = fmaf(g, a.y, loc.y); a.z = fmaf(g, a.z, loc.z); a.w = fmaf(g, a.w, loc.w);
+    loc = next;
   }
 }
 
