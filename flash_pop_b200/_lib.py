@@ -113,6 +113,8 @@ _SIGNATURES = {
     "fpb_groupnorm_gate_fwd": [ctypes.c_int32] * 5 + [ctypes.c_float, ctypes.c_int32, _SEQ_P, _SEQ_P, _SEQ_P, ctypes.c_void_p],
     "fpb_groupnorm_gate_bwd": [ctypes.c_int32] * 5 + [ctypes.c_float, ctypes.c_int32, _SEQ_P, _SEQ_P, _SEQ_P, _SEQ_P, _SEQ_P,
                                ctypes.c_void_p],
+    "fpb_copy_rows_async": [ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                            ctypes.c_void_p],
     "fpb_layernorm_fwd": [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_float, ctypes.c_void_p, ctypes.c_int64,
                           ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p],
     "fpb_layernorm_bwd": [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_float, ctypes.c_void_p, ctypes.c_int64,

@@ -263,6 +263,19 @@ int fpb_retention_fwd_static(const fpb_dims* dims, const fpb_seq* q, const fpb_s
                  (cudaStream_t)stream);
 }
 
+int fpb_copy_rows_async(void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch, int64_t width_bytes, int64_t rows,
+                        fpb_stream_t stream) {
+  if (rows == 0 || width_bytes == 0) return FPB_OK;
+  if (!dst || !src) return FPB_ERR_NULL_POINTER;
+  if (rows < 0 || width_bytes < 0 || dst_pitch < width_bytes || src_pitch < width_bytes) return FPB_ERR_BAD_STRIDE;
+  if (cudaMemcpy2DAsync(dst, (size_t)dst_pitch, src, (size_t)src_pitch, (size_t)width_bytes, (size_t)rows, cudaMemcpyDefault,
+                        (cudaStream_t)stream) != cudaSuccess) {
+    tl_last_cuda_error = (int)cudaGetLastError();
+    return FPB_ERR_LAUNCH;
+  }
+  return FPB_OK;
+}
+
 int fpb_retention_bwd(const fpb_dims* dims, const fpb_seq* q, const fpb_seq* k, const fpb_seq* v,
                       const fpb_state* s0, const fpb_seq* d_o, const fpb_state* d_s_out,
                       const fpb_seq* d_q, const fpb_seq* d_k, const fpb_seq* d_v, const fpb_state* d_s0,

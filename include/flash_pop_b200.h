@@ -102,6 +102,17 @@ int fpb_retention_fwd(const fpb_dims* dims, const fpb_seq* q, const fpb_seq* k, 
                       const fpb_state* s0, const fpb_seq* o, const fpb_state* s_out, fpb_stream_t stream);
 
 /*
+ * Host <-> device copy of a (batch rows, head group) slice of a contiguous (B, T, H, d) tensor: `rows` runs of
+ * `width_bytes` bytes, `src_pitch` / `dst_pitch` bytes apart (one run per (row, token): the heads of the group), queued
+ * on `stream` as ONE two-dimensional copy (cudaMemcpy2DAsync, direction from the pointers).  It lets
+ * flash_pop_b200.host_io pipeline its slices by heads as well as by rows - a strided slice copied tensor-wise by the
+ * framework goes through at a quarter of the link rate.  No counterpart in the reference, which keeps its tensors on
+ * the device.  Host memory should be pinned; widths and pitches in bytes, width <= both pitches.
+ */
+int fpb_copy_rows_async(void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch, int64_t width_bytes, int64_t rows,
+                        fpb_stream_t stream);
+
+/*
  * fpb_retention_fwd for callers that cannot allocate device memory.  This entry point has no counterpart in the
  * reference.  Who needs it: a host that hands the whole GPU to one arena at start-up (an inference server, a process
  * held to a fixed memory budget) has nothing left for a later cudaMalloc to take, and a plugin running on such a

@@ -175,17 +175,21 @@ def test_backward_runs_only_the_walks_that_are_needed():
     _lib.device_status()
 
 
-def test_host_memory_pipeline_equals_direct_call():
-    """Batch slices copied in / computed / copied out on three streams give the results of one direct call."""
+@pytest.mark.parametrize("B,H,dk,dv,slices,head_groups", [(4, 2, 128, 128, 3, 1), (4, 2, 128, 128, 3, None), (3, 8, 64, 128, None, 4),
+                                                          (2, 6, 128, 128, None, 3)])
+def test_host_memory_pipeline_equals_direct_call(B, H, dk, dv, slices, head_groups):
+    """Slices (batch rows x head groups) copied in / computed / copied out on three streams give the results of one
+    direct call, bit for bit; a head group crosses as one two-dimensional copy and must touch nothing beside it."""
     import flash_pop_b200 as fp
     from flash_pop_b200.host_io import HostRetentionPipeline
-    B, T, H, d = 4, 300, 2, 128
+    T = 300
     decays = orc.head_decays(H, (5, 12))
-    q, k, v, _, g = make_inputs(6, B, T, H, d, d, BF, state=False)
-    dO = torch.randn(B, T, H, d, generator=g).to(BF)
+    q, k, v, _, g = make_inputs(6, B, T, H, dk, dv, BF, state=False)
+    dO = torch.randn(B, T, H, dv, generator=g).to(BF)
     host = [t.pin_memory() for t in (q, k, v, dO)]
-    outs = [torch.empty_like(q).pin_memory() for _ in range(4)]
-    pipe = HostRetentionPipeline(q, v, "cuda", slices=3)
+    outs = [torch.empty_like(t).pin_memory() for t in (v, q, k, v)]
+    pipe = HostRetentionPipeline(q, v, "cuda", slices=slices, head_groups=head_groups)
+    assert pipe.slices == (slices or B) * (head_groups or (H if (slices or B) * H <= pipe.TARGET_SLICES else 1))
     pipe.run(*host, decays, *outs)
     torch.cuda.synchronize()
     leaves = [t.cuda().requires_grad_(True) for t in (q, k, v)]
