@@ -86,6 +86,10 @@ def test_layer_pass_and_step_entry_points_check_arguments_without_a_device(handl
     assert handle.fpb_layernorm_fwd(8, 2048, 0, 1e-6, None, 2048, None, None, None, 2048, None) == 2
     assert handle.fpb_layernorm_fwd(8, 64, 0, 1e-6, None, 64, None, None, None, 64, None) == 1
     assert handle.fpb_layernorm_bwd(8, 64, 3, 1e-6, None, 64, None, None, 64, None, None, None, None) == 3
+    # two-dimensional copy: nothing to do is fine, pointers and pitches are checked before anything is queued
+    assert handle.fpb_copy_rows_async(None, 64, None, 64, 32, 0, None) == 0
+    assert handle.fpb_copy_rows_async(None, 64, None, 64, 32, 4, None) == 1
+    assert handle.fpb_copy_rows_async(0x1000, 16, 0x2000, 64, 32, 4, None) == 4
     # decoding step: one token per row
     assert handle.fpb_retention_step(_dims(T=2), 0, seq, seq, seq, st, seq, st, None) == 2
     assert handle.fpb_retention_step(_dims(T=1), 4, seq, seq, seq, st, seq, st, None) == 3
