@@ -565,20 +565,13 @@ def main():
         with allocate_near(dev):
             outs_host = [torch.empty_like(hv).pin_memory(), torch.empty_like(hq).pin_memory(),
                          torch.empty_like(hk).pin_memory(), torch.empty_like(hv).pin_memory()]
-        if w["block"]:
-            def e2e_step(copy_only=False):
-                q.copy_(hq, non_blocking=True); k.copy_(hk, non_blocking=True)
-                v.copy_(hv, non_blocking=True); dO.copy_(hdO, non_blocking=True)
-                res = (dO, q, k, v) if copy_only else step()
-                for dst, src in zip(outs_host, res):
-                    dst.copy_(src, non_blocking=True)
-        else:
-            # the package's host-memory helper: batch slices, copies in / kernels / copies out on three streams
-            from flash_pop_b200.host_io import HostRetentionPipeline
-            pipe = HostRetentionPipeline(hq, hv, dev)
+        # the package's host-memory helper: slices (batch rows x head groups; whole rows for POP), copies in / kernels /
+        # copies out on three streams
+        from flash_pop_b200.host_io import HostRetentionPipeline
+        pipe = HostRetentionPipeline(hq, hv, dev, block_size=w["block"] or 0)
 
-            def e2e_step(copy_only=False):
-                pipe.run(hq, hk, hv, hdO, dec, *outs_host, copy_only=copy_only)
+        def e2e_step(copy_only=False):
+            pipe.run(hq, hk, hv, hdO, dec, *outs_host, copy_only=copy_only)
 
         e2e_step()
         barrier()

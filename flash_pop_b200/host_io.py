@@ -14,6 +14,7 @@ import torch
 
 from flash_pop_b200 import _lib
 from flash_pop_b200.fused_retention import retention_forward_backward_into
+from flash_pop_b200.pop_retention import pop_retention_forward_backward_into
 
 
 class HostRetentionPipeline:
@@ -28,9 +29,16 @@ class HostRetentionPipeline:
     TARGET_SLICES = 32
 
     def __init__(self, like_q: torch.Tensor, like_v: torch.Tensor, device, slices: Optional[int] = None,
-                 head_groups: Optional[int] = None):
-        B, _, H, _ = like_q.shape
+                 head_groups: Optional[int] = None, block_size: int = 0):
+        """block_size > 0: POP retention with blocks of that many tokens (the block states of a slice stay on the device
+        in `self.block_states`; they are contiguous over all heads, so POP slices are whole batch rows)."""
+        B, T, H, dk = like_q.shape
         row_slices = min(B, slices or B)
+        self.block_size = int(block_size)
+        if self.block_size > 0:
+            if head_groups not in (None, 1):
+                raise ValueError("POP slices are whole batch rows")
+            head_groups = 1
         if head_groups is None:
             # the largest divisor of H that keeps the slice count at or below the target
             head_groups = max(g for g in range(1, H + 1) if H % g == 0 and (g == 1 or row_slices * g <= self.TARGET_SLICES))
@@ -44,6 +52,11 @@ class HostRetentionPipeline:
         mk = lambda t: torch.empty(t.shape, dtype=t.dtype, device=self.device)
         self.q, self.k, self.dq, self.dk = mk(like_q), mk(like_q), mk(like_q), mk(like_q)
         self.v, self.do, self.o, self.dv = mk(like_v), mk(like_v), mk(like_v), mk(like_v)
+        self.block_states = None
+        if self.block_size > 0:
+            rows_max = max(b - a for a, b, _, _ in self.parts)
+            self.block_states = torch.empty((rows_max, T // self.block_size, H, dk, like_v.shape[-1]), dtype=like_q.dtype,
+                                            device=self.device)
         self.s_in, self.s_comp, self.s_out = (torch.cuda.Stream(self.device) for _ in range(3))
 
     def _copy(self, dst: torch.Tensor, src: torch.Tensor, a: int, b: int, h0: int, h1: int) -> None:
@@ -77,8 +90,13 @@ class HostRetentionPipeline:
                     self.s_comp.wait_event(landed)
                     if not copy_only:
                         part = lambda t: t[a:b, :, h0:h1]
-                        retention_forward_backward_into(part(self.q), part(self.k), part(self.v), part(self.do), head_decays[h0:h1],
-                                                        part(self.o), part(self.dq), part(self.dk), part(self.dv))
+                        if self.block_size > 0:
+                            pop_retention_forward_backward_into(part(self.q), part(self.k), part(self.v), part(self.do), head_decays,
+                                                                self.block_size, part(self.o), self.block_states[:b - a],
+                                                                part(self.dq), part(self.dk), part(self.dv))
+                        else:
+                            retention_forward_backward_into(part(self.q), part(self.k), part(self.v), part(self.do), head_decays[h0:h1],
+                                                            part(self.o), part(self.dq), part(self.dk), part(self.dv))
                     done = self.s_comp.record_event()
                 with torch.cuda.stream(self.s_out):
                     self.s_out.wait_event(done)

@@ -77,6 +77,29 @@ class FlashPOPRetention(torch.autograd.Function):
 flash_pop_retention = FlashPOPRetention.apply
 
 
+def pop_retention_forward_backward_into(q, k, v, dO, head_decays: Sequence[float], block_size: int, o, block_states, dQ, dK, dV) -> None:
+    """Forward and backward of POP retention (zero start state, no gradient into the block states) written straight
+    into tensors the caller provides - views of a staging buffer, say: two calls of the C ABI, no autograd graph, no
+    copies.  q ... dV (B,T,H,d) with unit inner stride; block_states (B, T // block_size, H, dk, dv) contiguous, of q's
+    dtype."""
+    _lib.require_cuda(q, k, v, dO, o, block_states, dQ, dK, dV)
+    head_decays = tuple(float(g) for g in head_decays)
+    B, T, H, dk = q.shape
+    dv = v.shape[-1]
+    for t in (q, k, v, dO, o, dQ, dK, dV):
+        if t.stride(-1) != 1:
+            raise ValueError("pop_retention_forward_backward_into takes tensors with unit inner stride")
+    if tuple(block_states.shape) != (B, T // int(block_size), H, dk, dv) or not block_states.is_contiguous() or block_states.dtype != q.dtype:
+        raise ValueError("block_states must be a contiguous (B, T // block_size, H, dk, dv) tensor of q's dtype")
+    with torch.cuda.device(q.device):
+        stream = _lib.stream_ptr(q.device)
+        d = _lib.dims(q, dv, head_decays, block_size=int(block_size), flags=_flags(), workspace=True)
+        _lib.check(_lib.lib().fpb_pop_retention_fwd(d, _lib.seq(q), _lib.seq(k), _lib.seq(v), _lib.state(None), _lib.seq(o),
+                                                    block_states.data_ptr(), stream))
+        _lib.check(_lib.lib().fpb_pop_retention_bwd(d, _lib.seq(q), _lib.seq(k), _lib.seq(v), _lib.state(None), _lib.seq(dO), None,
+                                                    _lib.seq(dQ), _lib.seq(dK), _lib.seq(dV), _lib.state(None), stream))
+
+
 class POPSuffixRetention(torch.autograd.Function):
 
     @staticmethod

@@ -199,6 +199,27 @@ def test_host_memory_pipeline_equals_direct_call(B, H, dk, dv, slices, head_grou
         assert torch.equal(got, want.detach().cpu())
 
 
+def test_host_memory_pipeline_pop():
+    """POP retention through the host pipeline (whole batch rows per slice) equals one direct call, bit for bit."""
+    import flash_pop_b200 as fp
+    from flash_pop_b200.host_io import HostRetentionPipeline
+    B, T, H, d, block = 3, 400, 2, 64, 80
+    decays = orc.head_decays(H, (5, 12))
+    q, k, v, _, g = make_inputs(7, B, T, H, d, d, BF, state=False)
+    dO = torch.randn(B, T, H, d, generator=g).to(BF)
+    host = [t.pin_memory() for t in (q, k, v, dO)]
+    outs = [torch.empty_like(q).pin_memory() for _ in range(4)]
+    pipe = HostRetentionPipeline(q, v, "cuda", block_size=block)
+    assert pipe.slices == B
+    pipe.run(*host, decays, *outs)
+    torch.cuda.synchronize()
+    leaves = [t.cuda().requires_grad_(True) for t in (q, k, v)]
+    o, _ = fp.flash_pop_retention(*leaves, None, decays, block)
+    o.backward(dO.cuda())
+    for got, want in zip(outs, (o, leaves[0].grad, leaves[1].grad, leaves[2].grad)):
+        assert torch.equal(got, want.detach().cpu())
+
+
 @pytest.mark.parametrize("M,N,P,d", [(8, 8, 80, 64), (12, 12, 40, 64), (9, 8, 80, 64), (6, 6, 100, 128)])
 def test_grouped_suffix_walks_equal_one_cta_per_suffix(M, N, P, d):
     """Consecutive suffixes of a row walked by one CTA as one sequence (state replaced at every suffix start) give
