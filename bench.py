@@ -449,9 +449,9 @@ NCU_TRAFFIC = {
                            "ncu at B=2 (zero fill of dQ and the dQ walk over the two halves of dv), scaled x2 by token-heads"),
     ("c3", "rev"): _traffic(21248 + 1914728704, 211275776 + 790550272, 2,
                             "ncu at B=2 (zero fill of dK and the fused reverse walk over the two halves of dv), scaled x2 by token-heads"),
-    ("c4", "fwd"): _traffic(251720960, 112434176, 1, "ncu at the full workload"),
-    ("c4", "dq"): _traffic(251710208, 60016384, 1, "ncu at the full workload"),
-    ("c4", "rev"): _traffic(335696896, 136674560, 1, "ncu at the full workload"),
+    ("c4", "fwd"): _traffic(251772416, 112364800, 1, "ncu at the full workload"),
+    ("c4", "dq"): _traffic(251708672, 60882944, 1, "ncu at the full workload"),
+    ("c4", "rev"): _traffic(402802432, 141126400, 1, "ncu at the full workload (block-state gradients read)"),
 }
 
 
@@ -507,11 +507,26 @@ def main():
             return fp.flash_pop_retention(q_, k_, v_, None, decays, w["block"])[0]
         return fp.fused_chunk_retention(q_, k_, v_, None, decays)[0]
 
+    # POP: in training the block states feed the prediction suffixes, so their gradient comes back into the backward of the
+    # observation stream (added to the carried state gradient at every block end); the step has it, seeded like dO
+    d_blocks = None
+    if w["block"]:
+        gb = torch.Generator(device=dev).manual_seed(70 + rank)
+        d_blocks = (torch.randn(B, T // w["block"], H, dk, dv, generator=gb, device=dev) * 0.1).to(torch.bfloat16)
+
+    def outputs_and_grads(q_, k_, v_):
+        """What the backward starts from: (outputs that carry a gradient, those gradients)."""
+        if w["block"]:
+            o, blocks = fp.flash_pop_retention(q_, k_, v_, None, dec, w["block"])
+            return (o, blocks), (dO, d_blocks)
+        o = fp.fused_chunk_retention(q_, k_, v_, None, dec)[0]
+        return (o,), (dO,)
+
     def step():
         ql, kl, vl = (t.detach().requires_grad_(True) for t in (q, k, v))
-        o = op(ql, kl, vl)
-        o.backward(dO)
-        return o, ql.grad, kl.grad, vl.grad
+        outs, grads = outputs_and_grads(ql, kl, vl)
+        torch.autograd.backward(outs, grads)
+        return outs[0], ql.grad, kl.grad, vl.grad
 
     def fwd_only():
         with torch.no_grad():
@@ -546,9 +561,9 @@ def main():
 
     def only_grads(of):
         leaves = [t.detach().requires_grad_(i in of) for i, t in enumerate((q, k, v))]
-        o = op(*leaves)
+        outs, grads = outputs_and_grads(*leaves)
         wanted = [leaves[i] for i in of]
-        return lambda: torch.autograd.grad(o, wanted, dO, retain_graph=True)
+        return lambda: torch.autograd.grad(outs, wanted, grads, retain_graph=True)
 
     fn_dq, fn_rev = only_grads((0,)), only_grads((1, 2))
     fn_dq(); fn_rev()
@@ -701,7 +716,9 @@ def main():
         pop_state = (2 * dk * dv * 2 * H * B * (T // w["block"])) if w["block"] else 0     # block states written / their gradients read
         # the launches of a step with their algorithmic bytes: forward (read q,k,v; write o), the dQ walk (read dO,k,v; write
         # dQ), the reverse walk(s) (read q,k,v,dO; write dK,dV) - one fused launch, or two launches where dv = 256
-        fused = launches_rev == 1 or launches_rev == 3
+        # (dk, dv up to 128: one fused launch, three when cut into T-segments; dk = 128 beside dv = 256 without POP blocks:
+        # the fused kernel over the two halves of dv after a zero fill of dK; otherwise two reverse walks)
+        fused = max(dk, dv) <= 128 or (dk == 128 and dv == 256 and not w["block"])
         kernels = {
             "fwd": {"kernel": "scan_kernel<MODE_FWD, forward>", "ms": ms_fwd, "bytes": bf * units + pop_state // 2},
             "dq": {"kernel": "scan_kernel<MODE_DQ, forward> (dQ walk)", "ms": ms_dq, "bytes": 2 * (dk + 2 * dv + dk) * units,

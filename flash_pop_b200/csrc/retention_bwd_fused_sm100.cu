@@ -43,6 +43,7 @@ constexpr int N_SCORE = 128;
 
 struct BwdParams {
   CUtensorMap map_q, map_k, map_v, map_do, map_dk, map_dv;
+  CUtensorMap map_bg;                            // POP, 64 x 64, bf16 states: the block-state gradients, one 64 x 64 box per (row, block, head)
   bf16* dk_out; int64_t dk_sb, dk_st, dk_sh;
   bf16* dv_out; int64_t dv_sb, dv_st, dv_sh;
   // states are bf16 or fp32 (state_f32), strides in elements
@@ -64,7 +65,7 @@ struct BwdParams {
 constexpr int MAXS = 5;          // most stages a configuration may have
 enum { B_FULL = 0, B_EMPTY = MAXS, B_VRDY = 2 * MAXS, B_SCFULL = 3 * MAXS, B_PRDY = B_SCFULL + 2, B_ACCFULL = B_PRDY + 2,
        B_ACCFREE = B_ACCFULL + 1, B_DSFULL = B_ACCFREE + 1, B_DSFREE = B_DSFULL + 2, B_SBRDY = B_DSFREE + 2, B_SBFREE = B_SBRDY + 1,
-       B_COUNT = B_SBFREE + 1 };
+       B_PFFULL = B_SBFREE + 1, B_PFFREE = B_PFFULL + 1, B_COUNT = B_PFFREE + 1 };
 constexpr int OFF_TMEM_SLOT = B_COUNT * 8, OFF_ABORT = OFF_TMEM_SLOT + 4, OFF_LIMIT = OFF_ABORT + 4, BAR_PAGE = 256;
 static_assert(OFF_LIMIT % 8 == 0 && OFF_LIMIT + 8 <= BAR_PAGE, "the wait limit sits right after the abort flag");
 
@@ -83,7 +84,9 @@ struct BCfg {
   static constexpr int P_BYTES = C * C * 2;
   static constexpr int NP = 2;
   static constexpr int GB_BYTES = DK * DV * 2;
-  static constexpr int FIXED = 2 * NP * P_BYTES + GB_BYTES + C * DV * 2 + C * DK * 2 + BAR_PAGE;
+  // POP: the block-state gradient that the walk adds next, fetched one block ahead by a bulk copy (64 x 64, bf16 states)
+  static constexpr int PF_BYTES = (DK == 64 && DV == 64) ? DK * DV * 2 : 0;
+  static constexpr int FIXED = 2 * NP * P_BYTES + GB_BYTES + C * DV * 2 + C * DK * 2 + BAR_PAGE + PF_BYTES;
   static constexpr int SMEM_LIMIT = 226 * 1024;
   // as many stages as the shared memory of the SM holds (the CTA has it to itself): 3 at d = 128, 5 at d = 64, where a
   // chunk's few kilobytes leave the walk bound by the number of chunks in flight
@@ -96,7 +99,8 @@ struct BCfg {
   static constexpr int OFF_GB = OFF_P2 + NP * P_BYTES;
   static constexpr int OFF_OUTV = OFF_GB + GB_BYTES;
   static constexpr int OFF_OUTK = OFF_OUTV + C * DV * 2;
-  static constexpr int OFF_BAR = OFF_OUTK + C * DK * 2;
+  static constexpr int OFF_PF = OFF_OUTK + C * DK * 2;       // (a swizzled TMA tile: 1024-byte aligned like the others)
+  static constexpr int OFF_BAR = OFF_PF + PF_BYTES;
   static constexpr int SMEM = OFF_BAR + BAR_PAGE;
   static_assert(SMEM <= SMEM_LIMIT, "shared memory budget");
   // tensor memory: Sc1 (2 buffers in lanes) | Sc2 (2 buffers in lanes) | ACCV (lanes 0-15) + ACCK (lanes 16-31) | dG x2
@@ -155,11 +159,13 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
     }
     mbar_init(bar(B_ACCFULL), 1); mbar_init(bar(B_ACCFREE), N_SCORE);
     mbar_init(bar(B_SBRDY), G::N_STATE); mbar_init(bar(B_SBFREE), 1);
+    mbar_init(bar(B_PFFULL), 1); mbar_init(bar(B_PFFREE), G::N_STATE);
     fence_mbar_init();
     *abort_flag = 0;
     *reinterpret_cast<volatile long long*>(sm + G::OFF_BAR + OFF_LIMIT) = p.tune.wait_cycles;
     prefetch_tmap(&p.map_q); prefetch_tmap(&p.map_k); prefetch_tmap(&p.map_v); prefetch_tmap(&p.map_do);
     prefetch_tmap(&p.map_dk); prefetch_tmap(&p.map_dv);
+    if (G::PF_BYTES > 0 && !SF32 && p.block_grads) prefetch_tmap(&p.map_bg);
   }
   if (warp == 1) { tmem_alloc(sbase + G::OFF_BAR + OFF_TMEM_SLOT, G::TM_COLS); tmem_relinquish(); }
   tc_fence_before();
@@ -525,10 +531,49 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
       }
       }
     };
+    // POP: the gradient of a block state is added to G where the block ends.  Loaded at that moment into the register
+    // layout of the state - 4-byte pieces, 512 sectors in flight per CTA - it stalled the walk's chunk-to-chunk chain for
+    // a DRAM round trip and more (64 block ends per sequence cost the reverse walk 29 %).  The walk knows which block
+    // comes next (the one before), so one thread fetches its gradient a block ahead with ONE TMA copy into shared
+    // memory (a 64 x 64 tile, 128-byte swizzled: read back in the state's register layout - eight rows per warp
+    // instruction - a plain row-major tile would put all eight on the same banks), and the addition reads it from there.
+    // (The 64 x 64 instance with bf16 states - the POP shape; the others have no shared memory to spare.)
+    constexpr bool PREFETCH = G::PF_BYTES > 0 && !SF32;
+    int pf_blk = -1, pf_want = -1, pf_issued = 0, pf_taken = 0;
+    auto block_grad = [&](int blk) { return at(p.block_grads, (((int64_t)b * p.n_blocks + blk) * p.H + h) * state_elems); };
+    auto prefetch = [&](int blk) {
+      if (t == 0) {
+        // the buffer is free once every state thread has read the previous gradient out of it
+        if (pf_issued > 0 && !mbar_wait(bar(B_PFFREE), (pf_issued - 1) & 1, abort_flag)) FPB_GIVE_UP(0x4fe);
+        else {
+          mbar_arrive_expect_tx(bar(B_PFFULL), G::PF_BYTES);
+          tma_load_4d(sbase + G::OFF_PF, &p.map_bg, bar(B_PFFULL), 0, 0, blk * p.H + h, b);
+        }
+      }
+      pf_blk = blk; ++pf_issued;
+    };
+    auto add_prefetched = [&]() {
+      if (!mbar_wait(bar(B_PFFULL), (pf_issued - 1) & 1, abort_flag)) { FPB_GIVE_UP(0x4fd); return; }
+      const uint8_t* src = sm + G::OFF_PF;             // [64 rows][128 B], 16-byte pieces XOR-swizzled by (row & 7)
+#pragma unroll
+      for (int i = 0; i < G::NS; i += 2) {
+        const int row = row_of(i), col = col_of(i);
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + row * 128 + (((col >> 3) ^ (row & 7)) << 4) + (col & 7) * 2));
+        S[i] += f.x; S[i + 1] += f.y;
+      }
+      mbar_arrive(bar(B_PFFREE));
+      ++pf_taken;
+    };
     auto inject = [&](int end) {
-      if (p.block_size > 0 && p.block_grads && end % p.block_size == 0 && end / p.block_size - 1 < p.n_blocks)
-        load_global(at(p.block_grads, (((int64_t)b * p.n_blocks + (end / p.block_size - 1)) * p.H + h) * state_elems),
-                    state_t, true);
+      if (p.block_size > 0 && p.block_grads && end % p.block_size == 0 && end / p.block_size - 1 < p.n_blocks) {
+        const int blk = end / p.block_size - 1;
+        if (PREFETCH && pf_blk == blk) add_prefetched();
+        else load_global(block_grad(blk), state_t, true);
+        // the walk's next block end, going down: the start of this block, if this CTA's piece reaches below it.  The
+        // fetch is issued after the state copy that follows (thread 0 first waits for the other warps to have read the
+        // buffer: better while the walk waits for the next increment than in front of the copy).
+        if (PREFETCH && blk > 0 && (int64_t)blk * p.block_size > t0) pf_want = blk - 1;
+      }
     };
     auto store_global = [&](void* dst_) {
       if constexpr (SF32) {
@@ -636,6 +681,7 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
             publish_gb();
             if (t == 0) FPB_TRACE(13, n_u);
             publish_due = false; progress = true;
+            if (PREFETCH && pf_want >= 0) { prefetch(pf_want); pf_want = -1; }
           }
         } else if (mbar_test_wait(bar(B_DSFULL + (n_u & 1)), (n_u >> 1) & 1)) {
           if (t == 0) FPB_TRACE(12, n_u);
@@ -673,6 +719,10 @@ __global__ void __launch_bounds__(BCfg<DK, DV>::NTHREADS, 1) bwd_fused_kernel(co
       }
     }
     if (x_end && !*abort_flag) store_global(x_end);
+    if (PREFETCH && t == 0 && pf_issued > pf_taken) {      // (only after a give-up) let the copy in flight land
+      const long long w0 = clock64();
+      while (!mbar_try_wait(bar(B_PFFULL), (pf_issued - 1) & 1) && clock64() - w0 < wait_limit(abort_flag)) {}
+    }
   }
 
   // ---------------- teardown
@@ -755,6 +805,11 @@ int launch_bwd_fused(const UmmaBwdArgs& a, cudaStream_t stream, int* n_launched)
   if ((r = make_seq_map(&p.map_do, dO, B, T, H, a.dv, C)) != FPB_OK) return r;
   if ((r = make_seq_map(&p.map_dk, dK, B, T, H, a.dk, C)) != FPB_OK) return r;
   if ((r = make_seq_map(&p.map_dv, dV, B, T, H, a.dv, C)) != FPB_OK) return r;
+  if (a.dk == 64 && a.dv == 64 && !a.state_f32 && a.d_block_states && a.n_blocks > 0) {
+    // (B, N, H, dk, dv) contiguous as a 4-D tensor of 64-wide rows: dk rows per (block, head), N * H of those per batch row
+    const SeqView bg{const_cast<void*>(a.d_block_states), (int64_t)a.n_blocks * H * a.dk * a.dv, (int64_t)a.dv, (int64_t)a.dk * a.dv};
+    if ((r = make_seq_map(&p.map_bg, bg, B, a.dk, a.n_blocks * H, a.dv, C)) != FPB_OK) return r;
+  }
   p.dk_out = (bf16*)dK.data; p.dk_sb = dK.sb; p.dk_st = dK.st; p.dk_sh = dK.sh;
   p.dv_out = (bf16*)dV.data; p.dv_sb = dV.sb; p.dv_st = dV.st; p.dv_sh = dV.sh;
   const bool split = sg.n > 1;
