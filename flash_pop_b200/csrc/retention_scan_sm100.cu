@@ -981,21 +981,51 @@ FPB_UNROLL_MMA
         ++m_part; partial_due = false;
       };
       // U(n_u): S <- gamma^L S + dS(n_u) (its barrier has completed), and what follows a chunk's end
-      auto update_state = [&]() {
+      // with_emit (EMIT walks): the partial increment of the chunk is complete as well - the block state and the update
+      // are made in one pass over the registers, both tensor-memory loads in flight together
+      auto update_state = [&](bool with_emit) {
         if (t == 0) FPB_TRACE(12, n_u);
         tc_fence_after();
         const float gl = exp2f((float)ck_u.L * lg);
-        // 16 registers at a time keeps the state warps inside the register budget
+        auto plain_update = [&]() {
+          // 16 registers at a time keeps the state warps inside the register budget
 #pragma unroll
-        for (int i0 = 0; i0 < (FPB_ABL(16) ? 0 : G::NS); i0 += TSTEP) {
-          uint32_t r[TSTEP];
-          if constexpr (R == 128) tmem_ld_32x32b_x16(tm + lane_base + tm_ds(n_u) + wcol0 + i0, r);
-          else tmem_ld_16x256b_x4(tm + lane_base + tm_ds(n_u) + wcol0 + i0 * 2, r);
-          tmem_wait_ld();
+          for (int i0 = 0; i0 < (FPB_ABL(16) ? 0 : G::NS); i0 += TSTEP) {
+            uint32_t r[TSTEP];
+            if constexpr (R == 128) tmem_ld_32x32b_x16(tm + lane_base + tm_ds(n_u) + wcol0 + i0, r);
+            else tmem_ld_16x256b_x4(tm + lane_base + tm_ds(n_u) + wcol0 + i0 * 2, r);
+            tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < TSTEP; ++i) S[i0 + i] = fmaf(gl, S[i0 + i], ds_scale * __uint_as_float(r[i]));
-        }
-        tc_fence_before();
+            for (int i = 0; i < TSTEP; ++i) S[i0 + i] = fmaf(gl, S[i0 + i], ds_scale * __uint_as_float(r[i]));
+          }
+          tc_fence_before();
+        };
+        if constexpr (G::EMIT && DEEP) {     // (the deep variant has the registers for both tiles in flight)
+          if (with_emit) {
+            const int pmid = mid_end(n_u);
+            const float gp = exp2f((float)pmid * lg), up = exp2f(-(float)(ck_u.L - pmid) * lg) * rs;
+            void* dst_ = at(p.block_states, (((int64_t)b * p.n_blocks + ((ck_u.a + pmid) / p.block_size - 1)) * p.H + h) * state_elems);
+#pragma unroll
+            for (int i0 = 0; i0 < G::NS; i0 += TSTEP) {
+              uint32_t rp[TSTEP], r[TSTEP];
+              tmem_ld_16x256b_x4(tm + lane_base + G::TM_DSP + wcol0 + i0 * 2, rp);
+              tmem_ld_16x256b_x4(tm + lane_base + tm_ds(n_u) + wcol0 + i0 * 2, r);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < TSTEP; i += 2) {
+                const float lo = fmaf(gp, S[i0 + i], up * __uint_as_float(rp[i])), hi = fmaf(gp, S[i0 + i + 1], up * __uint_as_float(rp[i + 1]));
+                const int64_t off = (int64_t)(row0 + row_of(i0 + i)) * p.dv + col0 + col_of(i0 + i);
+                if (SF32) *reinterpret_cast<float2*>((float*)dst_ + off) = make_float2(lo, hi);
+                else *reinterpret_cast<uint32_t*>((bf16*)dst_ + off) = pack_bf16(lo, hi);
+                S[i0 + i] = fmaf(gl, S[i0 + i], ds_scale * __uint_as_float(r[i]));
+                S[i0 + i + 1] = fmaf(gl, S[i0 + i + 1], ds_scale * __uint_as_float(r[i + 1]));
+              }
+            }
+            tc_fence_before();
+            warp_arrive(bar(B_DSPFREE));
+            ++m_part; partial_due = false;
+          } else plain_update();
+        } else plain_update();
         warp_arrive(bar(B_DSFREE + (n_u & 1)));   // the increment has been read: the one after next may overwrite it
         const int end = ck_u.a + ck_u.L;
         if (!REV && !SO && p.block_size > 0 && p.block_states && end % p.block_size == 0 && end / p.block_size - 1 < p.n_blocks)
@@ -1041,11 +1071,13 @@ FPB_UNROLL_MMA
           }
         } else if (G::EMIT && partial_due) {
           if (mbar_test_wait(bar(B_DSPFULL), m_part & 1)) {
-            emit_block_state();
+            // (the partial increment is issued right after the full one, so the latter is normally complete too)
+            if (DEEP && mbar_test_wait(bar(B_DSFULL + (n_u & 1)), (n_u >> 1) & 1)) update_state(true);
+            else emit_block_state();
             progress = true;
           }
         } else if (mbar_test_wait(bar(B_DSFULL + (n_u & 1)), (n_u >> 1) & 1)) {
-          update_state();
+          update_state(false);
           progress = true;
         }
         if constexpr (G::ONE) try_scale();
